@@ -1,0 +1,150 @@
+"""Decoder-only Transformer language model (dense or mixture-of-experts).
+
+Architecture options, block math and checkpoint key names follow the reference
+(``ajllm/modeling/transformer.py:13-126``): pre-norm ``h = x + Attn(N1 x); y = h + FFN(N2 h)`` or
+post-norm ``h = N1(x + Attn x); y = N2(h + FFN h)``; RoPE / learned / no positions; RMSNorm or none;
+SwiGLU or SiLU FFN; tied or untied head; ``final_norm`` only with pre-norm. Extensions: grouped KV
+heads, MoE feed-forward, tensor/expert parallel shards.
+
+Internally the residual stream is ``[tokens, d_model]`` (this rank's tokens under tensor parallelism)
+and, in the pre-norm RMSNorm configuration, each residual add is fused with the norm that follows it.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ajllm_b200 import ops
+from ajllm_b200.models.attention import SelfAttention
+from ajllm_b200.models.feed_forward import make_feed_forward
+from ajllm_b200.models.layers import Embedding, InitSpec, Linear, make_norm
+from ajllm_b200.models.moe import MoEFeedForward
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, d_model: int, num_heads: int, num_kv_heads: int | None, d_ff: int, context_length: int,
+                 position_encoding: str, rope_theta: float, normalization: str, norm_placement: str,
+                 feed_forward: str, moe: dict | None = None, init: InitSpec = InitSpec(),
+                 tp=None, ep=None, norm_epsilon: float = 1e-5) -> None:
+        super().__init__()
+        if norm_placement not in {"pre", "post"}:
+            raise ValueError("normalization.placement must be 'pre' or 'post'")
+        self.norm_placement = norm_placement
+        self.norm1 = make_norm(normalization, d_model, norm_epsilon)
+        self.norm2 = make_norm(normalization, d_model, norm_epsilon)
+        self.attention = SelfAttention(d_model, num_heads, num_kv_heads, context_length, position_encoding,
+                                       rope_theta, init, tp)
+        if moe:
+            self.feed_forward = MoEFeedForward(d_model, moe, init, ep)
+        else:
+            self.feed_forward = make_feed_forward(feed_forward, d_model, d_ff, init, tp)
+
+    def forward_prenorm(self, stream: torch.Tensor, pending: torch.Tensor | None, batch_shape):
+        """``stream + pending`` is the block input; returns the new ``(stream, pending)`` pair so the
+        caller (or the next block) can fuse the last residual add with its norm."""
+        stream, normed = self.norm1.add_and_norm(stream, pending)
+        attended = self.attention(normed, batch_shape)
+        stream, normed = self.norm2.add_and_norm(stream, attended)
+        return stream, self.feed_forward(normed)
+
+    def forward_postnorm(self, x: torch.Tensor, batch_shape) -> torch.Tensor:
+        hidden = self.norm1(x + self.attention(x, batch_shape))
+        return self.norm2(hidden + self.feed_forward(hidden))
+
+
+class TransformerLM(nn.Module):
+    def __init__(self, vocab_size: int, context_length: int, d_model: int, num_layers: int, num_heads: int,
+                 d_ff: int, num_kv_heads: int | None = None, position_encoding: str = "rope",
+                 rope_theta: float = 10_000.0, normalization: str = "rmsnorm", norm_placement: str = "pre",
+                 feed_forward: str = "swiglu", tie_embeddings: bool = False, moe: dict | None = None,
+                 init: InitSpec = InitSpec(), tp=None, ep=None, norm_epsilon: float = 1e-5,
+                 activation_checkpointing: str = "none") -> None:
+        super().__init__()
+        if position_encoding not in {"rope", "none", "learned"}:
+            raise ValueError("position encoding must be rope, none, or learned")
+        self.vocab_size, self.context_length, self.d_model = vocab_size, context_length, d_model
+        self.num_layers, self.num_heads, self.d_ff = num_layers, num_heads, d_ff
+        self.num_kv_heads = num_kv_heads or num_heads
+        self.position_encoding, self.normalization = position_encoding, normalization
+        self.norm_placement, self.feed_forward_type = norm_placement, feed_forward
+        self.tie_embeddings, self.moe = tie_embeddings, moe
+        self.rope_theta = rope_theta
+        self.tp, self.ep = tp, ep
+        self.activation_checkpointing = activation_checkpointing
+
+        self.token_embeddings = Embedding(vocab_size, d_model, init)
+        self.position_embeddings = Embedding(context_length, d_model, init) if position_encoding == "learned" else None
+        self.layers = nn.ModuleList([
+            TransformerBlock(d_model, num_heads, num_kv_heads, d_ff, context_length, position_encoding, rope_theta,
+                             normalization, norm_placement, feed_forward, moe, init, tp, ep, norm_epsilon)
+            for _ in range(num_layers)
+        ])
+        self.final_norm = make_norm(normalization if norm_placement == "pre" else "none", d_model, norm_epsilon)
+        self.lm_head = None if tie_embeddings else Linear(d_model, vocab_size, init)
+
+    # ------------------------------------------------------------------ pieces
+    @property
+    def head_weight(self) -> torch.Tensor:
+        return self.token_embeddings.weight if self.tie_embeddings else self.lm_head.weight
+
+    def _local_tokens(self, flat: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None and self.tp.size > 1:
+            return self.tp.local_rows(flat)
+        return flat
+
+    def hidden_states(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """Final-norm output for this rank's tokens, ``[local_tokens, d_model]``."""
+        B, T = token_ids.shape
+        if T > self.context_length:
+            raise ValueError(f"Input length {T} exceeds context length {self.context_length}")
+        ids = self._local_tokens(token_ids.reshape(-1))
+        stream = self.token_embeddings(ids)
+        if self.position_embeddings is not None:
+            positions = torch.arange(T, device=token_ids.device).repeat(B)
+            stream = stream + self.position_embeddings(self._local_tokens(positions))
+        shape = (B, T)
+        if self.norm_placement == "pre":
+            pending = None
+            for layer in self.layers:
+                if self.activation_checkpointing == "layer" and torch.is_grad_enabled():
+                    from torch.utils.checkpoint import checkpoint
+                    stream, pending = checkpoint(layer.forward_prenorm, stream, pending, shape, use_reentrant=False)
+                else:
+                    stream, pending = layer.forward_prenorm(stream, pending, shape)
+            return self.final_norm.add_and_norm(stream, pending)[1]
+        for layer in self.layers:
+            stream = layer.forward_postnorm(stream, shape)
+        return stream
+
+    def aux_loss(self) -> torch.Tensor | None:
+        terms = [layer.feed_forward.last_aux_loss for layer in self.layers
+                 if isinstance(layer.feed_forward, MoEFeedForward) and layer.feed_forward.last_aux_loss is not None]
+        return sum(terms) if terms else None
+
+    # ------------------------------------------------------------------ public
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """Logits ``[B, T, vocab]`` (all tokens on every rank)."""
+        B, T = token_ids.shape
+        logits = ops.linear(self.hidden_states(token_ids), self.head_weight)
+        if self.tp is not None and self.tp.size > 1:
+            logits = self.tp.all_gather_cat(logits, 0, differentiable=True)
+        return logits.reshape(B, T, self.vocab_size)
+
+    def loss(self, token_ids: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0) -> torch.Tensor:
+        """Mean next-token cross-entropy without materialising the logits.
+
+        Under tensor parallelism each rank scores its own tokens; the returned value is that rank's
+        share ``sum_local / N_global`` (sum over ranks = global mean), which is also the quantity whose
+        gradient the sharded backward needs.
+        """
+        hidden = self.hidden_states(token_ids)
+        local_targets = self._local_tokens(targets.reshape(-1))
+        share = 1.0
+        if self.tp is not None and self.tp.size > 1:
+            share = 1.0 / self.tp.size
+        loss = ops.linear_cross_entropy(hidden, self.head_weight, local_targets, loss_scale) * share
+        aux = self.aux_loss()
+        if aux is not None:
+            loss = loss + aux * (share * loss_scale if loss_scale != 1.0 else share)
+        return loss

@@ -1,0 +1,21 @@
+"""Ops layer: oracle math (CPU) and sm_100a kernels (CUDA) behind one functional API."""
+
+from ajllm_b200.ops import native, reference
+from ajllm_b200.ops.functional import (
+    add_rms_norm,
+    cross_entropy,
+    embedding,
+    gemm,
+    linear,
+    linear_cross_entropy,
+    rms_norm,
+    rope_attention,
+    silu,
+    split_packed_qkv,
+    swiglu_interleaved,
+)
+
+__all__ = [
+    "native", "reference", "add_rms_norm", "cross_entropy", "embedding", "gemm", "linear",
+    "linear_cross_entropy", "rms_norm", "rope_attention", "silu", "split_packed_qkv", "swiglu_interleaved",
+]

@@ -1,0 +1,385 @@
+"""Differentiable ops. CPU tensors run the oracle math in :mod:`ajllm_b200.ops.reference` under
+autograd; CUDA tensors run the sm_100a kernels through hand-written backward passes.
+
+GPU data layout: activations are bf16 ``[tokens, features]`` row-major; the three attention
+projections are one GEMM whose output row is ``[q heads | k heads | v heads]`` and the attention
+kernels read that packed row in place; the two SwiGLU input projections are one GEMM whose output
+interleaves gate (even) and up (odd) columns so the activation pairs sit side by side.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ajllm_b200.ops import native, reference
+
+EPI_STORE_BF16 = 0
+EPI_ACCUM_F32 = 1
+EPI_STORE_F32 = 2
+
+
+def _is_cuda(t: torch.Tensor) -> bool:
+    return t.device.type == "cuda"
+
+
+# ----------------------------------------------------------------------------- GEMM
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, m: int, n: int, k: int, *,
+         a_mn_major: bool = False, b_mn_major: bool = False, epilogue: int = EPI_STORE_BF16) -> torch.Tensor:
+    """``out[m,n] (+)= op(a)[m,k] @ op(b)[k,n]`` on the tcgen05 kernel.
+
+    ``a`` is stored ``[m,k]`` (k contiguous) or, with ``a_mn_major``, ``[k,m]`` (m contiguous); ``b`` is
+    stored ``[n,k]`` (k contiguous) or, with ``b_mn_major``, ``[k,n]`` (n contiguous). Leading dimensions
+    come from ``stride(0)`` so column slices of wider buffers can be passed without a copy.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+    native.call("ajb_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k,
+                a.stride(0), b.stride(0), out.stride(0), int(a_mn_major), int(b_mn_major), epilogue,
+                native.stream_ptr())
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        n, k = weight.shape
+        out = torch.empty(x2.shape[0], n, dtype=torch.bfloat16, device=x.device)
+        gemm(x2, weight, out, x2.shape[0], n, k)
+        ctx.save_for_backward(x2, weight)
+        ctx.lead = lead
+        return out.view(*lead, n)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x2, weight = ctx.saved_tensors
+        n, k = weight.shape
+        g2 = grad_out.reshape(-1, n)
+        if g2.stride(-1) != 1 or g2.dtype != torch.bfloat16:
+            g2 = g2.to(torch.bfloat16).contiguous()
+        m = g2.shape[0]
+        grad_x = grad_w = None
+        if ctx.needs_input_grad[0]:
+            grad_x = torch.empty(m, k, dtype=torch.bfloat16, device=g2.device)
+            gemm(g2, weight, grad_x, m, k, n, b_mn_major=True)
+            grad_x = grad_x.view(*ctx.lead, k)
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                # fp32 accumulation straight into the optimizer's gradient buffer
+                gemm(g2, x2, main, n, k, m, a_mn_major=True, b_mn_major=True, epilogue=EPI_ACCUM_F32)
+                weight.main_grad_written = True
+            else:
+                grad_w = torch.empty(n, k, dtype=torch.bfloat16, device=g2.device)
+                gemm(g2, x2, grad_w, n, k, m, a_mn_major=True, b_mn_major=True)
+        return grad_x, grad_w
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x @ weight.T`` for a bias-free ``[out, in]`` weight (``ajllm/modeling/layers.py:33``)."""
+    if _is_cuda(x) and x.dtype == torch.bfloat16:
+        return _LinearFn.apply(x, weight)
+    return reference.linear(x, weight)
+
+
+# ----------------------------------------------------------------------------- RMSNorm (+ residual)
+
+_NORM_BWD_ROWS_PER_BLOCK = 64
+
+
+def _norm_bwd_partials(rows: int) -> int:
+    return max(1, min(1024, (rows + _NORM_BWD_ROWS_PER_BLOCK - 1) // _NORM_BWD_ROWS_PER_BLOCK))
+
+
+class _AddRmsNormFn(torch.autograd.Function):
+    """``h = x + delta`` (``delta`` may be ``None``), ``y = rmsnorm(h) * gain``; returns ``(h, y)``."""
+
+    @staticmethod
+    def forward(ctx, x, delta, gain, eps):
+        dim = x.shape[-1]
+        x2 = x.reshape(-1, dim)
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        if delta is not None:
+            h = torch.empty_like(x2)
+            d2 = delta.reshape(-1, dim)
+        else:
+            h, d2 = x2, None
+        native.call("ajb_rmsnorm_fwd", x2.data_ptr(), native.ptr(d2), gain.data_ptr(), y.data_ptr(),
+                    h.data_ptr() if delta is not None else None, rstd.data_ptr(), rows, dim, float(eps),
+                    native.stream_ptr())
+        ctx.save_for_backward(h, gain, rstd)
+        ctx.has_delta = delta is not None
+        ctx.shape = x.shape
+        return h.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, grad_h, grad_y):
+        h, gain, rstd = ctx.saved_tensors
+        rows, dim = h.shape
+        gy = grad_y.reshape(rows, dim).contiguous()
+        gh = None if grad_h is None else grad_h.reshape(rows, dim).contiguous()
+        dx = torch.empty_like(h)
+        nparts = _norm_bwd_partials(rows)
+        partial = torch.empty(nparts, dim, dtype=torch.float32, device=h.device)
+        native.call("ajb_rmsnorm_bwd", gy.data_ptr(), h.data_ptr(), gain.data_ptr(), rstd.data_ptr(),
+                    native.ptr(gh), dx.data_ptr(), partial.data_ptr(), rows, dim, nparts, native.stream_ptr())
+        main = getattr(gain, "main_grad", None)
+        grad_gain = None
+        if main is not None:
+            native.call("ajb_colsum_f32", partial.data_ptr(), main.data_ptr(), nparts, dim, 1, native.stream_ptr())
+            gain.main_grad_written = True
+        else:
+            gsum = torch.zeros(dim, dtype=torch.float32, device=h.device)
+            native.call("ajb_colsum_f32", partial.data_ptr(), gsum.data_ptr(), nparts, dim, 0, native.stream_ptr())
+            grad_gain = gsum.to(gain.dtype)
+        dx = dx.view(ctx.shape)
+        return dx, (dx if ctx.has_delta else None), grad_gain, None
+
+
+def add_rms_norm(x: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, eps: float = 1e-5):
+    """Residual add fused with RMSNorm: returns ``(x + delta, rmsnorm(x + delta) * gain)``."""
+    if _is_cuda(x) and x.dtype == torch.bfloat16:
+        return _AddRmsNormFn.apply(x, delta, gain, eps)
+    h = x if delta is None else x + delta
+    return h, reference.rms_norm(h, gain, eps)
+
+
+def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    return add_rms_norm(x, None, gain, eps)[1]
+
+
+# ----------------------------------------------------------------------------- RoPE + attention
+
+
+class _RopeAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, num_heads, num_kv_heads, head_dim, causal, use_rope):
+        B, T, width = qkv.shape
+        assert width == (num_heads + 2 * num_kv_heads) * head_dim
+        qkv = qkv.contiguous()
+        rows = B * T
+        stream = native.stream_ptr()
+        if use_rope:
+            # rotates the q and k heads of the packed rows in place (positions = row % T)
+            native.call("ajb_rope_qk", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), None, rows, T,
+                        num_heads, num_kv_heads, head_dim, width, 0, stream)
+        out = torch.empty(B, T, num_heads * head_dim, dtype=torch.bfloat16, device=qkv.device)
+        lse = torch.empty(B, num_heads, T, dtype=torch.float32, device=qkv.device)
+        scale = 1.0 / math.sqrt(head_dim)
+        native.call("ajb_flash_fwd", qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, num_heads,
+                    num_kv_heads, head_dim, width, int(causal), scale, stream)
+        ctx.save_for_backward(qkv, out, lse, cos, sin)
+        ctx.meta = (num_heads, num_kv_heads, head_dim, causal, use_rope, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        qkv, out, lse, cos, sin = ctx.saved_tensors
+        num_heads, num_kv_heads, head_dim, causal, use_rope, scale = ctx.meta
+        B, T, width = qkv.shape
+        stream = native.stream_ptr()
+        grad_out = grad_out.contiguous()
+        dqkv = torch.empty_like(qkv)
+        delta = torch.empty(B, num_heads, T, dtype=torch.float32, device=qkv.device)
+        native.call("ajb_flash_bwd", qkv.data_ptr(), out.data_ptr(), grad_out.data_ptr(), lse.data_ptr(),
+                    delta.data_ptr(), dqkv.data_ptr(), B, T, num_heads, num_kv_heads, head_dim, width,
+                    int(causal), scale, stream)
+        if use_rope:
+            native.call("ajb_rope_qk", dqkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), None, B * T, T,
+                        num_heads, num_kv_heads, head_dim, width, 1, stream)
+        return dqkv, None, None, None, None, None, None, None
+
+
+def rope_attention(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None, num_heads: int,
+                   num_kv_heads: int, head_dim: int, causal: bool = True) -> torch.Tensor:
+    """Causal self-attention over a packed ``[B, T, (Hq + 2 Hkv) * hd]`` projection.
+
+    RoPE (interleaved pairs, ``ajllm/modeling/attention.py:50-60``) is applied to the q and k heads when
+    tables are given; the result is ``[B, T, Hq * hd]``.
+    """
+    B, T, _ = qkv.shape
+    if _is_cuda(qkv) and qkv.dtype == torch.bfloat16:
+        use_rope = cos is not None
+        dummy = qkv.new_empty(1, dtype=torch.float32)
+        return _RopeAttentionFn.apply(qkv, cos if use_rope else dummy, sin if use_rope else dummy,
+                                      num_heads, num_kv_heads, head_dim, causal, use_rope)
+    q, k, v = split_packed_qkv(qkv, num_heads, num_kv_heads, head_dim)
+    if cos is not None:
+        pos = torch.arange(T, device=qkv.device)
+        q = reference.rope_interleaved(q, cos, sin, pos)
+        k = reference.rope_interleaved(k, cos, sin, pos)
+    return reference.attention(q, k, v, causal=causal).reshape(B, T, num_heads * head_dim)
+
+
+def split_packed_qkv(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int):
+    lead = qkv.shape[:-1]
+    nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+    q = qkv[..., :nq].reshape(*lead, num_heads, head_dim)
+    k = qkv[..., nq:nq + nk].reshape(*lead, num_kv_heads, head_dim)
+    v = qkv[..., nq + nk:].reshape(*lead, num_kv_heads, head_dim)
+    return q, k, v
+
+
+# ----------------------------------------------------------------------------- SwiGLU
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        width = gate_up.shape[-1]
+        g2 = gate_up.reshape(-1, width).contiguous()
+        act = torch.empty(g2.shape[0], width // 2, dtype=g2.dtype, device=g2.device)
+        native.call("ajb_swiglu_fwd", g2.data_ptr(), act.data_ptr(), g2.shape[0], width // 2, native.stream_ptr())
+        ctx.save_for_backward(g2)
+        ctx.shape = gate_up.shape
+        return act.view(*gate_up.shape[:-1], width // 2)
+
+    @staticmethod
+    def backward(ctx, grad_act):
+        (g2,) = ctx.saved_tensors
+        rows, width = g2.shape
+        ga = grad_act.reshape(rows, width // 2).contiguous()
+        dgu = torch.empty_like(g2)
+        native.call("ajb_swiglu_bwd", g2.data_ptr(), ga.data_ptr(), dgu.data_ptr(), rows, width // 2,
+                    native.stream_ptr())
+        return dgu.view(ctx.shape)
+
+
+def swiglu_interleaved(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` where even columns are gate and odd columns are up."""
+    if _is_cuda(gate_up) and gate_up.dtype == torch.bfloat16:
+        return _SwigluFn.apply(gate_up)
+    return reference.swiglu_interleaved(gate_up)
+
+
+def silu(x: torch.Tensor) -> torch.Tensor:
+    return reference.silu(x)
+
+
+# ----------------------------------------------------------------------------- embedding
+
+
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        flat = ids.reshape(-1).to(torch.int64).contiguous()
+        vocab, dim = table.shape
+        out = torch.empty(flat.numel(), dim, dtype=table.dtype, device=table.device)
+        native.call("ajb_embedding_fwd", flat.data_ptr(), table.data_ptr(), out.data_ptr(), flat.numel(), dim,
+                    vocab, native.stream_ptr())
+        ctx.save_for_backward(flat, table)
+        return out.view(*ids.shape, dim)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        flat, table = ctx.saved_tensors
+        vocab, dim = table.shape
+        g = grad_out.reshape(-1, dim).contiguous()
+        main = getattr(table, "main_grad", None)
+        if main is not None:
+            native.call("ajb_embedding_bwd", flat.data_ptr(), g.data_ptr(), main.data_ptr(), flat.numel(), dim,
+                        vocab, native.stream_ptr())
+            table.main_grad_written = True
+            return None, None
+        acc = torch.zeros(vocab, dim, dtype=torch.float32, device=g.device)
+        native.call("ajb_embedding_bwd", flat.data_ptr(), g.data_ptr(), acc.data_ptr(), flat.numel(), dim, vocab,
+                    native.stream_ptr())
+        return None, acc.to(table.dtype)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """Row gather ``table[ids]`` (``ajllm/modeling/layers.py:53``)."""
+    if _is_cuda(table) and table.dtype == torch.bfloat16:
+        return _EmbeddingFn.apply(ids, table)
+    return table[ids]
+
+
+# ----------------------------------------------------------------------------- LM head + cross-entropy
+
+_CE_ROWS_PER_CHUNK = 8192
+
+
+class _LinearCrossEntropyFn(torch.autograd.Function):
+    """Mean cross-entropy of ``hidden @ weight.T`` without keeping the ``[tokens, vocab]`` logits.
+
+    Row chunks go through GEMM -> in-place softmax-minus-onehot -> the two gradient GEMMs while still in
+    the forward pass, so the only saved tensors are ``d hidden`` and (optionally) ``d weight``.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, loss_scale):
+        dim = hidden.shape[-1]
+        h2 = hidden.reshape(-1, dim).contiguous()
+        tgt = targets.reshape(-1).to(torch.int64).contiguous()
+        rows, vocab = h2.shape[0], weight.shape[0]
+        stream = native.stream_ptr()
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=h2.device)
+        grad_h = torch.empty_like(h2)
+        main = getattr(weight, "main_grad", None)
+        grad_w = main if main is not None else torch.zeros(vocab, dim, dtype=torch.float32, device=h2.device)
+        inv = float(loss_scale) / rows
+        chunk = min(rows, _CE_ROWS_PER_CHUNK)
+        logits = torch.empty(chunk, vocab, dtype=torch.bfloat16, device=h2.device)
+        for start in range(0, rows, chunk):
+            r = min(chunk, rows - start)
+            hs = h2[start:start + r]
+            gemm(hs, weight, logits, r, vocab, dim)
+            native.call("ajb_ce_fwd_bwd", logits.data_ptr(), tgt[start:start + r].data_ptr(), loss_sum.data_ptr(),
+                        r, vocab, vocab, inv, 1, stream)
+            gemm(logits, weight, grad_h[start:start + r], r, dim, vocab, b_mn_major=True)
+            gemm(logits, hs, grad_w, vocab, dim, r, a_mn_major=True, b_mn_major=True, epilogue=EPI_ACCUM_F32)
+        ctx.save_for_backward(grad_h, None if main is not None else grad_w)
+        ctx.uses_main = main is not None
+        if main is not None:
+            weight.main_grad_written = True
+        ctx.hshape = hidden.shape
+        ctx.wdtype = weight.dtype
+        return (loss_sum / rows).reshape(())
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        grad_h, grad_w = ctx.saved_tensors
+        # the chunk gradients were scaled by loss_scale/rows already; grad_loss multiplies on top
+        gh = grad_h.view(ctx.hshape) * grad_loss.to(grad_h.dtype)
+        gw = None if ctx.uses_main else (grad_w * grad_loss).to(ctx.wdtype)
+        return gh, gw, None, None
+
+
+def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
+                         loss_scale: float = 1.0) -> torch.Tensor:
+    """Mean CE of the LM head (``ajllm/modeling/transformer.py:123-126`` followed by
+    ``ajllm/training/losses.py:8-18``). ``loss_scale`` pre-multiplies the gradients only (used for
+    gradient accumulation); the returned loss is unscaled.
+
+    On the GPU the gradients are produced during the forward call, so the caller must backpropagate the
+    returned loss with a unit (or scalar) upstream gradient.
+    """
+    if _is_cuda(hidden) and hidden.dtype == torch.bfloat16:
+        return _LinearCrossEntropyFn.apply(hidden, weight, targets, loss_scale)
+    logits = reference.linear(hidden, weight)
+    loss = reference.cross_entropy(logits, targets)
+    if loss_scale != 1.0:
+        # same value, scaled gradient
+        loss = loss.detach() + (loss - loss.detach()) * loss_scale
+    return loss
+
+
+def cross_entropy(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Mean CE over materialised logits (evaluation path)."""
+    if _is_cuda(logits) and logits.dtype == torch.bfloat16 and not logits.requires_grad:
+        flat = logits.reshape(-1, logits.shape[-1]).contiguous()
+        tgt = targets.reshape(-1).to(torch.int64).contiguous()
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=flat.device)
+        native.call("ajb_ce_fwd_bwd", flat.data_ptr(), tgt.data_ptr(), loss_sum.data_ptr(), flat.shape[0],
+                    flat.shape[1], flat.stride(0), 0.0, 0, native.stream_ptr())
+        return (loss_sum / flat.shape[0]).reshape(())
+    return reference.cross_entropy(logits, targets)

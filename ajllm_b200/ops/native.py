@@ -1,0 +1,114 @@
+"""ctypes binding to the in-tree sm_100a kernel library.
+
+The library is built by ``ajllm_b200.build`` into ``ajllm_b200/_native/libajllm_b200.so`` with
+``nvcc -gencode arch=compute_100a,code=sm_100a``. Kernels take raw device pointers and a CUDA stream,
+so nothing here depends on torch's C++ headers. A CUDA tensor handed to an op when the library is
+absent raises: there is no silent eager fallback on a GPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB_DIR = Path(__file__).resolve().parent.parent / "_native"
+_LIB_NAME = "libajllm_b200.so"
+_lib: ctypes.CDLL | None = None
+_load_error: str | None = None
+
+c_void = ctypes.c_void_p
+c_int = ctypes.c_int
+c_long = ctypes.c_longlong
+c_float = ctypes.c_float
+
+# name -> argument ctypes; every entry point returns int (0 = ok)
+_SIGNATURES: dict[str, list] = {
+    "ajb_gemm_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long,
+                      c_int, c_int, c_int, c_void],
+    "ajb_rmsnorm_fwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float, c_void],
+    "ajb_rmsnorm_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_void],
+    "ajb_colsum_f32": [c_void, c_void, c_int, c_int, c_int, c_void],
+    "ajb_rope_qk": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_void],
+    "ajb_swiglu_fwd": [c_void, c_void, c_long, c_int, c_void],
+    "ajb_swiglu_bwd": [c_void, c_void, c_void, c_long, c_int, c_void],
+    "ajb_ce_fwd_bwd": [c_void, c_void, c_void, c_int, c_int, c_long, c_float, c_int, c_void],
+    "ajb_embedding_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],
+    "ajb_embedding_bwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],
+    "ajb_sumsq_f32": [c_void, c_long, c_void, c_void],
+    "ajb_adamw_flat": [c_void, c_void, c_void, c_void, c_void, c_long, c_float, c_float, c_float, c_float,
+                       c_float, c_float, c_float, c_void, c_float, c_void],
+    "ajb_add_bf16": [c_void, c_void, c_void, c_long, c_void],
+    "ajb_flash_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_float, c_void],
+    "ajb_flash_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
+                      c_long, c_int, c_float, c_void],
+}
+
+
+def library_path() -> Path:
+    return _LIB_DIR / _LIB_NAME
+
+
+def _try_load() -> None:
+    global _lib, _load_error
+    if _lib is not None or _load_error is not None:
+        return
+    path = library_path()
+    if not path.is_file():
+        _load_error = f"{path} has not been built (run `python -m ajllm_b200.build`)"
+        return
+    try:
+        lib = ctypes.CDLL(str(path), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else ctypes.DEFAULT_MODE)
+    except OSError as error:
+        _load_error = f"could not load {path}: {error}"
+        return
+    for name, argtypes in _SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            continue
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    lib.ajb_last_error.restype = ctypes.c_char_p
+    lib.ajb_last_error.argtypes = []
+    _lib = lib
+
+
+def available() -> bool:
+    _try_load()
+    return _lib is not None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises with the reason when it cannot be used."""
+    _try_load()
+    if _lib is None:
+        raise RuntimeError(f"ajllm_b200 native kernels are required for CUDA tensors: {_load_error}")
+    return _lib
+
+
+def bind(name: str, argtypes: list, restype=c_int):
+    """Declare an entry point that is not in the static table (used by optional subsystems)."""
+    fn = getattr(lib(), name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def call(name: str, *args) -> None:
+    fn = getattr(lib(), name)
+    status = fn(*args)
+    if status != 0:
+        message = lib().ajb_last_error()
+        detail = message.decode("utf-8", "replace") if message else ""
+        raise RuntimeError(f"{name} failed with status {status}: {detail}")
