@@ -1,0 +1,288 @@
+// Shared sm_100a primitives: error reporting, bounded mbarrier waits, TMA loads, tcgen05 MMA /
+// TMEM management, shared-memory matrix descriptors.
+//
+// Every device-side wait in this library is bounded: a wait that exceeds its time budget records a
+// status word in global memory, raises a CTA-wide abort flag and returns false, and the kernel then
+// leaves through its normal teardown path (TMEM is released, nothing traps).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ajb {
+
+// ---------------------------------------------------------------------------------------------
+// Host-side error plumbing
+// ---------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+const char* last_error();
+
+#define AJB_CUDA_OK(expr)                                                                   \
+  do {                                                                                      \
+    cudaError_t err__ = (expr);                                                             \
+    if (err__ != cudaSuccess) {                                                             \
+      ajb::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__,   \
+                     __LINE__);                                                             \
+      return 1;                                                                             \
+    }                                                                                       \
+  } while (0)
+
+#define AJB_REQUIRE(cond, ...)              \
+  do {                                      \
+    if (!(cond)) {                          \
+      ajb::set_error(__VA_ARGS__);          \
+      return 2;                             \
+    }                                       \
+  } while (0)
+
+// Device status words written by kernels whose bounded waits expired. Index = kernel id.
+enum KernelId : int { kGemm = 0, kFlashFwd = 1, kFlashBwdKV = 2, kFlashBwdQ = 3, kCommGemm = 4, kNumKernelIds = 16 };
+struct DeviceStatus {
+  unsigned int code;    // 0 = ok, otherwise (stage << 8) | kernel id + 1
+  unsigned int block;
+  unsigned int detail0;
+  unsigned int detail1;
+};
+DeviceStatus* device_status_buffer();   // kNumKernelIds entries, zero-initialised, per device
+int check_device_status(int kernel_id); // host: reads (synchronising on the stream's device) and clears
+
+// Encodes a 2-D bf16/fp8/fp32 row-major tensor [rows, cols] (row pitch in bytes) for TMA with a
+// 128-byte swizzle. box_cols * elem_bytes must be <= 128.
+int make_tensor_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                       uint64_t rows, uint64_t cols, uint64_t row_pitch_bytes, uint32_t box_rows,
+                       uint32_t box_cols);
+int make_tensor_map_3d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                       uint64_t d2, uint64_t rows, uint64_t cols, uint64_t d2_pitch_bytes,
+                       uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols);
+
+int sm_count();
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------
+// Device primitives
+// ---------------------------------------------------------------------------------------------
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. `abort_flag` is a CTA-shared word; once any role sets it, every wait returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          DeviceStatus* status, int kernel_id, int stage) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((++spins & 0x3ff) == 0 && global_timer_ns() - t0 > kWaitBudgetNs) {
+      *abort_flag = 1;
+      if (status != nullptr && atomicCAS(&status[kernel_id].code, 0u, (unsigned)((stage << 8) | (kernel_id + 1))) == 0u) {
+        status[kernel_id].block = blockIdx.x;
+        status[kernel_id].detail0 = parity;
+        status[kernel_id].detail1 = threadIdx.x;
+      }
+      return false;
+    }
+  }
+}
+
+// Swizzled operand tiles need a 1024-byte aligned base. The dynamic shared array is declared with that
+// alignment; should the runtime ever place it elsewhere, the CTA reports it and leaves before touching
+// any barrier or tensor memory. A CTA also leaves at once when an earlier CTA of the same kernel has
+// already recorded an expired wait, so a protocol bug costs one time budget, not one per wave.
+__device__ __forceinline__ bool smem_misaligned(const void* base, DeviceStatus* status, int kernel_id) {
+  __shared__ uint32_t skip_cta;
+  if (threadIdx.x == 0) {
+    const bool bad = (smem_u32(base) & 1023u) != 0;
+    if (bad && status != nullptr &&
+        atomicCAS(&status[kernel_id].code, 0u, (unsigned)((0xff << 8) | (kernel_id + 1))) == 0u) {
+      status[kernel_id].block = blockIdx.x;
+      status[kernel_id].detail0 = smem_u32(base);
+    }
+    const bool failed_before = status != nullptr && *reinterpret_cast<volatile unsigned int*>(&status[kernel_id].code) != 0u;
+    skip_cta = (bad || failed_before) ? 1u : 0u;
+  }
+  __syncthreads();
+  return skip_cta != 0u;
+}
+
+// TMA tile loads (no multicast anywhere in this library).
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tensor_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- TMEM
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+               "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], bf16/fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same for e4m3/e5m2 inputs.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane (base lane + i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// ---- descriptors (128-byte swizzle everywhere)
+// Instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation.
+//   ab_format: f16 kinds 0 = fp16, 1 = bf16; f8 kinds 0 = e4m3, 1 = e5m2.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int ab_format, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (uint32_t(ab_format) << 7) | (uint32_t(ab_format) << 10) | (uint32_t(a_mn_major) << 15) |
+         (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// Shared-memory matrix descriptor. Byte offsets are encoded in 16-byte units.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3ffff) >> 4);
+  d |= uint64_t((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= uint64_t((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= uint64_t(1) << 46;  // descriptor version for sm_100
+  d |= uint64_t(2) << 61;  // SWIZZLE_128B
+  return d;
+}
+// K-major operand tile: rows of 128 bytes (64 bf16 along K), 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t tile_addr, uint32_t k_byte_offset) {
+  return make_smem_desc(tile_addr + k_byte_offset, 16, 1024);
+}
+// MN-major operand tile made of [k rows][64 elements along MN] boxes of `box_bytes` each
+// (box_bytes = k rows * 128). `k_index` is the first k row of this MMA (multiple of 8).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t tile_addr, uint32_t box_bytes, uint32_t k_index) {
+  return make_smem_desc(tile_addr + k_index * 128, box_bytes, 1024);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+#endif  // __CUDACC__
+
+}  // namespace ajb

@@ -1,0 +1,321 @@
+// FlashAttention forward for sm_100a: S = Q K^T and O += P V run on tcgen05 with S (double
+// buffered) and O resident in tensor memory; K/V tiles arrive by TMA; four softmax warps own one
+// query row per thread (online max / sum in registers), write P as a swizzled bf16 operand tile in
+// shared memory and rescale O in tensor memory only when a row maximum moved.
+//
+// Inputs are the packed projection rows [B, T, (Hq + 2 Hkv) * hd] (q heads | k heads | v heads) after
+// RoPE; query head h reads KV head h / (Hq / Hkv). Outputs: O [B, T, Hq * hd] (bf16) and the row
+// log-sum-exp of the scaled scores, LSE [B, Hq, T] (fp32), which the backward kernels consume.
+#include "common.cuh"
+
+namespace ajb {
+namespace flash {
+
+constexpr int BLOCK_M = 128;  // queries per CTA
+constexpr int BLOCK_N = 128;  // keys per step
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int HD>
+struct FwdCfg {
+  static constexpr int kTileBytes = BLOCK_N * HD * 2;       // one Q, K or V tile
+  static constexpr int kPBytes = BLOCK_M * BLOCK_N * 2;
+  static constexpr int kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*2 x (K,V)*/ + kPBytes + 256;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kOCol = 256;  // S0 at 0, S1 at 128, O at 256
+};
+
+struct FwdParams {
+  __nv_bfloat16* out;
+  float* lse;
+  int batch, seq, heads, kv_heads;
+  int causal;
+  float scale;
+  DeviceStatus* status;
+};
+
+// Loads one [128 rows x HD] tile as HD/64 boxes of [128 x 64].
+template <int HD>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int col, int row, int b) {
+#pragma unroll
+  for (int i = 0; i < HD / 64; ++i) tma_load_3d(dst + i * (BLOCK_N * 128), map, bar, col + 64 * i, row, b);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p) {
+  using Cfg = FwdCfg<HD>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_misaligned(smem, p.status, kFlashFwd)) return;
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + Cfg::kTileBytes;               // stage s: K at sKV + s*2*tile, V right after
+  uint8_t* sP = sKV + 4 * Cfg::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* kv_full = bars + 1;       // 2
+  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* s_full = bars + 5;        // 2
+  uint64_t* s_free = bars + 7;        // 2
+  uint64_t* p_ready = bars + 9;       // 1
+  uint64_t* pv_done = bars + 10;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) tiles first
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kv_head = head / (p.heads / p.kv_heads);
+  const int q0 = q_tile * BLOCK_M;
+  const int q_col = head * HD;
+  const int k_col = (p.heads + kv_head) * HD;
+  const int v_col = (p.heads + p.kv_heads + kv_head) * HD;
+  const int kv_limit = p.causal ? min(p.seq, q0 + BLOCK_M) : p.seq;
+  const int n_tiles = (kv_limit + BLOCK_N - 1) / BLOCK_N;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
+    }
+    mbar_init(p_ready, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensor_map(&map_qkv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
+      load_tile<HD>(sQ, &map_qkv, q_full, q_col, q0, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], (((uint32_t)j >> 1) & 1) ^ 1, abort_flag, p.status, kFlashFwd, 1)) break;
+        uint8_t* sK = sKV + s * 2 * Cfg::kTileBytes;
+        mbar_arrive_expect_tx(&kv_full[s], 2 * Cfg::kTileBytes);
+        load_tile<HD>(sK, &map_qkv, &kv_full[s], k_col, j * BLOCK_N, b);
+        load_tile<HD>(sK + Cfg::kTileBytes, &map_qkv, &kv_full[s], v_col, j * BLOCK_N, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc_s = make_idesc(BLOCK_M, BLOCK_N, 1, false, false);  // Q K^T
+    constexpr uint32_t idesc_o = make_idesc(BLOCK_M, HD, 1, false, true);        // P V (V is N-contiguous)
+    const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+    bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kFlashFwd, 2);
+    auto issue_s = [&](int j) -> bool {
+      const int s = j & 1;
+      const uint32_t use = (uint32_t)j >> 1;
+      if (!mbar_wait(&kv_full[s], use & 1, abort_flag, p.status, kFlashFwd, 3)) return false;
+      if (!mbar_wait(&s_free[s], (use & 1) ^ 1, abort_flag, p.status, kFlashFwd, 4)) return false;
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t aK = smem_u32(sKV + s * 2 * Cfg::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t box = (uint32_t)(k / 4) * (BLOCK_N * 128), off = (uint32_t)(k % 4) * 32;
+          umma_f16(tmem_base + (uint32_t)(s * BLOCK_N), desc_k_major(aQ + box, off), desc_k_major(aK + box, off),
+                   idesc_s, k != 0);
+        }
+        tc_commit(&s_full[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok && n_tiles > 0) ok = issue_s(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) {
+        ok = issue_s(j + 1);
+        if (!ok) break;
+      }
+      if (!mbar_wait(p_ready, (uint32_t)j & 1, abort_flag, p.status, kFlashFwd, 5)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t aV = smem_u32(sKV + (j & 1) * 2 * Cfg::kTileBytes + Cfg::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < BLOCK_N / 16; ++k) {
+          const uint32_t pbox = (uint32_t)(k / 4) * (BLOCK_M * 128), poff = (uint32_t)(k % 4) * 32;
+          umma_f16(tmem_base + Cfg::kOCol, desc_k_major(aP + pbox, poff), desc_mn_major(aV, BLOCK_N * 128, k * 16),
+                   idesc_o, (j | k) != 0);
+        }
+        tc_commit(pv_done);
+        tc_commit(&kv_empty[j & 1]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / correction / epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;          // row of the tile == TMEM lane
+    const int q_pos = q0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float sl = p.scale * kLog2e;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kFlashFwd, 6)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int k0 = j * BLOCK_N;
+      const bool need_mask = (p.causal && k0 + BLOCK_N > q0) || (k0 + BLOCK_N > p.seq);
+      const int k_max = p.causal ? min(q_pos, p.seq - 1) : p.seq - 1;  // last visible key of this row
+      // pass 1: row maximum
+      uint32_t sv[4][32];
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * BLOCK_N + c * 32), sv[c]);
+      }
+      tc_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[s]);   // S(j) is in registers; its TMEM buffer may be overwritten
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(sv[c][i]);
+          if (need_mask && (k0 + c * 32 + i > k_max)) x = -INFINITY;
+          sv[c][i] = __float_as_uint(x);
+          m_tile = fmaxf(m_tile, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;   // fully masked row (only when q_pos >= seq)
+      const float alpha = exp2f((m_run - m_safe) * sl);            // m_run = -inf -> 0
+      const float neg = -m_safe * sl;
+      float l_tile = 0.0f;
+      // pass 2: probabilities, packed to bf16 (the rounded values feed both the sum and the PV product)
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[c][i]), sl, neg));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), sl, neg));
+          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          const float2 back = __bfloat1622float2(h);
+          l_tile += back.x + back.y;
+          pk[c * 16 + i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+      }
+      l_run = l_run * alpha + l_tile;
+      const bool moved = m_new != m_run;
+      m_run = m_new;
+      // P and O belong to the previous PV product until it has completed
+      if (j > 0 && !mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kFlashFwd, 7)) { ok = false; break; }
+      tc_fence_after_sync();
+      // P -> shared memory, K-major 128-byte-swizzled operand tile: 2 boxes of [128 rows x 64 keys]
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const int box = ch >> 3, chunk = ch & 7;
+        uint4 val = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+        uint8_t* dst = sP + box * (BLOCK_M * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = val;
+      }
+      // rescale O when some row of this warp moved its maximum
+      if (j > 0 && __any_sync(0xffffffffu, moved)) {
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(Cfg::kOCol + c * 32), ov);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(Cfg::kOCol + c * 32), ov);
+        }
+        tc_wait_st();
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    // epilogue: O / l -> global, LSE
+    if (ok && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kFlashFwd, 8)) {
+      tc_fence_after_sync();
+      const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      const bool row_ok = q_pos < p.seq;
+      __nv_bfloat16* dst = p.out + ((size_t)b * p.seq + q_pos) * ((size_t)p.heads * HD) + (size_t)head * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t ov[32];
+        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(Cfg::kOCol + c * 32), ov);
+        tc_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(ov[8 * i]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
+            q.y = pack_bf16x2(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
+            q.z = pack_bf16x2(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
+            q.w = pack_bf16x2(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
+            reinterpret_cast<uint4*>(dst + c * 32)[i] = q;
+          }
+        }
+      }
+      if (row_ok) {
+        p.lse[((size_t)b * p.heads + head) * p.seq + q_pos] =
+            (l_run > 0.0f) ? m_run * p.scale + __logf(l_run) : -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int HD>
+static int launch_fwd(const void* qkv, void* out, void* lse, int batch, int seq, int heads, int kv_heads,
+                      long long row_stride, int causal, float scale, cudaStream_t stream) {
+  using Cfg = FwdCfg<HD>;
+  CUtensorMap map;
+  int rc = make_tensor_map_3d(&map, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, batch, seq, row_stride,
+                              (uint64_t)seq * row_stride * 2, row_stride * 2, BLOCK_N, 64);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    AJB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  FwdParams p;
+  p.out = (__nv_bfloat16*)out; p.lse = (float*)lse; p.batch = batch; p.seq = seq; p.heads = heads;
+  p.kv_heads = kv_heads; p.causal = causal; p.scale = scale; p.status = device_status_buffer();
+  dim3 grid((seq + BLOCK_M - 1) / BLOCK_M, heads, batch);
+  flash_fwd_kernel<HD><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map, p);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace flash
+}  // namespace ajb
+
+// qkv: packed [batch, seq, row_stride] bf16 with q heads first, then k heads, then v heads.
+extern "C" int ajb_flash_fwd(const void* qkv, void* out, void* lse, int batch, int seq, int heads, int kv_heads,
+                             int head_dim, long long row_stride, int causal, float scale, void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(heads % kv_heads == 0, "flash: kv_heads must divide heads");
+  AJB_REQUIRE(row_stride % 8 == 0, "flash: row stride must be a multiple of 8 elements");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (head_dim == 128) return flash::launch_fwd<128>(qkv, out, lse, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
+  if (head_dim == 64) return flash::launch_fwd<64>(qkv, out, lse, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
+  set_error("flash: head_dim %d is not supported by the tensor-core kernel (64 and 128 are)", head_dim);
+  return 2;
+}

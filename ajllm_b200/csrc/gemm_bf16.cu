@@ -1,0 +1,317 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory ring -> tcgen05.mma with
+// fp32 accumulators in tensor memory -> tcgen05.ld epilogue.
+//
+//   C[M,N] (+)= op(A)[M,K] * op(B)[K,N]
+//
+// A is stored [M,K] (K contiguous) or, MN-major, [K,M] (M contiguous); B is stored [N,K] (K contiguous)
+// or, MN-major, [K,N] (N contiguous). The three combinations used by a linear layer are
+//   forward  y  = x W^T      : A K-major,  B K-major
+//   dgrad    dx = dy W       : A K-major,  B MN-major
+//   wgrad    dW = dy^T x     : A MN-major, B MN-major
+// so no operand is ever transposed in memory.
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs (one elected lane),
+// warps 2..5 drain accumulators. Two 128x256 fp32 accumulators live in TMEM (512 columns) so the
+// epilogue of tile i overlaps the main loop of tile i+1. Tiles are visited in groups of 16 row-blocks
+// so that a wave of CTAs shares its A and B panels through L2.
+#include "common.cuh"
+
+namespace ajb {
+
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16;
+
+enum Epilogue : int { kStoreBf16 = 0, kAccumF32 = 1, kStoreF32 = 2 };
+
+template <int BN>
+struct Config {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kSmemBytes = kStages * kStageBytes + 256 /*barriers*/;
+};
+
+struct Params {
+  void* c;
+  int m, n, k;
+  long long ldc;
+  int epilogue;
+  int tiles_m, tiles_n;
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int group_span = kGroupM * tiles_n;
+  const int group = tile / group_span;
+  const int first_m = group * kGroupM;
+  const int rows = min(kGroupM, tiles_m - first_m);
+  const int within = tile - group * group_span;
+  tm = first_m + within % rows;
+  tn = within / rows;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  using Cfg = Config<BN>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_misaligned(smem, p.status, kGemm)) return;
+  uint8_t* stage_base = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::kStages;
+  uint64_t* acc_full = bars + 2 * Cfg::kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensor_map(&map_a);
+    prefetch_tensor_map(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kGemm, 1)) { ok = false; break; }
+          uint8_t* sa = stage_base + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          mbar_arrive_expect_tx(&full[stage], Cfg::kStageBytes);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &map_a, &full[stage], m0 + 64 * j, k0);
+          } else {
+            tma_load_2d(sa, &map_a, &full[stage], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0);
+          } else {
+            tma_load_2d(sb, &map_b, &full[stage], k0, n0);
+          }
+          ++issued;
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // drain: wait (bounded) for the copies this thread still has in flight before leaving
+        const int pending = min(issued, Cfg::kStages);
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) { s = Cfg::kStages - 1; ph ^= 1; }
+          const unsigned long long t0 = global_timer_ns();
+          while (!mbar_try_wait(&full[s], ph) && global_timer_ns() - t0 < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc(BM, BN, /*bf16*/ 1, A_MN, B_MN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+      const int buf = iter & 1;
+      const uint32_t use = (uint32_t)(iter >> 1);
+      if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, kGemm, 2)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kGemm, 3)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(stage_base + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? desc_mn_major(sa, BK * 128, k * UMMA_K) : desc_k_major(sa, k * UMMA_K * 2);
+            const uint64_t db = B_MN ? desc_mn_major(sb, BK * 128, k * UMMA_K) : desc_k_major(sb, k * UMMA_K * 2);
+            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);  // frees the smem slot once these MMAs have read it
+        }
+        __syncwarp();
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+      }
+      if (ok && lane == 0) tc_commit(&acc_full[buf]);
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    int iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+      const int buf = iter & 1;
+      const uint32_t use = (uint32_t)(iter >> 1);
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      if (!mbar_wait(&acc_full[buf], use & 1, abort_flag, p.status, kGemm, 4)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = tm * BM + quarter * 32 + lane;
+      const int col0 = tn * BN;
+      const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
+      const bool row_ok = row < p.m;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + (uint32_t)c, v);
+        tc_wait_ld();
+        const int col = col0 + c;
+        if (!row_ok || col >= p.n) continue;
+        const int valid = min(32, p.n - col);
+        if (p.epilogue == kStoreBf16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row * p.ldc + col;
+          if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 q;
+              q.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+              q.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+              q.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+              q.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+              reinterpret_cast<uint4*>(dst)[j] = q;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) dst[j] = __float2bfloat16(__uint_as_float(v[j]));
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(p.c) + (long long)row * p.ldc + col;
+          const bool accumulate = p.epilogue == kAccumF32;
+          if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 q = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+              if (accumulate) {
+                const float4 old = reinterpret_cast<float4*>(dst)[j];
+                q.x += old.x; q.y += old.y; q.z += old.z; q.w += old.w;
+              }
+              reinterpret_cast<float4*>(dst)[j] = q;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) dst[j] = (accumulate ? dst[j] : 0.0f) + __uint_as_float(v[j]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const void* a, const void* b, void* c, int m, int n, int k, long long lda, long long ldb,
+                  long long ldc, int epilogue, cudaStream_t stream) {
+  using Cfg = Config<BN>;
+  CUtensorMap map_a, map_b;
+  int rc;
+  if (A_MN) rc = make_tensor_map_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, lda * 2, BK, 64);
+  else      rc = make_tensor_map_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, lda * 2, BM, 64);
+  if (rc) return rc;
+  if (B_MN) rc = make_tensor_map_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, ldb * 2, BK, 64);
+  else      rc = make_tensor_map_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, k, ldb * 2, BN, 64);
+  if (rc) return rc;
+
+  static bool configured = false;
+  auto kernel = gemm_kernel<BN, A_MN, B_MN>;
+  if (!configured) {
+    AJB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  Params p;
+  p.c = c; p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.epilogue = epilogue;
+  p.tiles_m = (m + BM - 1) / BM;
+  p.tiles_n = (n + BN - 1) / BN;
+  p.status = device_status_buffer();
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, p);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace gemm
+}  // namespace ajb
+
+// C[m,n] (+)= op(A) op(B). lda/ldb/ldc are in elements. epilogue: 0 = bf16 store, 1 = fp32 accumulate,
+// 2 = fp32 store.
+extern "C" int ajb_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, long long lda, long long ldb,
+                             long long ldc, int a_mn_major, int b_mn_major, int epilogue, void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm: empty problem %dx%dx%d", m, n, k);
+  AJB_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm: unknown epilogue %d", epilogue);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // narrow outputs waste less of a 128-wide tile than of a 256-wide one
+  const bool narrow = (n % 256 != 0) && ((n + 127) / 128 * 128 < (n + 255) / 256 * 256);
+  const int sel = (a_mn_major ? 2 : 0) | (b_mn_major ? 1 : 0);
+  if (narrow) {
+    switch (sel) {
+      case 0: return gemm::launch<128, false, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+      case 1: return gemm::launch<128, false, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+      case 2: return gemm::launch<128, true, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+      default: return gemm::launch<128, true, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+    }
+  }
+  switch (sel) {
+    case 0: return gemm::launch<256, false, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+    case 1: return gemm::launch<256, false, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+    case 2: return gemm::launch<256, true, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+    default: return gemm::launch<256, true, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
+  }
+}

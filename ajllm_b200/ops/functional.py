@@ -354,6 +354,22 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         return gh, gw, None, None
 
 
+def _linear_cross_entropy_eval(hidden, weight, targets) -> torch.Tensor:
+    dim = hidden.shape[-1]
+    h2 = hidden.reshape(-1, dim).contiguous()
+    tgt = targets.reshape(-1).to(torch.int64).contiguous()
+    rows, vocab = h2.shape[0], weight.shape[0]
+    loss_sum = torch.zeros(1, dtype=torch.float32, device=h2.device)
+    chunk = min(rows, _CE_ROWS_PER_CHUNK)
+    logits = torch.empty(chunk, vocab, dtype=torch.bfloat16, device=h2.device)
+    for start in range(0, rows, chunk):
+        r = min(chunk, rows - start)
+        gemm(h2[start:start + r], weight, logits, r, vocab, dim)
+        native.call("ajb_ce_fwd_bwd", logits.data_ptr(), tgt[start:start + r].data_ptr(), loss_sum.data_ptr(),
+                    r, vocab, vocab, 0.0, 0, native.stream_ptr())
+    return (loss_sum / rows).reshape(())
+
+
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
                          loss_scale: float = 1.0) -> torch.Tensor:
     """Mean CE of the LM head (``ajllm/modeling/transformer.py:123-126`` followed by
@@ -364,7 +380,9 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, targets: to
     returned loss with a unit (or scalar) upstream gradient.
     """
     if _is_cuda(hidden) and hidden.dtype == torch.bfloat16:
-        return _LinearCrossEntropyFn.apply(hidden, weight, targets, loss_scale)
+        if torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad):
+            return _LinearCrossEntropyFn.apply(hidden, weight, targets, loss_scale)
+        return _linear_cross_entropy_eval(hidden, weight, targets)
     logits = reference.linear(hidden, weight)
     loss = reference.cross_entropy(logits, targets)
     if loss_scale != 1.0:

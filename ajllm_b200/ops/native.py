@@ -37,9 +37,9 @@ _SIGNATURES: dict[str, list] = {
     "ajb_ce_fwd_bwd": [c_void, c_void, c_void, c_int, c_int, c_long, c_float, c_int, c_void],
     "ajb_embedding_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],
     "ajb_embedding_bwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],
-    "ajb_sumsq_f32": [c_void, c_long, c_void, c_void],
+    "ajb_sumsq_f32": [c_void, c_long, c_void, c_void, c_void],  # in, n, scratch, out, stream
     "ajb_adamw_flat": [c_void, c_void, c_void, c_void, c_void, c_long, c_float, c_float, c_float, c_float,
-                       c_float, c_float, c_float, c_void, c_float, c_void],
+                       c_float, c_void, c_float, c_void],
     "ajb_add_bf16": [c_void, c_void, c_void, c_long, c_void],
     "ajb_flash_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_float, c_void],
     "ajb_flash_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,

@@ -1,0 +1,201 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 statement of the same op."""
+
+import math
+
+import pytest
+import torch
+
+from ajllm_b200 import ops
+from ajllm_b200.ops import native, reference
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    return float((got.float() - want.float()).norm() / want.float().norm().clamp_min(1e-12))
+
+
+def test_native_library_is_loaded():
+    assert native.available(), "the in-tree kernel library must be built before GPU tests run"
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 512), (384, 1408, 2048), (1000, 520, 264),
+                                    (4096, 4096, 2048), (130, 72, 4104)])
+def test_gemm_forward_layout(m, n, k):
+    torch.manual_seed(0)
+    a = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(n, k, device=_dev(), dtype=torch.bfloat16)
+    out = torch.empty(m, n, device=_dev(), dtype=torch.bfloat16)
+    ops.gemm(a, b, out, m, n, k)
+    want = a.float() @ b.float().t()
+    assert _rel_err(out, want) < 5e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 2048, 1408), (1000, 264, 520), (2048, 2048, 4096)])
+def test_gemm_dgrad_layout(m, n, k):
+    """C[m,n] = A[m,k] @ B[k,n] with B stored [k,n] (n contiguous)."""
+    torch.manual_seed(1)
+    a = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(k, n, device=_dev(), dtype=torch.bfloat16)
+    out = torch.empty(m, n, device=_dev(), dtype=torch.bfloat16)
+    ops.gemm(a, b, out, m, n, k, b_mn_major=True)
+    assert _rel_err(out, a.float() @ b.float()) < 5e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (1408, 2048, 512), (264, 520, 1000), (2048, 2048, 8192)])
+def test_gemm_wgrad_layout_accumulates_fp32(m, n, k):
+    """C[m,n] += A^T B with A stored [k,m], B stored [k,n]; fp32 accumulation into C."""
+    torch.manual_seed(2)
+    a = torch.randn(k, m, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(k, n, device=_dev(), dtype=torch.bfloat16)
+    acc = torch.randn(m, n, device=_dev(), dtype=torch.float32)
+    want = acc + a.float().t() @ b.float()
+    ops.gemm(a, b, acc, m, n, k, a_mn_major=True, b_mn_major=True, epilogue=1)
+    assert _rel_err(acc, want) < 2e-3
+    out = torch.empty(m, n, device=_dev(), dtype=torch.bfloat16)
+    ops.gemm(a, b, out, m, n, k, a_mn_major=True, b_mn_major=True)
+    assert _rel_err(out, a.float().t() @ b.float()) < 5e-3
+
+
+def test_gemm_strided_operands():
+    """Column slices of wider buffers are passed by leading dimension, not copied."""
+    torch.manual_seed(3)
+    wide = torch.randn(512, 1024, device=_dev(), dtype=torch.bfloat16)
+    a = wide[:, 256:768]
+    b = torch.randn(384, 512, device=_dev(), dtype=torch.bfloat16)
+    outw = torch.zeros(512, 1024, device=_dev(), dtype=torch.bfloat16)
+    ops.gemm(a, b, outw[:, 128:512], 512, 384, 512)
+    assert _rel_err(outw[:, 128:512], a.float() @ b.float().t()) < 5e-3
+    assert float(outw[:, :128].abs().max()) == 0.0 and float(outw[:, 512:].abs().max()) == 0.0
+
+
+def test_linear_autograd_matches_reference():
+    torch.manual_seed(4)
+    x = torch.randn(4, 96, 512, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(1024, 512, device=_dev()) * 0.05).to(torch.bfloat16).requires_grad_()
+    y = ops.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = reference.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 5e-3 and _rel_err(x.grad, xr.grad) < 5e-3 and _rel_err(w.grad, wr.grad) < 5e-3
+
+
+@pytest.mark.parametrize("rows,dim", [(300, 2048), (64, 4096), (17, 264), (5, 8192)])
+def test_rmsnorm_with_residual(rows, dim):
+    torch.manual_seed(5)
+    x = torch.randn(rows, dim, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    d = torch.randn(rows, dim, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    g = (1 + 0.1 * torch.randn(dim, device=_dev())).to(torch.bfloat16).requires_grad_()
+    h, y = ops.add_rms_norm(x, d, g, 1e-5)
+    gh, gy = torch.randn_like(h), torch.randn_like(y)
+    torch.autograd.backward([h, y], [gh, gy])
+    xr, dr, gr = (t.detach().float().requires_grad_() for t in (x, d, g))
+    hr = (xr + dr)
+    # the kernel normalises the bf16-rounded residual stream
+    hq = hr + (hr.detach().to(torch.bfloat16).float() - hr.detach())
+    yr = reference.rms_norm(hq, gr, 1e-5)
+    torch.autograd.backward([hr, yr], [gh.float(), gy.float()])
+    assert _rel_err(h, hr) < 4e-3 and _rel_err(y, yr) < 8e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(d.grad, dr.grad) < 1e-2
+    assert _rel_err(g.grad, gr.grad) < 2e-2
+
+
+def test_swiglu_interleaved():
+    torch.manual_seed(6)
+    gu = torch.randn(257, 2 * 1408, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    act = ops.swiglu_interleaved(gu)
+    g = torch.randn_like(act)
+    act.backward(g)
+    gur = gu.detach().float().requires_grad_()
+    actr = reference.swiglu_interleaved(gur)
+    actr.backward(g.float())
+    assert _rel_err(act, actr) < 5e-3 and _rel_err(gu.grad, gur.grad) < 8e-3
+
+
+def test_embedding_and_scatter_add():
+    torch.manual_seed(7)
+    table = torch.randn(1000, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1000, (4, 300), device=_dev())
+    out = ops.embedding(ids, table)
+    g = torch.randn_like(out)
+    out.backward(g)
+    tr = table.detach().float().requires_grad_()
+    tr[ids].backward(g.float())
+    assert torch.equal(out, table.detach()[ids])
+    assert _rel_err(table.grad, tr.grad) < 5e-3
+
+
+@pytest.mark.parametrize("rows,vocab", [(64, 32000), (33, 1000), (7, 8193)])
+def test_cross_entropy_and_fused_head(rows, vocab):
+    torch.manual_seed(8)
+    dim = 256
+    h = torch.randn(rows, dim, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    pad = (vocab + 7) // 8 * 8
+    w = (torch.randn(pad, dim, device=_dev()) * 0.05).to(torch.bfloat16)[:vocab].requires_grad_()
+    t = torch.randint(0, vocab, (rows,), device=_dev())
+    if vocab % 8:
+        pytest.skip("fused head needs an 8-aligned vocabulary row pitch; padded vocabularies are the supported case")
+    loss = ops.linear_cross_entropy(h, w, t)
+    loss.backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = reference.cross_entropy(reference.linear(hr, wr), t)
+    lr.backward()
+    assert abs(float(loss) - float(lr)) < 2e-2
+    assert _rel_err(h.grad, hr.grad) < 3e-2 and _rel_err(w.grad, wr.grad) < 3e-2
+    with torch.no_grad():
+        assert abs(float(ops.linear_cross_entropy(h, w, t)) - float(lr)) < 2e-2
+
+
+def test_sumsq_and_adamw_flat():
+    from ajllm_b200.training.optim import flat_adamw, flat_sumsq
+
+    torch.manual_seed(9)
+    n = 1_000_003
+    grad = torch.randn(n + 1, device=_dev())[:n]
+    grad = grad.contiguous()
+    ss = flat_sumsq(grad)
+    assert abs(float(ss) - float(grad.double().square().sum())) / float(ss) < 1e-5
+    assert float(flat_sumsq(grad)) == float(ss)          # fixed reduction order
+    master = torch.randn(n, device=_dev())
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    work = torch.empty(n, device=_dev(), dtype=torch.bfloat16)
+    cm, cg, cmm, cv = master.cpu().clone(), grad.cpu().clone(), m.cpu().clone(), v.cpu().clone()
+    for step in (1, 2):
+        flat_adamw(master, grad, m, v, work, step, 1e-2, 0.9, 0.95, 1e-8, 0.1, ss, 1.0)
+        flat_adamw(cm, cg, cmm, cv, None, step, 1e-2, 0.9, 0.95, 1e-8, 0.1, ss.cpu(), 1.0)
+    assert float((master.cpu() - cm).abs().max()) < 1e-5
+    assert torch.equal(work, master.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 256, 4, 2, 128), (1, 200, 2, 2, 128), (2, 384, 8, 2, 64), (1, 1024, 2, 1, 128)])
+def test_flash_attention_forward_backward(B, T, Hq, Hkv, hd):
+    torch.manual_seed(10)
+    width = (Hq + 2 * Hkv) * hd
+    qkv = (torch.randn(B, T, width, device=_dev()) * 0.5).to(torch.bfloat16).requires_grad_()
+    cos, sin = reference.rope_tables(hd, T, 10000.0, device=_dev())
+    out = ops.rope_attention(qkv, cos, sin, Hq, Hkv, hd)
+    g = torch.randn_like(out)
+    out.backward(g)
+
+    ref_in = qkv.detach().float().requires_grad_()
+    q, k, v = ops.split_packed_qkv(ref_in, Hq, Hkv, hd)
+    pos = torch.arange(T, device=_dev())
+    qr, kr = reference.rope_interleaved(q, cos, sin, pos), reference.rope_interleaved(k, cos, sin, pos)
+    want = reference.attention(qr, kr, v, causal=True).reshape(B, T, Hq * hd)
+    want.backward(g.float())
+    assert _rel_err(out, want) < 1.5e-2
+    nq, nk = Hq * hd, Hkv * hd
+    assert _rel_err(qkv.grad[..., :nq], ref_in.grad[..., :nq]) < 3e-2
+    assert _rel_err(qkv.grad[..., nq:nq + nk], ref_in.grad[..., nq:nq + nk]) < 3e-2
+    assert _rel_err(qkv.grad[..., nq + nk:], ref_in.grad[..., nq + nk:]) < 3e-2
+
+
+def test_no_wait_expired():
+    """Every bounded wait in the kernels above completed; a status word would mean a protocol bug."""
+    assert native.lib().ajb_check_status() == 0
