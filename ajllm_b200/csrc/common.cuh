@@ -142,8 +142,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // alignment; should the runtime ever place it elsewhere, the CTA reports it and leaves before touching
 // any barrier or tensor memory. A CTA also leaves at once when an earlier CTA of the same kernel has
 // already recorded an expired wait, so a protocol bug costs one time budget, not one per wave.
-__device__ __forceinline__ bool smem_misaligned(const void* base, DeviceStatus* status, int kernel_id) {
-  __shared__ uint32_t skip_cta;
+// `skip_word` is a word of the CTA's dynamic shared memory that nothing else uses.
+__device__ __forceinline__ bool smem_misaligned(const void* base, DeviceStatus* status, int kernel_id,
+                                                volatile uint32_t* skip_word) {
   if (threadIdx.x == 0) {
     const bool bad = (smem_u32(base) & 1023u) != 0;
     if (bad && status != nullptr &&
@@ -152,10 +153,10 @@ __device__ __forceinline__ bool smem_misaligned(const void* base, DeviceStatus* 
       status[kernel_id].detail0 = smem_u32(base);
     }
     const bool failed_before = status != nullptr && *reinterpret_cast<volatile unsigned int*>(&status[kernel_id].code) != 0u;
-    skip_cta = (bad || failed_before) ? 1u : 0u;
+    *skip_word = (bad || failed_before) ? 1u : 0u;
   }
   __syncthreads();
-  return skip_cta != 0u;
+  return *skip_word != 0u;
 }
 
 // TMA tile loads (no multicast anywhere in this library).

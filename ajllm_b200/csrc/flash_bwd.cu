@@ -85,13 +85,13 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_co
   using Cfg = KvCfg<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  if (smem_misaligned(smem, p.status, kFlashBwdKV)) return;
   uint8_t* sK = smem;
   uint8_t* sV = sK + Cfg::kTile;
   uint8_t* sQdO = sV + Cfg::kTile;            // stage s: Q at sQdO + s*2*tile, dO right after
   uint8_t* sPdS = sQdO + 4 * Cfg::kTile;
   float* sStats = reinterpret_cast<float*>(sPdS + Cfg::kPds);   // [stage][lse 128 | delta 128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStats + 2 * 2 * BLK);
+  if (smem_misaligned(smem, p.status, kFlashBwdKV, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* kv_full = bars;          // 1
   uint64_t* qdo_full = bars + 1;     // 2
   uint64_t* qdo_empty = bars + 3;    // 2
@@ -348,12 +348,12 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
   using Cfg = QCfg<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  if (smem_misaligned(smem, p.status, kFlashBwdQ)) return;
   uint8_t* sQ = smem;
   uint8_t* sDO = sQ + Cfg::kTile;
   uint8_t* sKV = sDO + Cfg::kTile;           // stage s: K at sKV + s*2*tile, V right after
   uint8_t* sDS = sKV + 4 * Cfg::kTile;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + Cfg::kDs);
+  if (smem_misaligned(smem, p.status, kFlashBwdQ, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* q_full = bars;           // 1
   uint64_t* kv_full = bars + 1;      // 2
   uint64_t* kv_empty = bars + 3;     // 2

@@ -47,11 +47,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
   using Cfg = FwdCfg<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  if (smem_misaligned(smem, p.status, kFlashFwd)) return;
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Cfg::kTileBytes;               // stage s: K at sKV + s*2*tile, V right after
   uint8_t* sP = sKV + 4 * Cfg::kTileBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+  if (smem_misaligned(smem, p.status, kFlashFwd, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* q_full = bars;            // 1
   uint64_t* kv_full = bars + 1;       // 2
   uint64_t* kv_empty = bars + 3;      // 2

@@ -63,9 +63,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   using Cfg = Config<BN>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  if (smem_misaligned(smem, p.status, kGemm)) return;
   uint8_t* stage_base = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  if (smem_misaligned(smem, p.status, kGemm, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* full = bars;
   uint64_t* empty = bars + Cfg::kStages;
   uint64_t* acc_full = bars + 2 * Cfg::kStages;
