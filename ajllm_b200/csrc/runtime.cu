@@ -68,7 +68,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Descriptor encoding is a driver call and needs the primary context current on the calling thread.
+// Threads that have only ever used the runtime lazily (autograd worker threads, for one) may not have
+// it bound yet; one cudaFree(nullptr) per thread binds it.
+static void bind_context_once() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 static EncodeTiledFn encode_fn() {
+  bind_context_once();
   static EncodeTiledFn fn = nullptr;
   if (fn == nullptr) {
     void* ptr = nullptr;

@@ -1,0 +1,123 @@
+"""Runs a :class:`~ajllm_b200.models.TransformerLM` in serving mode over a paged KV cache.
+
+One call processes a ragged batch: every scheduled sequence contributes ``n_i`` new tokens (a prompt
+chunk, one decode token, or ``k+1`` tokens of a speculative verify). Keys and values of the new tokens
+are written to the sequence's cache slots and each new token attends to everything cached for its
+sequence up to and including itself. Under tensor parallelism activations are replicated, every rank
+holds its own heads of the cache, and the two row-parallel projections end in an all-reduce.
+Weights may be bf16 tensors or block-scaled fp8 (:mod:`ajllm_b200.engine.quant`).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ajllm_b200 import ops
+from ajllm_b200.engine.kv_cache import PagedKVCache
+from ajllm_b200.engine.quant import Fp8Weight, fp8_linear
+from ajllm_b200.models.moe import MoEFeedForward
+from ajllm_b200.ops import reference
+
+
+@dataclass
+class RunItem:
+    seq_id: int
+    token_ids: list[int]
+    num_logits: int          # how many trailing positions need logits (0 = none)
+
+
+def _matmul(x: torch.Tensor, weight) -> torch.Tensor:
+    if isinstance(weight, Fp8Weight):
+        return fp8_linear(x, weight)
+    return ops.linear(x, weight)
+
+
+class ModelRunner:
+    def __init__(self, model, cache: PagedKVCache, quantization: str | None = None) -> None:
+        self.model = model
+        self.cache = cache
+        self.tp = getattr(model, "tp", None)
+        self.device = next(model.parameters()).device
+        self.dtype = next(model.parameters()).dtype
+        if model.norm_placement != "pre":
+            raise ValueError("the serving engine supports pre-norm models")
+        self.weights = []
+        for layer in model.layers:
+            entry = {"qkv": layer.attention.qkv_proj.data, "out": layer.attention.output_proj.data}
+            ff = layer.feed_forward
+            if isinstance(ff, MoEFeedForward):
+                entry["moe"] = ff
+            elif hasattr(ff, "w13"):
+                entry["w13"], entry["w2"] = ff.w13.data, ff.w2.data
+            else:
+                entry["w1"], entry["w2"] = ff.w1.data, ff.w2.data
+            if quantization == "fp8":
+                for key in ("qkv", "out", "w13", "w2", "w1"):
+                    if key in entry:
+                        entry[key] = Fp8Weight.from_dense(entry[key])
+            elif quantization not in (None, "none", "bf16"):
+                raise ValueError(f"unknown quantization '{quantization}'")
+            self.weights.append(entry)
+
+    def _reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None and self.tp.size > 1:
+            self.tp.all_reduce_sum_(x)
+        return x
+
+    @torch.no_grad()
+    def forward(self, items: list[RunItem]) -> torch.Tensor:
+        """Returns logits ``[sum_i num_logits_i, vocab]`` in item order."""
+        model, cache = self.model, self.cache
+        tokens, positions, slots, q_lens, ctx_lens, seq_ids, logit_rows = [], [], [], [], [], [], []
+        cursor = 0
+        for item in items:
+            start = cache.length(item.seq_id)
+            n = len(item.token_ids)
+            if start + n > model.context_length:
+                raise ValueError(f"sequence {item.seq_id} would exceed the context length {model.context_length}")
+            slots.extend(cache.append_slots(item.seq_id, n))
+            tokens.extend(item.token_ids)
+            positions.extend(range(start, start + n))
+            q_lens.append(n)
+            ctx_lens.append(start + n)
+            seq_ids.append(item.seq_id)
+            logit_rows.extend(range(cursor + n - item.num_logits, cursor + n))
+            cursor += n
+        dev = self.device
+        ids = torch.tensor(tokens, dtype=torch.long, device=dev)
+        pos = torch.tensor(positions, dtype=torch.long, device=dev)
+        slot_t = torch.tensor(slots, dtype=torch.long, device=dev)
+        tables = cache.block_table_tensor(seq_ids, dev)
+        ctx_t = torch.tensor(ctx_lens, dtype=torch.int32, device=dev)
+        qlen_t = torch.tensor(q_lens, dtype=torch.int32, device=dev)
+
+        stream = model.token_embeddings(ids)
+        if model.position_embeddings is not None:
+            stream = stream + model.position_embeddings(pos)
+        pending = None
+        for index, (layer, w) in enumerate(zip(model.layers, self.weights)):
+            attn = layer.attention
+            stream, normed = layer.norm1.add_and_norm(stream, pending)
+            qkv = _matmul(normed, w["qkv"])
+            q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
+            if attn.use_rope:
+                q = reference.rope_interleaved(q, attn.rope_cos, attn.rope_sin, pos)
+                k = reference.rope_interleaved(k, attn.rope_cos, attn.rope_sin, pos)
+            cache.write(index, slot_t, k, v)
+            attended = ops.paged_attention_ragged(q, cache.keys[index], cache.values[index], tables, ctx_t, qlen_t,
+                                                  q_lens, ctx_lens)
+            attended = self._reduce(_matmul(attended.reshape(ids.shape[0], -1), w["out"]))
+            stream, normed = layer.norm2.add_and_norm(stream, attended)
+            if "moe" in w:
+                pending = w["moe"](normed)
+            elif "w13" in w:
+                pending = self._reduce(_matmul(ops.swiglu_interleaved(_matmul(normed, w["w13"])), w["w2"]))
+            else:
+                pending = self._reduce(_matmul(ops.silu(_matmul(normed, w["w1"])), w["w2"]))
+        hidden = model.final_norm.add_and_norm(stream, pending)[1]
+        if not logit_rows:
+            return hidden.new_zeros(0, model.vocab_size)
+        rows = hidden[torch.tensor(logit_rows, dtype=torch.long, device=dev)]
+        return ops.linear(rows, model.head_weight).float()

@@ -8,6 +8,7 @@ from ajllm_b200.ops.functional import (
     gemm,
     linear,
     linear_cross_entropy,
+    paged_attention_ragged,
     rms_norm,
     rope_attention,
     silu,
@@ -17,5 +18,5 @@ from ajllm_b200.ops.functional import (
 
 __all__ = [
     "native", "reference", "add_rms_norm", "cross_entropy", "embedding", "gemm", "linear",
-    "linear_cross_entropy", "rms_norm", "rope_attention", "silu", "split_packed_qkv", "swiglu_interleaved",
+    "linear_cross_entropy", "paged_attention_ragged", "rms_norm", "rope_attention", "silu", "split_packed_qkv", "swiglu_interleaved",
 ]

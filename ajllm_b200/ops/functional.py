@@ -204,7 +204,8 @@ def rope_attention(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tenso
     """Causal self-attention over a packed ``[B, T, (Hq + 2 Hkv) * hd]`` projection.
 
     RoPE (interleaved pairs, ``ajllm/modeling/attention.py:50-60``) is applied to the q and k heads when
-    tables are given; the result is ``[B, T, Hq * hd]``.
+    tables are given; the result is ``[B, T, Hq * hd]``. On the GPU path the rotation is done in place:
+    ``qkv`` must be a buffer the caller no longer needs un-rotated (the output of the projection GEMM).
     """
     B, T, _ = qkv.shape
     if _is_cuda(qkv) and qkv.dtype == torch.bfloat16:
@@ -401,3 +402,34 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
                     flat.shape[1], flat.stride(0), 0.0, 0, native.stream_ptr())
         return (loss_sum / flat.shape[0]).reshape(())
     return reference.cross_entropy(logits, targets)
+
+
+# ----------------------------------------------------------------------------- paged attention (serving)
+
+
+def paged_attention_ragged(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                           block_tables: torch.Tensor, context_lens: torch.Tensor, q_lens: torch.Tensor,
+                           q_lens_host: list[int], context_lens_host: list[int]) -> torch.Tensor:
+    """Attention of ragged new tokens over a paged KV cache.
+
+    ``q`` is ``[total_new_tokens, Hq, hd]``, concatenated per sequence; sequence ``i`` contributes
+    ``q_lens[i]`` rows which sit at positions ``context_lens[i] - q_lens[i] ..`` of that sequence and
+    attend causally to its first ``context_lens[i]`` cached tokens. Caches are
+    ``[num_blocks, block, Hkv, hd]``. Returns ``[total_new_tokens, Hq, hd]``.
+    """
+    if _is_cuda(q) and q.dtype == torch.bfloat16 and native.available() and hasattr(native.lib(), "ajb_paged_attention"):
+        from ajllm_b200.ops import serving
+        return serving.paged_attention(q, key_cache, value_cache, block_tables, context_lens, q_lens,
+                                       q_lens_host, context_lens_host)
+    out = torch.empty_like(q)
+    block = key_cache.shape[1]
+    cursor = 0
+    for i, (n, length) in enumerate(zip(q_lens_host, context_lens_host)):
+        nblk = (length + block - 1) // block
+        ids = block_tables[i, :nblk].long()
+        keys = key_cache[ids].reshape(nblk * block, *key_cache.shape[2:])[:length]
+        values = value_cache[ids].reshape(nblk * block, *value_cache.shape[2:])[:length]
+        out[cursor:cursor + n] = reference.attention(q[cursor:cursor + n][None], keys[None], values[None],
+                                                     causal=True)[0]
+        cursor += n
+    return out

@@ -1,0 +1,6 @@
+"""Parallel runtime: process mesh, tensor / expert / fully-sharded data parallelism, symmetric memory."""
+
+from ajllm_b200.parallel.mesh import AxisGroup, ParallelMesh, init_distributed
+from ajllm_b200.parallel.tensor_parallel import TensorParallel, tp_optimizer_classes
+
+__all__ = ["AxisGroup", "ParallelMesh", "init_distributed", "TensorParallel", "tp_optimizer_classes"]

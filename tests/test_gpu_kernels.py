@@ -179,11 +179,12 @@ def test_flash_attention_forward_backward(B, T, Hq, Hkv, hd):
     width = (Hq + 2 * Hkv) * hd
     qkv = (torch.randn(B, T, width, device=_dev()) * 0.5).to(torch.bfloat16).requires_grad_()
     cos, sin = reference.rope_tables(hd, T, 10000.0, device=_dev())
-    out = ops.rope_attention(qkv, cos, sin, Hq, Hkv, hd)
+    ref_in = qkv.detach().float().requires_grad_()
+    # the GPU path rotates q and k inside the packed buffer it is given, so hand it a copy
+    out = ops.rope_attention(qkv.clone(), cos, sin, Hq, Hkv, hd)
     g = torch.randn_like(out)
     out.backward(g)
 
-    ref_in = qkv.detach().float().requires_grad_()
     q, k, v = ops.split_packed_qkv(ref_in, Hq, Hkv, hd)
     pos = torch.arange(T, device=_dev())
     qr, kr = reference.rope_interleaved(q, cos, sin, pos), reference.rope_interleaved(k, cos, sin, pos)
