@@ -105,7 +105,14 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+# kernels launched per entry point (everything else launches one)
+_LAUNCHES_PER_CALL = {"ajb_flash_bwd": 3, "ajb_sumsq_f32": 2}
+launch_count = 0
+
+
 def call(name: str, *args) -> None:
+    global launch_count
+    launch_count += _LAUNCHES_PER_CALL.get(name, 1)
     fn = getattr(lib(), name)
     status = fn(*args)
     if status != 0:

@@ -6,7 +6,7 @@ from ajllm_b200.training.logger import RunLogger
 from ajllm_b200.training.losses import cross_entropy
 from ajllm_b200.training.optim import AdamW, FlatAdamW, clip_gradients
 from ajllm_b200.training.schedulers import warmup_cosine_learning_rate
-from ajllm_b200.training.trainer import Trainer
+from ajllm_b200.training.trainer import Trainer, optimizer_step
 
 __all__ = [
     "load_checkpoint", "save_checkpoint", "BatchStager", "SyntheticTokens", "TokenDataset", "RunLogger",

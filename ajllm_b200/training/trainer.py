@@ -49,6 +49,21 @@ def _mean_over_group(value: torch.Tensor, group=None) -> torch.Tensor:
     return value
 
 
+def optimizer_step(model, optimizer, next_batch, accumulation: int, gradient_clip: float):
+    """One optimisation step: ``accumulation`` micro-batches of forward + backward, then the clipped
+    AdamW update. ``next_batch()`` yields device ``(inputs, targets)``. Returns ``(loss, grad_norm)`` as
+    device scalars (the loss is the mean over the micro-batches); nothing is read back to the host."""
+    optimizer.zero_grad(set_to_none=True)
+    total = None
+    for _ in range(accumulation):
+        inputs, targets = next_batch()
+        loss = model.loss(inputs, targets, 1.0 / accumulation)
+        loss.backward()
+        piece = loss.detach().float() / accumulation
+        total = piece if total is None else total + piece
+    return total, optimizer.step(gradient_clip)
+
+
 class Trainer:
     def __init__(self, model: torch.nn.Module, train_dataset, validation_dataset, run_directory: str | Path,
                  config: dict[str, Any], device: torch.device, seed: int, optimizer=None,
@@ -170,14 +185,8 @@ class Trainer:
                 if use_cuda:
                     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     begin.record()
-                self.optimizer.zero_grad(set_to_none=True)
-                loss_value = torch.zeros((), device=self.device)
-                for _ in range(accumulation):
-                    inputs, targets = stager.next()
-                    loss = self._loss(inputs, targets, 1.0 / accumulation)
-                    loss.backward()
-                    loss_value = loss_value + loss.detach().float() / accumulation
-                gradient_norm = self.optimizer.step(gradient_clip)
+                loss_value, gradient_norm = optimizer_step(self.model, self.optimizer, stager.next, accumulation,
+                                                           gradient_clip)
                 if use_cuda:
                     end.record()
                     pending_events.append((begin, end))

@@ -1,0 +1,328 @@
+"""Headline benchmark: training tokens/s of the dense 1.3B-class decoder (24 layers, d_model 2048,
+16 heads x 128, 8 KV heads, SwiGLU 5632, vocab 32000, seq 4096, global batch 32 sequences, bf16 with
+fp32 AdamW master weights, no activation checkpointing) on N GPUs of one node, tensor-parallel over N.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 5 --warmup 3
+    python bench.py --impl reference ...        # the unmodified reference from baseline/_ref
+
+Rank 0 prints one JSON line. ``value`` is device-timed (CUDA events, max over ranks) with the step's
+token batches already resident on the GPU; ``e2e`` times the same steps through the training API with
+every micro-batch copied from pinned host memory and the loss read back each step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+MODEL = {"name": "dense_1p3b", "context_length": 4096, "d_model": 2048, "num_layers": 24, "num_heads": 16,
+         "num_kv_heads": 8, "d_ff": 5632, "position_encoding": {"type": "rope", "theta": 10000.0},
+         "init": {"type": "normal", "std": 0.02}}
+VOCAB = 32000
+GLOBAL_BATCH = 32
+SEQ = 4096
+METRIC = "train tokens/sec"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch (0 = pick by N)")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    ap.add_argument("--seq", type=int, default=SEQ)
+    return ap.parse_args()
+
+
+def baseline_value():
+    try:
+        published = json.loads((ROOT / "BASELINE.json").read_text()).get("published") or {}
+        for key in ("train_tokens_per_sec", "tokens_per_sec", "value"):
+            if key in published:
+                return float(published[key])
+    except Exception:
+        pass
+    return None
+
+
+def emit(payload: dict) -> None:
+    print(json.dumps(payload), flush=True)
+
+
+def synthetic_batches(global_batch: int, seq: int, micro: int, count: int, pin: bool):
+    """``count`` steps of uniform-random token ids (seed 0): list[step] of list[micro-batch] of int64
+    ``[micro, seq + 1]`` host tensors."""
+    import torch
+
+    gen = torch.Generator().manual_seed(0)
+    steps = []
+    for _ in range(count):
+        tokens = torch.randint(0, VOCAB, (global_batch, seq + 1), generator=gen, dtype=torch.int64)
+        pieces = [tokens[i:i + micro].contiguous() for i in range(0, global_batch, micro)]
+        steps.append([p.pin_memory() if pin else p for p in pieces])
+    return steps
+
+
+# =============================================================================================== ours
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from ajllm_b200.models import build_model
+    from ajllm_b200.ops import native
+    from ajllm_b200.parallel import ParallelMesh, TensorParallel, init_distributed, tp_optimizer_classes
+    from ajllm_b200.training import FlatAdamW, optimizer_step
+    from ajllm_b200.utils.timing import ClockSampler, max_over_ranks
+
+    rank, world, device = init_distributed("cuda")
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}; launch with torch.distributed.run")
+    assert native.available(), "native kernel library missing: run python -m ajllm_b200.build"
+    torch.manual_seed(0)
+    config = dict(MODEL)
+    config["context_length"] = args.seq
+    if args.layers:
+        config["num_layers"] = args.layers
+    tp = None
+    classes = None
+    if world > 1:
+        mesh = ParallelMesh(tp=world)
+        fused = None
+        if os.environ.get("AJB_FUSED_TP", "1") != "0":
+            try:
+                from ajllm_b200.parallel.fused import FusedTensorParallel
+                fused = FusedTensorParallel(mesh.tp.group, device)
+            except Exception as error:  # noqa: BLE001 - reported in the JSON line
+                fused = None
+                if rank == 0:
+                    print(f"[bench] fused TP unavailable, using NCCL collectives: {error}", file=sys.stderr)
+        tp = TensorParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size, fused=fused)
+        classes = tp_optimizer_classes(tp)
+    micro = args.micro_batch or {1: 8, 2: 8, 4: 16, 8: 32}.get(world, 8)
+    micro = min(micro, args.global_batch)
+    accumulation = args.global_batch // micro
+    with torch.device(device):
+        model = build_model(config, VOCAB, tp=tp)
+    model = model.to(device=device, dtype=torch.bfloat16)
+    optimizer = FlatAdamW(model, learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1, classes=classes)
+    params = sum(p.numel() for p in model.parameters())
+
+    total_steps = args.warmup + args.steps
+    host_steps = synthetic_batches(args.global_batch, args.seq, micro, total_steps, pin=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def device_feed(step_batches):
+        staged = [b.to(device, non_blocking=True) for b in step_batches]
+        it = iter(staged)
+
+        def next_batch():
+            t = next(it)
+            return t[:, :-1], t[:, 1:]
+        return next_batch
+
+    # ---- pass A: device-timed, batches resident on the GPU
+    for s in range(args.warmup):
+        optimizer_step(model, optimizer, device_feed(host_steps[s]), accumulation, 1.0)
+    timed = host_steps[args.warmup:]
+    feeds = [device_feed(b) for b in timed]
+    barrier()
+    sampler = ClockSampler(device.index or 0).start()
+    launches0 = native.launch_count
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for feed in feeds:
+        loss, norm = optimizer_step(model, optimizer, feed, accumulation, 1.0)
+    end.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = native.launch_count - launches0
+    ms = max_over_ranks(begin.elapsed_time(end), device)
+    final_loss = float(loss) * (world if tp is not None else 1)
+    tokens = args.global_batch * args.seq * args.steps
+    value = tokens / (ms / 1e3)
+
+    # ---- pass B: end to end (pinned host -> device every micro-batch, loss read back every step)
+    copy_stream = torch.cuda.Stream(device=device)
+
+    def host_feed(step_batches):
+        it = iter(step_batches)
+
+        def next_batch():
+            with torch.cuda.stream(copy_stream):
+                t = next(it).to(device, non_blocking=True)
+            torch.cuda.current_stream().wait_stream(copy_stream)
+            t.record_stream(torch.cuda.current_stream())
+            return t[:, :-1], t[:, 1:]
+        return next_batch
+
+    barrier()
+    t0 = time.perf_counter()
+    begin2, end2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin2.record()
+    readback = []
+    for step_batches in timed:
+        loss, norm = optimizer_step(model, optimizer, host_feed(step_batches), accumulation, 1.0)
+        readback.append(float(loss))          # device -> host read of the step's result
+    end2.record()
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max_over_ranks(max(begin2.elapsed_time(end2), wall_ms), device)
+    h2d = args.global_batch * (args.seq + 1) * 8
+    status = native.lib().ajb_check_status()
+
+    if rank == 0:
+        base = baseline_value()
+        emit({
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / base) if base else None, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": "dense-1.3B (24L d2048 16h/8kv hd128 ffn5632 vocab32000)", "params": params * (world if False else 1),
+                       "global_batch": args.global_batch, "seq_len": args.seq, "micro_batch": micro,
+                       "grad_accumulation": accumulation, "parallelism": f"tp{world}",
+                       "tp_backend": ("fused-symmetric-memory" if (tp is not None and tp.fused is not None) else ("nccl" if tp else "none")),
+                       "optimizer": "AdamW fp32 master, global-norm clip 1.0", "activation_checkpointing": "off",
+                       "l2": "inputs larger than L2 (multi-GB working set per step)",
+                       "layers_override": args.layers or None},
+            "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
+                       "reasons": clocks.get("reasons"), "power_w_max": clocks.get("power_w_max")},
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches, "final_loss": final_loss, "kernel_status": status,
+            "valid": not args.layers and args.global_batch == GLOBAL_BATCH and args.seq == SEQ,
+        })
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# =============================================================================================== reference
+def run_reference(args) -> None:
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "ajllm" / "__init__.py").is_file():
+        emit({"impl": "reference", "unavailable": "baseline/_ref holds no reference install (see DESIGN.md)"})
+        return
+    sys.path.insert(0, str(ref_root))
+    try:
+        import torch
+        import torch.distributed as dist
+        from ajllm.modeling.factory import build_model
+        from ajllm.training.distributed import FullyShardedDataParallel
+        from ajllm.training.losses import cross_entropy
+        from ajllm.training.optimizers import AdamW
+        from ajllm.training.trainer import clip_gradients
+    except Exception as error:  # noqa: BLE001
+        emit({"impl": "reference", "unavailable": f"reference import failed: {type(error).__name__}: {error}"[:300]})
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    torch.manual_seed(0)
+    # the reference has no grouped KV heads: same shape with 16 full heads (1.364 B parameters)
+    config = {"name": "dense_1p3b_mha", "context_length": args.seq, "d_model": 2048, "num_layers": args.layers or 24,
+              "num_heads": 16, "d_ff": 5632, "position_encoding": {"type": "rope", "theta": 10000.0}}
+    try:
+        model = build_model(config, VOCAB, use_flash_attention=True).to(device)
+        model = FullyShardedDataParallel(model, compute_dtype=torch.bfloat16)
+        optimizer = AdamW(model.parameters(), learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1)
+        # no gradient accumulation in the reference: the optimizer steps on every micro-batch
+        micro = args.micro_batch or 4
+        per_rank = args.global_batch // world
+        micro = min(micro, per_rank)
+        total_steps = args.warmup + args.steps
+        host_steps = synthetic_batches(args.global_batch, args.seq, micro, total_steps, pin=True)
+        mine = [[b for i, b in enumerate(step) if i % world == rank] for step in host_steps]
+
+        def one_step(step_batches):
+            last = None
+            for batch in step_batches:
+                t = batch.to(device, non_blocking=True)
+                logits = model(t[:, :-1])
+                loss = cross_entropy(logits, t[:, 1:])
+                optimizer.zero_grad(set_to_none=True)
+                loss.backward()
+                model.finish_gradient_synchronization()
+                clip_gradients(model.parameters(), 1.0)
+                optimizer.step()
+                last = loss
+            return last
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for s in range(args.warmup):
+            one_step(mine[s])
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        begin.record()
+        for s in range(args.warmup, total_steps):
+            loss = one_step(mine[s])
+            float(loss)
+        end.record()
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        ms = begin.elapsed_time(end)
+        if world > 1:
+            box = torch.tensor([ms, wall_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(box, op=dist.ReduceOp.MAX)
+            ms, wall_ms = float(box[0]), float(box[1])
+        flash_used = None
+        try:
+            from ajllm.modeling import flash_attention as fa
+            cache = getattr(fa.flash_fwd_kernel, "device_caches", None) or getattr(fa.flash_fwd_kernel, "cache", None)
+            flash_used = bool(cache) and any(bool(v) for v in (cache.values() if hasattr(cache, "values") else [cache]))
+        except Exception:  # noqa: BLE001
+            pass
+        tokens = args.global_batch * args.seq * args.steps
+        if rank == 0:
+            emit({
+                "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+                "config": {"model": "dense-1.3B as the reference can express it: MHA 16 heads (1.364B params)",
+                           "global_batch": args.global_batch, "seq_len": args.seq, "micro_batch": micro,
+                           "parallelism": f"reference FSDP over {world} (its only parallelism), bf16 compute, Triton flash attention",
+                           "note": "no gradient accumulation in the reference: optimizer step per micro-batch",
+                           "triton_flash_kernel_compiled": flash_used},
+                "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s",
+                        "h2d_bytes_per_step": args.global_batch * (args.seq + 1) * 8, "d2h_bytes_per_step": 4},
+            })
+    except Exception as error:  # noqa: BLE001
+        if rank == 0:
+            emit({"impl": "reference", "unavailable": f"reference run failed: {type(error).__name__}: {error}"[:400]})
+    if world > 1 and dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    arguments = parse_args()
+    if arguments.impl == "reference":
+        run_reference(arguments)
+    else:
+        run_ours(arguments)
