@@ -53,12 +53,9 @@ class SelfAttention(nn.Module):
         init_matrix_(full_o, num_heads * hd, d_model, init)
         self.qkv_proj = nn.Parameter(self.pack_qkv(*self._shard_qkv(full_q, full_k, full_v)))
         self.output_proj = nn.Parameter(self._shard_out(full_o))
-        if self.use_rope:
-            cos, sin = reference.rope_tables(hd, context_length, rope_theta)
-            self.register_buffer("rope_cos", cos, persistent=False)
-            self.register_buffer("rope_sin", sin, persistent=False)
-        else:
-            self.rope_cos = self.rope_sin = None
+        # cos/sin tables stay fp32 whatever dtype the module is cast to (the kernels read fp32), so they
+        # are cached per device instead of being registered as buffers
+        self._rope_tables: dict = {}
         self._register_state_dict_hook(self._split_on_save)
         self._register_load_state_dict_pre_hook(self._merge_on_load)
 
@@ -107,6 +104,22 @@ class SelfAttention(nn.Module):
         key = prefix + "output_proj.weight"
         if key in state:
             state[prefix + "output_proj"] = self._shard_out(state.pop(key))
+
+    def rope_tables(self, device) -> tuple[torch.Tensor | None, torch.Tensor | None]:
+        if not self.use_rope:
+            return None, None
+        key = str(device)
+        if key not in self._rope_tables:
+            self._rope_tables[key] = reference.rope_tables(self.head_dim, self.context_length, self.rope_theta, device)
+        return self._rope_tables[key]
+
+    @property
+    def rope_cos(self):
+        return self.rope_tables(self.qkv_proj.device)[0]
+
+    @property
+    def rope_sin(self):
+        return self.rope_tables(self.qkv_proj.device)[1]
 
     # ----- compute
     def project_qkv(self, x: torch.Tensor) -> torch.Tensor:

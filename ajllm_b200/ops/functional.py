@@ -210,6 +210,8 @@ def rope_attention(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tenso
     B, T, _ = qkv.shape
     if _is_cuda(qkv) and qkv.dtype == torch.bfloat16:
         use_rope = cos is not None
+        if use_rope and (cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape[0] < T):
+            raise ValueError("RoPE tables must be fp32 and cover the sequence length")
         dummy = qkv.new_empty(1, dtype=torch.float32)
         return _RopeAttentionFn.apply(qkv, cos if use_rope else dummy, sin if use_rope else dummy,
                                       num_heads, num_kv_heads, head_dim, causal, use_rope)
