@@ -592,3 +592,54 @@ extern "C" int ajb_add_bf16(const void* a, const void* b, void* out, long long n
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of ajb_sumsq_f32 (declared in ajllm_b200.h; no counterpart in the reference).
+//
+// Who needs it: code that runs where device memory cannot be requested. Examples are an inference
+// plug-in whose enqueue hook is forbidden to allocate, a host thread working inside a region in which
+// the process has frozen its memory pool, or a tool that was handed a fixed memory budget up front
+// and owns no allocator at all. Such callers can still pass their input and a 4-byte output, but they
+// have nowhere to get the partial-sum buffer that the two-stage reduction needs between its kernels.
+//
+// The partial sums therefore live in a file-scope device array that is part of the loaded module:
+// every GPU that loads this library holds these 4 KB until the process exits. The array is shared by
+// every call. Stage one overwrites exactly the entries stage two reads, so nothing has to be cleared
+// between calls, but two calls that are in flight on the GPU at the same time (different streams)
+// would write the same entries and corrupt each other's result: callers must serialise them.
+//
+// A host function cannot use the array's name as a pointer (on the host the name is only a handle),
+// so the device address is looked up with cudaGetSymbolAddress once per device, with that device
+// current, on the first call made for that device. That first call should be made before any stream
+// capture begins, because the lookup is not a stream operation.
+constexpr long long kSumsqStaticMaxElements = 1ll << 32;   // 16 GiB of fp32 input
+static __device__ __align__(256) float g_sumsq_static_partials[ajb::pw::kSumsqBlocks];
+static float* g_sumsq_static_address[16] = {nullptr};
+
+extern "C" long long ajb_sumsq_f32_static_max_elements() { return kSumsqStaticMaxElements; }
+
+extern "C" int ajb_sumsq_f32_static(const void* x, long long n, void* out, void* stream) {
+  AJB_REQUIRE(x != nullptr && out != nullptr, "sumsq_static: input and output pointers are required");
+  AJB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, "sumsq_static: input must be 16-byte aligned");
+  AJB_REQUIRE(n >= 0 && n <= kSumsqStaticMaxElements,
+              "sumsq_static: %lld elements is outside the supported range [0, %lld]; use ajb_sumsq_f32 with a "
+              "caller-provided scratch buffer for larger inputs", n, kSumsqStaticMaxElements);
+  int device = -1;
+  AJB_CUDA_OK(cudaGetDevice(&device));
+  AJB_REQUIRE(device >= 0 && device < 16, "sumsq_static: device index %d is not supported", device);
+  if (g_sumsq_static_address[device] == nullptr) {
+    float* address = nullptr;
+    AJB_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_sumsq_static_partials));
+    AJB_REQUIRE(address != nullptr, "sumsq_static: the scratch symbol has no device address");
+    g_sumsq_static_address[device] = address;
+  }
+  float* partials = g_sumsq_static_address[device];
+  long long blocks = ((n >> 2) + kSumsqThreads - 1) / kSumsqThreads;
+  if (blocks < 1) blocks = 1;
+  if (blocks > kSumsqBlocks) blocks = kSumsqBlocks;
+  sumsq_partial_kernel<<<(int)blocks, kSumsqThreads, 0, STREAM(stream)>>>((const float*)x, n, partials);
+  AJB_CUDA_OK(cudaGetLastError());
+  sumsq_final_kernel<<<1, kSumsqThreads, 0, STREAM(stream)>>>(partials, (int)blocks, (float*)out);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
