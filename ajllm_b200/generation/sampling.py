@@ -27,7 +27,16 @@ def sample_next_token(logits: torch.Tensor, temperature: float, top_p: float | N
     """``logits`` is ``[rows, vocab]``; returns ``[rows, 1]`` token ids."""
     if temperature <= 0:
         return torch.argmax(logits, dim=-1, keepdim=True)
-    probs = sampling_probabilities(logits, temperature, top_p)
+    probs = torch.softmax(logits.float() / temperature, dim=-1)
+    if top_p is not None and top_p < 1.0:
+        if not 0 < top_p <= 1:
+            raise ValueError("top_p must be in (0, 1]")
+        # draw in sorted order, as the reference does, so equal seeds give equal tokens
+        ordered, index = torch.sort(probs, descending=True, dim=-1)
+        before = torch.cumsum(ordered, dim=-1) - ordered
+        ordered = ordered.masked_fill(before >= top_p, 0.0)
+        ordered = ordered / ordered.sum(dim=-1, keepdim=True)
+        return torch.gather(index, -1, torch.multinomial(ordered, 1, generator=generator))
     return torch.multinomial(probs, 1, generator=generator)
 
 

@@ -1,0 +1,160 @@
+import pytest
+import torch
+
+from ajllm_b200.engine import BlockAllocator, LLMEngine, OutOfBlocks, PagedKVCache, SamplingParams, Scheduler
+from ajllm_b200.engine.quant import Fp8Weight, fp8_linear
+from ajllm_b200.engine.spec_decode import verify_greedy, verify_rejection
+from ajllm_b200.generation import generate, sample_next_token, sampling_probabilities
+from ajllm_b200.models import build_model
+from ajllm_b200.ops import reference
+
+CFG = {"name": "e", "context_length": 128, "d_model": 64, "num_layers": 2, "num_heads": 4, "num_kv_heads": 2, "d_ff": 128}
+
+
+@pytest.fixture(scope="module")
+def models():
+    torch.manual_seed(0)
+    return build_model(CFG, 300), build_model({**CFG, "num_layers": 1}, 300)
+
+
+def _prompts():
+    gen = torch.Generator().manual_seed(5)
+    return [torch.randint(0, 300, (n,), generator=gen).tolist() for n in (5, 17, 33, 9)]
+
+
+def test_block_allocator_and_rollback():
+    alloc = BlockAllocator(3)
+    a, b, c = alloc.allocate(), alloc.allocate(), alloc.allocate()
+    with pytest.raises(OutOfBlocks):
+        alloc.allocate()
+    alloc.share(a)
+    alloc.release(a)
+    assert alloc.free_blocks == 0
+    alloc.release(a)
+    assert alloc.free_blocks == 1
+    cache = PagedKVCache(1, 8, 4, 1, 8, torch.float32, torch.device("cpu"))
+    slots = cache.append_slots(7, 10)
+    assert len(slots) == 10 and len(cache.tables[7].blocks) == 3
+    cache.truncate(7, 5)
+    assert cache.length(7) == 5 and len(cache.tables[7].blocks) == 2 and cache.allocator.free_blocks == 6
+    cache.fork(7, 8)
+    assert cache.allocator.ref_count(cache.tables[7].blocks[0]) == 2
+    cache.free(7); cache.free(8)
+    assert cache.allocator.free_blocks == 8
+
+
+def test_paged_attention_matches_contiguous_attention():
+    torch.manual_seed(1)
+    cache = PagedKVCache(1, 16, 4, 2, 8, torch.float32, torch.device("cpu"))
+    lens = [9, 4, 13]
+    ks, vs = [torch.randn(n, 2, 8) for n in lens], [torch.randn(n, 2, 8) for n in lens]
+    for sid, (k, v) in enumerate(zip(ks, vs)):
+        cache.write(0, torch.tensor(cache.append_slots(sid, k.shape[0])), k, v)
+    q = torch.randn(3, 2, 4, 8)     # two query rows per sequence (verify-style)
+    out = reference.paged_attention(q, cache.keys[0], cache.values[0], cache.block_table_tensor([0, 1, 2], torch.device("cpu")),
+                                    torch.tensor(lens))
+    for i in range(3):
+        want = reference.attention(q[i:i + 1], ks[i][None], vs[i][None], causal=True)
+        assert torch.allclose(out[i:i + 1], want, atol=1e-5)
+
+
+@pytest.mark.needs_reference
+def test_sampling_and_greedy_generation_match_the_reference(reference_path):
+    from ajllm.generation.generator import generate as ref_generate
+    from ajllm.generation.sampling import sample_next_token as ref_sample
+    from ajllm.modeling.factory import build_model as ref_build
+
+    cfg = {k: v for k, v in CFG.items() if k != "num_kv_heads"}
+    torch.manual_seed(0)
+    ref, ours = ref_build(cfg, 300), build_model(cfg, 300)
+    ours.load_state_dict(ref.state_dict())
+    prompt = torch.randint(0, 300, (7,))
+    assert ref_generate(ref, prompt, 20, 0.0, None, None).tolist() == generate(ours, prompt, 20, 0.0, None, None).tolist()
+    logits = torch.randn(3, 50)
+    for top_p in (None, 0.3, 0.9):
+        torch.manual_seed(11); a = ref_sample(logits, 0.7, top_p)
+        torch.manual_seed(11); b = sample_next_token(logits, 0.7, top_p)
+        assert torch.equal(a, b)
+
+
+def test_top_p_keeps_the_token_that_crosses_the_threshold():
+    probs = sampling_probabilities(torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]])), 1.0, 0.6)
+    assert torch.allclose(probs, torch.tensor([[0.625, 0.375, 0.0, 0.0]]), atol=1e-6)
+    with pytest.raises(ValueError):
+        sampling_probabilities(torch.zeros(1, 4), 1.0, 0.0)
+
+
+def test_continuous_batching_equals_one_at_a_time(models):
+    target, _ = models
+    prompts = _prompts()
+    batched = LLMEngine(target, num_blocks=64, max_num_seqs=3, max_batched_tokens=24).generate(prompts, SamplingParams(20, 0.0, None))
+    single = [generate(target, torch.tensor(p), 20, 0.0).tolist()[len(p):] for p in prompts]
+    assert [o.output for o in batched] == single
+    assert all(o.finish_reason == "length" for o in batched)
+
+
+def test_preemption_by_recompute_preserves_outputs(models):
+    target, _ = models
+    prompts = _prompts()
+    roomy = LLMEngine(target, num_blocks=64, max_num_seqs=4).generate(prompts, SamplingParams(20, 0.0, None))
+    tight_engine = LLMEngine(target, num_blocks=8, max_num_seqs=4, max_batched_tokens=64)
+    tight = tight_engine.generate(prompts, SamplingParams(20, 0.0, None))
+    assert tight_engine.stats.preemptions > 0
+    assert [o.output for o in tight] == [o.output for o in roomy]
+    assert tight_engine.cache.allocator.free_blocks == 8
+
+
+def test_eos_stops_a_sequence(models):
+    target, _ = models
+    prompt = _prompts()[0]
+    free_run = LLMEngine(target, num_blocks=32).generate([prompt], SamplingParams(10, 0.0, None))[0].output
+    stopped = LLMEngine(target, num_blocks=32).generate([prompt], SamplingParams(10, 0.0, None, eos_token_id=free_run[3]))[0]
+    assert stopped.finish_reason == "eos" and stopped.output == free_run[:free_run.index(free_run[3]) + 1]
+
+
+def test_speculative_greedy_is_lossless_and_self_draft_accepts_everything(models):
+    target, draft = models
+    prompts = _prompts()
+    plain = LLMEngine(target, num_blocks=64).generate(prompts, SamplingParams(20, 0.0, None))
+    spec_engine = LLMEngine(target, num_blocks=64, draft_model=draft, num_speculative_tokens=4)
+    assert [o.output for o in spec_engine.generate(prompts, SamplingParams(20, 0.0, None))] == [o.output for o in plain]
+    self_engine = LLMEngine(target, num_blocks=64, draft_model=target, num_speculative_tokens=3)
+    outs = self_engine.generate(prompts, SamplingParams(12, 0.0, None))
+    assert [o.output for o in outs] == [o.output[:12] for o in plain]
+    assert self_engine.stats.acceptance_rate == 1.0 and self_engine.stats.steps < 12
+    assert self_engine.cache.allocator.free_blocks == 64 and self_engine.draft_cache.allocator.free_blocks == 64
+
+
+def test_rejection_sampling_preserves_the_target_distribution():
+    torch.manual_seed(0)
+    gen = torch.Generator().manual_seed(0)
+    p = torch.tensor([0.5, 0.2, 0.2, 0.1])
+    q = torch.tensor([0.1, 0.6, 0.2, 0.1])
+    counts = torch.zeros(4)
+    trials = 20000
+    for _ in range(trials):
+        d = torch.multinomial(q, 1, generator=gen)
+        accepted, nxt = verify_rejection(d, q[None], torch.stack([p, p]), gen)
+        counts[int(d) if accepted == 1 else nxt] += 1      # first emitted token
+    assert torch.allclose(counts / trials, p, atol=0.015)
+    assert verify_greedy(torch.tensor([3, 1, 2]), torch.eye(5)[[3, 1, 4, 0]]) == (2, 4)
+
+
+def test_fp8_block_quantisation_error_is_small():
+    torch.manual_seed(0)
+    w, x = torch.randn(200, 300) * 0.05, torch.randn(7, 300)
+    q = Fp8Weight.from_dense(w)
+    assert q.q.dtype == torch.float8_e4m3fn and q.scale.shape == (2, 3)
+    assert (q.dequantize() - w).abs().max() / w.abs().max() < 0.07
+    y = fp8_linear(x, q)
+    assert (y - x @ w.t()).norm() / (x @ w.t()).norm() < 0.06
+
+
+def test_scheduler_rejects_impossible_requests(models):
+    target, _ = models
+    cache = PagedKVCache(1, 2, 4, 1, 8, torch.float32, torch.device("cpu"))
+    sched = Scheduler(cache, max_num_seqs=2, max_batched_tokens=64, context_length=128)
+    with pytest.raises(ValueError):
+        sched.add([], SamplingParams())
+    sched.add(list(range(30)), SamplingParams())
+    assert sched.schedule() == []          # the prompt can never fit in two blocks of four tokens

@@ -1,0 +1,105 @@
+import json
+
+import pytest
+import torch
+import yaml
+
+from ajllm_b200.cli import build_parser
+from ajllm_b200.workflows import lm_compare, lm_evaluate, lm_generate, lm_sweep, lm_train, model_report
+from ajllm_b200.workflows.lm_train_distributed import build_command, parse
+from tests.helpers import base_run, loaded, make_project, prepare_artifacts, train_config
+
+
+@pytest.fixture(scope="module")
+def project(tmp_path_factory):
+    root = make_project(tmp_path_factory.mktemp("project"))
+    prepare_artifacts(root)
+    return root
+
+
+def test_tokenizer_artifacts_are_registered(project):
+    tok = json.loads((project / "artifacts/tokenizers/toy_bpe/manifest.json").read_text())
+    enc = json.loads((project / "artifacts/encoded/toy/toy_bpe/manifest.json").read_text())
+    assert tok["artifact_type"] == "tokenizer" and tok["vocab_size"] == 290 and "fingerprint" in tok
+    assert enc["dtype"] == "uint32" and enc["tokenizer_fingerprint"] == tok["fingerprint"]
+    for split in ("train", "validation"):
+        entry = enc["splits"][split]
+        assert (project / "artifacts/encoded/toy/toy_bpe" / entry["path"]).stat().st_size == 4 * entry["token_count"]
+
+
+def test_train_then_resume_then_generate_with_best(project):
+    first = lm_train.run(loaded(project, train_config(project, max_steps=1)))
+    run_dir = project / first["run_directory"] if not first["run_directory"].startswith("/") else None
+    from pathlib import Path
+    run_dir = Path(first["run_directory"])
+    names = {p.name for p in (run_dir / "checkpoints").iterdir()}
+    assert {"final.pt", "latest.pt", "best.pt", "step_00000001.pt"} <= names
+    for name in ("resolved_config.yaml", "manifest.json", "metrics.jsonl", "summary.json", "model_report.md"):
+        assert (run_dir / name).is_file()
+    events = [json.loads(line) for line in (run_dir / "metrics.jsonl").read_text().splitlines()]
+    assert {"train", "evaluation"} <= {e["event"] for e in events}
+    train_event = next(e for e in events if e["event"] == "train")
+    assert {"loss", "learning_rate", "gradient_norm", "tokens_per_second"} <= set(train_event)
+    resumed = lm_train.run(loaded(project, train_config(project, max_steps=2,
+                                                       resume_from=str(run_dir / "checkpoints" / "final.pt"))))
+    assert resumed["steps"] == 2 and resumed["status"] == "completed"
+    ckpt = torch.load(Path(resumed["run_directory"]) / "checkpoints" / "final.pt", weights_only=False)
+    assert ckpt["step"] == 2 and ckpt["optimizer_state_dict"]["state"][0]["step"] == 2
+
+    gen = lm_generate.run(loaded(project, {"name": "g", "run_directory": str(run_dir), "checkpoint": "best",
+                                           "prompts": ["The night train", "A small robot"], "max_new_tokens": 5,
+                                           "temperature": 0.0, "samples_per_prompt": 2, "device": "cpu"}))
+    assert len(gen["results"]) == 2 and len(gen["results"][0]["completions"]) == 2
+    a, b = gen["results"][0]["completions"]
+    assert a["text"] == b["text"] and a["text"].startswith("The night train")      # greedy is deterministic
+    ev = lm_evaluate.run(loaded(project, {"name": "e", "run_directory": str(run_dir), "checkpoint": "final",
+                                          "batches": 2, "batch_size": 2, "device": "cpu"}))
+    assert ev["perplexity"] == pytest.approx(pytest.importorskip("math").exp(ev["loss"]))
+
+
+def test_sweep_compare_and_report(project):
+    cfg = train_config(project, max_steps=1)
+    cfg.update({"name": "lr", "grid": {"optimizer.max_lr": [1e-3, 3e-3]}, "comparison": {"generate_plot": True}})
+    sweep = lm_sweep.run(loaded(project, cfg))
+    assert len(sweep["trials"]) == 2 and sweep["best_run"] is not None
+    out = sweep["output_dir"]
+    from pathlib import Path
+    assert (Path(out) / "comparison.csv").is_file() and (Path(out) / "trials.json").is_file()
+    assert any(Path(out).glob("learning_curves.*"))
+    runs = [t["run_directory"] for t in sweep["trials"]]
+    cmp = lm_compare.run(loaded(project, {"name": "c", "runs": runs, "generate_plot": False}))
+    losses = [r["validation_loss"] for r in cmp["results"]]
+    assert losses == sorted(losses)
+    rep = model_report.run(loaded(project, {"model": base_run(project)["model"], "report_vocab_size": 290}))
+    assert Path(rep["output_path"]).is_file() and rep["parameter_count"] > 0
+
+
+def test_sweep_records_failed_trials_when_asked(project):
+    cfg = train_config(project, max_steps=1)
+    cfg.update({"name": "bad", "grid": {"model.num_heads": [4, 5]}, "continue_on_error": True,
+                "comparison": {"generate_plot": False}})
+    sweep = lm_sweep.run(loaded(project, cfg))
+    assert [t.get("status") for t in sweep["trials"]].count("failed") == 1
+
+
+def test_training_refuses_a_mismatched_tokenizer(project):
+    manifest_path = project / "artifacts/encoded/toy/toy_bpe/manifest.json"
+    original = manifest_path.read_text()
+    data = json.loads(original)
+    data["tokenizer_fingerprint"] = "0" * 64
+    manifest_path.write_text(json.dumps(data))
+    try:
+        with pytest.raises(ValueError, match="different tokenizer"):
+            lm_train.run(loaded(project, train_config(project, max_steps=1)))
+    finally:
+        manifest_path.write_text(original)
+
+
+def test_cli_accepts_every_verb_and_launcher_builds_torchrun():
+    parser = build_parser()
+    for argv in (["tokenizer", "train"], ["tokenizer", "encode"], ["lm", "train"], ["lm", "sweep"], ["lm", "evaluate"],
+                 ["lm", "compare"], ["lm", "generate"], ["model", "report"]):
+        assert parser.parse_args([*argv, "--config", "x.yaml"]).config == "x.yaml"
+    command = build_command(parse(["--config", "c.yaml", "--nproc-per-node", "4"]))
+    assert "torch.distributed.run" in command and command[-5:] == ["ajllm_b200", "lm", "train", "--config", "c.yaml"]
+    assert command[command.index("--master-addr") + 1] == "127.0.0.1"
