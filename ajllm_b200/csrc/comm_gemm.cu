@@ -1,0 +1,529 @@
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (sm_100a).
+//
+//   ag_gemm : C[M, N] = gather_rows(A_shards)[M, K] * op(B)      (column-parallel: all-gather -> GEMM)
+//   gemm_rs : C_local[M/tp, N] = reduce_scatter_rows(A[M, K] * op(B))   (row-parallel: GEMM -> reduce-scatter)
+//
+// Both are one persistent kernel per rank built on the same tcgen05 main loop as gemm_bf16.cu
+// (TMA ring -> tcgen05.mma -> TMEM -> epilogue warps).
+//
+// ag_gemm: a few "copy" CTAs pull every peer's [M/tp, K] shard out of that peer's symmetric staging
+// buffer with bulk asynchronous copies (peer global -> shared -> local global; no multicast) and
+// publish one flag per shard; the GEMM CTAs walk the output tiles shard by shard, starting with the
+// shard that is already local, and their TMA producer waits for a shard's flag before touching it,
+// so each remote byte crosses NVLink once and the transfer hides behind the tiles of earlier shards.
+//
+// gemm_rs: tiles are visited so that the rows owned by the other ranks come first; the epilogue stores
+// each bf16 partial tile straight into the owning rank's symmetric receive buffer (slot = this rank)
+// and bumps a counter there; after its last tile every CTA waits until all partials of its own rows
+// have arrived and sums them in fp32 into the local output.
+//
+// Every wait on another CTA or another GPU is bounded (see common.cuh); on expiry the kernel records a
+// status word, skips the dependent work and exits through the normal teardown.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace ajb {
+namespace comm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = BN * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 256;
+constexpr int kMaxRanks = 8;
+constexpr int kGroupM = 16;
+constexpr int kCopyPiece = 32768;                       // bytes per bulk copy
+constexpr int kCopyBufs = kStages * kStageBytes / kCopyPiece;   // 6 pieces in flight per copy CTA
+
+enum Mode : int { kAllGather = 0, kReduceScatter = 1 };
+
+struct Params {
+  int mode;
+  int m, n, k;            // full problem (m = all rows)
+  int tp, rank;
+  int m_local;            // rows per rank
+  int copy_ctas;          // all-gather: CTAs that move data instead of computing
+  // all-gather
+  const void* stage_ptrs[kMaxRanks];     // each rank's symmetric [m_local, k] staging buffer (peer addresses)
+  void* gathered;                        // local [m, k]
+  unsigned int* shard_flags;             // local, zeroed by the host before launch, one per shard
+  // reduce-scatter
+  void* recv_ptrs[kMaxRanks];            // each rank's symmetric [tp, m_local, n] receive buffer
+  unsigned int* counter_ptrs[kMaxRanks]; // each rank's symmetric arrival counters, one per source rank
+  unsigned int expected_count;           // counter value that means "all partials of this call arrived"
+  void* out_local;                       // [m_local, n] bf16 (reduce-scatter) / [m, n] bf16 (all-gather)
+  long long ldc;
+  // cross-rank handshakes (symmetric flag words)
+  unsigned int* ready_ptrs[kMaxRanks];   // ready_ptrs[p][r] : rank r's staging buffer holds this call's data
+  unsigned int* done_ptrs[kMaxRanks];    // done_ptrs[p][r]  : rank r no longer touches rank p's buffers for this call
+  unsigned int epoch;
+  unsigned int* local_cta_counter;       // local, zeroed by the host before launch
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded spin until *p >= want (signed distance, so epochs may wrap). `sys` selects the scope.
+__device__ __forceinline__ bool wait_ge(const unsigned int* p, unsigned int want, bool sys, volatile uint32_t* abort_flag,
+                                        DeviceStatus* status, int stage) {
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    const unsigned int v = sys ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if ((int)(v - want) >= 0) return true;
+    if (abort_flag != nullptr && *abort_flag) return false;
+    if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (abort_flag != nullptr) *abort_flag = 1;
+      if (status != nullptr && atomicCAS(&status[kCommGemm].code, 0u, (unsigned)((stage << 8) | (kCommGemm + 1))) == 0u) {
+        status[kCommGemm].block = blockIdx.x;
+        status[kCommGemm].detail0 = want;
+        status[kCommGemm].detail1 = v;
+      }
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+// Tile order: shard by shard (`first_shard`, then increasing modulo tp); inside a shard, groups of
+// kGroupM row-blocks sweep the column blocks so a wave of CTAs shares its panels through L2.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m_local, int tiles_n, int tp, int first_shard,
+                                            int& shard, int& tm, int& tn) {
+  const int per_shard = tiles_m_local * tiles_n;
+  const int s = tile / per_shard;
+  shard = (first_shard + s) % tp;
+  const int within_shard = tile - s * per_shard;
+  const int group_span = kGroupM * tiles_n;
+  const int group = within_shard / group_span;
+  const int first_m = group * kGroupM;
+  const int rows = min(kGroupM, tiles_m_local - first_m);
+  const int within = within_shard - group * group_span;
+  tm = shard * tiles_m_local + first_m + within % rows;
+  tn = within / rows;
+}
+
+// ---- bulk copies (async proxy, no multicast)
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// One copy CTA's share of the all-gather: thread 0 streams 32 KB pieces through a shared-memory ring.
+__device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* bars, volatile uint32_t* abort_flag) {
+  if (threadIdx.x != 0) return;
+  const int cta = blockIdx.x, n_copy = p.copy_ctas;
+  const long long shard_bytes = (long long)p.m_local * p.k * 2;
+  const long long pieces = (shard_bytes + kCopyPiece - 1) / kCopyPiece;
+  if (cta == 0) {
+    // tell every peer that this rank's staging buffer holds the data of this call
+    for (int r = 0; r < p.tp; ++r) st_release_sys(p.ready_ptrs[r] + p.rank, p.epoch);
+  }
+  uint32_t issued = 0, drained = 0;   // running counts over all shards (ring position / barrier phase)
+  bool ok = true;
+  for (int s = 0; s < p.tp && ok; ++s) {
+    const int shard = (p.rank + s) % p.tp;
+    if (shard != p.rank) ok = wait_ge(p.ready_ptrs[p.rank] + shard, p.epoch, true, abort_flag, p.status, 20);
+    if (!ok) break;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.stage_ptrs[shard]);
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.gathered) + (long long)shard * shard_bytes;
+    // pieces cta, cta + n_copy, ... of this shard
+    long long next_load = cta, next_store = cta;
+    auto piece_bytes = [&](long long piece) -> uint32_t {
+      const long long off = piece * kCopyPiece;
+      return (uint32_t)min((long long)kCopyPiece, shard_bytes - off);
+    };
+    while (next_store < pieces) {
+      while (next_load < pieces && issued - drained < (uint32_t)kCopyBufs) {
+        const int buf = issued % kCopyBufs;
+        mbar_arrive_expect_tx(&bars[buf], piece_bytes(next_load));
+        bulk_g2s(ring + (size_t)buf * kCopyPiece, src + next_load * kCopyPiece, piece_bytes(next_load), &bars[buf]);
+        ++issued;
+        next_load += n_copy;
+      }
+      const int buf = drained % kCopyBufs;
+      if (!mbar_wait(&bars[buf], (drained / kCopyBufs) & 1, abort_flag, p.status, kCommGemm, 21)) { ok = false; break; }
+      bulk_s2g(dst + next_store * kCopyPiece, ring + (size_t)buf * kCopyPiece, piece_bytes(next_store));
+      bulk_commit();
+      bulk_wait_read_all();      // the ring slot may be refilled once the store has read it
+      ++drained;
+      next_store += n_copy;
+    }
+    bulk_wait_all();             // stores of this shard are complete in global memory
+    fence_proxy_async_all();
+    __threadfence();
+    red_release_gpu_add(p.shard_flags + shard, 1u);
+  }
+  if (!ok) {
+    // loads still in flight land in this CTA's shared memory: give them a bounded moment before leaving
+    const unsigned long long t0 = global_timer_ns();
+    while (issued != drained && global_timer_ns() - t0 < 100000000ull) {
+      if (mbar_try_wait(&bars[drained % kCopyBufs], (drained / kCopyBufs) & 1)) ++drained;
+    }
+  }
+  // last copy CTA to finish tells the peers that it no longer reads their staging buffers, then waits for
+  // the same message from everyone so that the next call may overwrite this rank's buffer
+  if (atomicAdd(p.local_cta_counter, 1u) == (unsigned)(n_copy - 1)) {
+    for (int r = 0; r < p.tp; ++r) st_release_sys(p.done_ptrs[r] + p.rank, p.epoch);
+    for (int r = 0; r < p.tp; ++r)
+      if (!wait_ge(p.done_ptrs[p.rank] + r, p.epoch, true, nullptr, p.status, 22)) break;
+  }
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  if (smem_misaligned(smem, p.status, kCommGemm, reinterpret_cast<uint32_t*>(bars) + 60)) return;
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* acc_full = bars + 2 * kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint64_t* copy_bars = acc_empty + 2;                              // kCopyBufs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(copy_bars + kCopyBufs);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_copy_cta = p.mode == kAllGather && (int)blockIdx.x < p.copy_ctas;
+
+  if (is_copy_cta) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < kCopyBufs; ++i) mbar_init(&copy_bars[i], 1);
+      *abort_flag = 0;
+      fence_barrier_init();
+    }
+    __syncthreads();
+    copy_cta_all_gather(p, smem, copy_bars, abort_flag);
+    return;
+  }
+
+  const int first_gemm_cta = p.mode == kAllGather ? p.copy_ctas : 0;
+  const int gemm_ctas = (int)gridDim.x - first_gemm_cta;
+  const int gemm_id = (int)blockIdx.x - first_gemm_cta;
+  const int tiles_m_local = p.m_local / BM;
+  const int tiles_n = (p.n + BN - 1) / BN;
+  const int num_tiles = tiles_m_local * p.tp * tiles_n;
+  const int num_kb = (p.k + BK - 1) / BK;
+  // all-gather: the local shard is ready first. reduce-scatter: the rows this rank owns come last.
+  const int first_shard = p.mode == kAllGather ? p.rank : (p.rank + 1) % p.tp;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensor_map(&map_a);
+    prefetch_tensor_map(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0, ready_shard = -1;
+      bool ok = true;
+      for (int tile = gemm_id; tile < num_tiles && ok; tile += gemm_ctas) {
+        int shard, tm, tn;
+        tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, shard, tm, tn);
+        if (p.mode == kAllGather && shard != ready_shard) {
+          if (!wait_ge(p.shard_flags + shard, (unsigned)p.copy_ctas, false, abort_flag, p.status, 10)) { ok = false; break; }
+          fence_proxy_async_all();      // copied rows were written through the async proxy of other CTAs
+          ready_shard = shard;
+        }
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kCommGemm, 1)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_arrive_expect_tx(&full[stage], kStageBytes);
+          const int k0 = kb * BK;
+          tma_load_2d(sa, &map_a, &full[stage], k0, m0);
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0);
+          } else {
+            tma_load_2d(sb, &map_b, &full[stage], k0, n0);
+          }
+          ++issued;
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        const int pending = min(issued, kStages);
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) { s = kStages - 1; ph ^= 1; }
+          const unsigned long long t0 = global_timer_ns();
+          while (!mbar_try_wait(&full[s], ph) && global_timer_ns() - t0 < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc = make_idesc(BM, BN, 1, false, B_MN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int iter = 0;
+    bool ok = true;
+    for (int tile = gemm_id; tile < num_tiles && ok; tile += gemm_ctas, ++iter) {
+      const int buf = iter & 1;
+      const uint32_t use = (uint32_t)(iter >> 1);
+      if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, kCommGemm, 2)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kCommGemm, 3)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = desc_k_major(sa, k * UMMA_K * 2);
+            const uint64_t db = B_MN ? desc_mn_major(sb, BK * 128, k * UMMA_K) : desc_k_major(sb, k * UMMA_K * 2);
+            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      if (ok && lane == 0) tc_commit(&acc_full[buf]);
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    int iter = 0;
+    bool ok = true;
+    for (int tile = gemm_id; tile < num_tiles && ok; tile += gemm_ctas, ++iter) {
+      const int buf = iter & 1;
+      const uint32_t use = (uint32_t)(iter >> 1);
+      int shard, tm, tn;
+      tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, shard, tm, tn);
+      if (!mbar_wait(&acc_full[buf], use & 1, abort_flag, p.status, kCommGemm, 4)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = tm * BM + quarter * 32 + lane;
+      const int col0 = tn * BN;
+      const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
+      __nv_bfloat16* dst_row;
+      if (p.mode == kAllGather) {
+        dst_row = reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row * p.ldc;
+      } else {
+        // partial sums of shard `shard` go to that rank's receive buffer, slot = this rank
+        dst_row = reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[shard]) +
+                  ((long long)p.rank * p.m_local + (row - shard * p.m_local)) * p.n;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + (uint32_t)c, v);
+        tc_wait_ld();
+        const int col = col0 + c;
+        if (col >= p.n) continue;
+        const int valid = min(32, p.n - col);
+        __nv_bfloat16* dst = dst_row + col;
+        if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+            q.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            q.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            q.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            reinterpret_cast<uint4*>(dst)[j] = q;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) dst[j] = __float2bfloat16(__uint_as_float(v[j]));
+        }
+      }
+      tc_fence_before_sync();
+      if (p.mode == kReduceScatter) __threadfence_system();   // partial tile visible to its owner before the count
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&acc_empty[buf]);
+        if (p.mode == kReduceScatter) red_release_sys_add(p.counter_ptrs[shard] + p.rank, 1u);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+
+  if (p.mode == kReduceScatter) {
+    // ---- sum the tp partial copies of the rows this rank owns (fp32) into the local output
+    __shared__ int arrived;
+    if (threadIdx.x == 0) {
+      bool ok = *abort_flag == 0;
+      for (int r = 0; r < p.tp && ok; ++r)
+        ok = wait_ge(p.counter_ptrs[p.rank] + r, p.expected_count, true, nullptr, p.status, 30);
+      arrived = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (arrived) {
+      const long long vec_total = (long long)p.m_local * p.n / 8;
+      const uint4* base = reinterpret_cast<const uint4*>(p.recv_ptrs[p.rank]);
+      uint4* out = reinterpret_cast<uint4*>(p.out_local);
+      for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < vec_total; i += (long long)gridDim.x * kThreads) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int r = 0; r < p.tp; ++r) {
+          const uint4 q = base[(long long)r * vec_total + i];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        out[i] = o;
+      }
+    }
+    __syncthreads();
+    // the last CTA tells the peers that this rank is done reading its receive buffer, and waits for the
+    // same from everyone: after the kernel, every rank may write into every receive buffer again
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(p.local_cta_counter, 1u) == gridDim.x - 1) {
+        for (int r = 0; r < p.tp; ++r) st_release_sys(p.done_ptrs[r] + p.rank, p.epoch);
+        for (int r = 0; r < p.tp; ++r)
+          if (!wait_ge(p.done_ptrs[p.rank] + r, p.epoch, true, nullptr, p.status, 31)) break;
+      }
+    }
+  }
+}
+
+}  // namespace comm
+}  // namespace ajb
+
+// Shared argument block (all pointer tables have `tp` entries). See comm::Params for the meaning.
+struct AjbCommArgs {
+  int mode, m, n, k, tp, rank, b_mn_major, copy_ctas;
+  long long ldb, ldc;
+  const void* a;                 // reduce-scatter: local [m, k] activations; all-gather: unused
+  const void* b;                 // local weight shard
+  void* out;                     // all-gather: [m, n]; reduce-scatter: [m / tp, n]
+  void* gathered;                // all-gather: local [m, k] buffer that receives every shard
+  const void* stage_ptrs[8];
+  void* recv_ptrs[8];
+  unsigned int* counter_ptrs[8];
+  unsigned int* ready_ptrs[8];
+  unsigned int* done_ptrs[8];
+  unsigned int* shard_flags;     // local scratch (>= 8 words) + 1 word CTA counter at index 8
+  unsigned int expected_count;
+  unsigned int epoch;
+};
+
+extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
+  using namespace ajb;
+  using namespace ajb::comm;
+  const AjbCommArgs& a = *args;
+  AJB_REQUIRE(a.tp >= 2 && a.tp <= kMaxRanks, "comm_gemm: tp must be in [2, %d]", kMaxRanks);
+  AJB_REQUIRE(a.m % a.tp == 0 && (a.m / a.tp) % BM == 0, "comm_gemm: rows per rank (%d / %d) must be a multiple of %d",
+              a.m, a.tp, BM);
+  AJB_REQUIRE(a.k % 8 == 0 && a.n % 8 == 0, "comm_gemm: n and k must be multiples of 8");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  Params p;
+  memset(&p, 0, sizeof(p));
+  p.mode = a.mode; p.m = a.m; p.n = a.n; p.k = a.k; p.tp = a.tp; p.rank = a.rank;
+  p.m_local = a.m / a.tp;
+  p.copy_ctas = a.mode == kAllGather ? a.copy_ctas : 0;
+  for (int r = 0; r < a.tp; ++r) {
+    p.stage_ptrs[r] = a.stage_ptrs[r];
+    p.recv_ptrs[r] = a.recv_ptrs[r];
+    p.counter_ptrs[r] = a.counter_ptrs[r];
+    p.ready_ptrs[r] = a.ready_ptrs[r];
+    p.done_ptrs[r] = a.done_ptrs[r];
+  }
+  p.gathered = a.gathered;
+  p.shard_flags = a.shard_flags;
+  p.local_cta_counter = a.shard_flags + 8;
+  p.expected_count = a.expected_count;
+  p.out_local = a.out;
+  p.ldc = a.ldc;
+  p.epoch = a.epoch;
+  p.status = device_status_buffer();
+  AJB_CUDA_OK(cudaMemsetAsync(a.shard_flags, 0, 16 * sizeof(unsigned int), s));
+
+  const void* a_ptr = a.mode == kAllGather ? a.gathered : a.a;
+  CUtensorMap map_a, map_b;
+  int rc = make_tensor_map_2d(&map_a, a_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.m, a.k, (uint64_t)a.k * 2, BM, 64);
+  if (rc) return rc;
+  if (a.b_mn_major) rc = make_tensor_map_2d(&map_b, a.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.k, a.n, a.ldb * 2, BK, 64);
+  else              rc = make_tensor_map_2d(&map_b, a.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.k, a.ldb * 2, BN, 64);
+  if (rc) return rc;
+  static bool configured[2] = {false, false};
+  const int which = a.b_mn_major ? 1 : 0;
+  if (!configured[which]) {
+    if (which) AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    else       AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    configured[which] = true;
+  }
+  // every CTA of this kernel must be resident at once (copy CTAs feed compute CTAs): one CTA per SM
+  const int grid = sm_count();
+  AJB_REQUIRE(p.copy_ctas < grid, "comm_gemm: too many copy CTAs");
+  if (which) comm_gemm_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
+  else       comm_gemm_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,205 @@
+"""Tensor-parallel projections fused with their collective over symmetric NVLink memory.
+
+``gather_linear`` (column-parallel, all-gather -> GEMM) and ``linear_scatter`` (row-parallel, GEMM ->
+reduce-scatter) each run as one persistent tcgen05 kernel per rank (``csrc/comm_gemm.cu``): remote
+activation shards are pulled from the peers' symmetric staging buffers by copy CTAs while the compute
+CTAs already work on the local shard, and partial output tiles are stored by the epilogue directly
+into the owning rank's symmetric receive buffer. The backward passes are the mirrored kernels
+(all-gather <-> reduce-scatter) plus a local weight-gradient GEMM. Symmetric buffers and flag words
+come from ``torch.distributed._symmetric_memory``; the NCCL path in
+:mod:`ajllm_b200.parallel.tensor_parallel` is the baseline these kernels are measured against.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ajllm_b200.ops import native
+from ajllm_b200.ops.functional import EPI_ACCUM_F32, gemm
+
+_MAX_RANKS = 8
+MODE_ALL_GATHER, MODE_REDUCE_SCATTER = 0, 1
+
+
+class _CommArgs(ctypes.Structure):
+    _fields_ = [
+        ("mode", ctypes.c_int), ("m", ctypes.c_int), ("n", ctypes.c_int), ("k", ctypes.c_int),
+        ("tp", ctypes.c_int), ("rank", ctypes.c_int), ("b_mn_major", ctypes.c_int), ("copy_ctas", ctypes.c_int),
+        ("ldb", ctypes.c_longlong), ("ldc", ctypes.c_longlong),
+        ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("out", ctypes.c_void_p), ("gathered", ctypes.c_void_p),
+        ("stage_ptrs", ctypes.c_void_p * _MAX_RANKS), ("recv_ptrs", ctypes.c_void_p * _MAX_RANKS),
+        ("counter_ptrs", ctypes.c_void_p * _MAX_RANKS), ("ready_ptrs", ctypes.c_void_p * _MAX_RANKS),
+        ("done_ptrs", ctypes.c_void_p * _MAX_RANKS),
+        ("shard_flags", ctypes.c_void_p), ("expected_count", ctypes.c_uint), ("epoch", ctypes.c_uint),
+    ]
+
+
+class FusedTensorParallel:
+    BLOCK_M, BLOCK_N = 128, 256
+
+    def __init__(self, group, device: torch.device, copy_ctas: int | None = None) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._symm = symm_mem
+        self.group = group
+        self.device = device
+        self.size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if not 2 <= self.size <= _MAX_RANKS:
+            raise ValueError("fused tensor parallelism supports 2..8 ranks")
+        self.copy_ctas = int(copy_ctas or os.environ.get("AJB_COPY_CTAS", "16"))
+        self.epoch = 0
+        self.expected_count = 0
+        self._stage = self._recv = None
+        self._stage_ptrs = self._recv_ptrs = None
+        # flag words: [0:8] ready, [8:16] done, [16:24] arrival counters
+        self._flags = symm_mem.empty(64, dtype=torch.int32, device=device)
+        self._flags.zero_()
+        self._flag_ptrs = list(symm_mem.rendezvous(self._flags, group).buffer_ptrs)
+        self._local = torch.zeros(16, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        fn = native.lib().ajb_comm_gemm
+        fn.argtypes = [ctypes.POINTER(_CommArgs), ctypes.c_void_p]
+        fn.restype = ctypes.c_int
+        self._fn = fn
+
+    # ------------------------------------------------------------------ symmetric buffers (grown on demand)
+    def _ensure(self, which: str, nbytes: int):
+        current = getattr(self, f"_{which}")
+        if current is not None and current.numel() >= nbytes:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        size = max(nbytes, 1 << 20)
+        buf = self._symm.empty(size, dtype=torch.uint8, device=self.device)
+        ptrs = list(self._symm.rendezvous(buf, self.group).buffer_ptrs)
+        setattr(self, f"_{which}", buf)
+        setattr(self, f"_{which}_ptrs", ptrs)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def supports(self, rows_total: int) -> bool:
+        return rows_total % self.size == 0 and (rows_total // self.size) % self.BLOCK_M == 0
+
+    def _launch(self, mode: int, m: int, n: int, k: int, b: torch.Tensor, b_mn: bool, out: torch.Tensor,
+                a: torch.Tensor | None = None, gathered: torch.Tensor | None = None) -> None:
+        self.epoch += 1
+        args = _CommArgs()
+        args.mode, args.m, args.n, args.k = mode, m, n, k
+        args.tp, args.rank, args.b_mn_major, args.copy_ctas = self.size, self.rank, int(b_mn), self.copy_ctas
+        args.ldb, args.ldc = b.stride(0), out.stride(0)
+        args.a = a.data_ptr() if a is not None else None
+        args.b, args.out = b.data_ptr(), out.data_ptr()
+        args.gathered = gathered.data_ptr() if gathered is not None else None
+        if mode == MODE_REDUCE_SCATTER:
+            tiles = (m // self.size // self.BLOCK_M) * ((n + self.BLOCK_N - 1) // self.BLOCK_N)
+            self.expected_count += tiles * 4          # one count per epilogue warp per tile
+        for r in range(self.size):
+            args.stage_ptrs[r] = self._stage_ptrs[r] if self._stage_ptrs else None
+            args.recv_ptrs[r] = self._recv_ptrs[r] if self._recv_ptrs else None
+            args.ready_ptrs[r] = self._flag_ptrs[r]
+            args.done_ptrs[r] = self._flag_ptrs[r] + 8 * 4
+            args.counter_ptrs[r] = self._flag_ptrs[r] + 16 * 4
+        args.shard_flags = self._local.data_ptr()
+        args.expected_count = self.expected_count & 0xFFFFFFFF
+        args.epoch = self.epoch & 0xFFFFFFFF
+        native.launch_count += 1
+        status = self._fn(ctypes.byref(args), native.stream_ptr())
+        if status != 0:
+            raise RuntimeError(f"ajb_comm_gemm failed: {native.lib().ajb_last_error().decode()}")
+
+    # ------------------------------------------------------------------ raw fused ops
+    def all_gather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, b_mn: bool, n: int, k: int):
+        """Returns ``(gathered [M, k], out [M, n])`` with ``out = gathered @ op(weight)``."""
+        m_local = x_local.shape[0]
+        m = m_local * self.size
+        self._ensure("stage", m_local * k * 2)
+        stage = self._stage[: m_local * k * 2].view(torch.bfloat16).view(m_local, k)
+        stage.copy_(x_local)
+        gathered = torch.empty(m, k, dtype=torch.bfloat16, device=self.device)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
+        self._launch(MODE_ALL_GATHER, m, n, k, weight, b_mn, out, gathered=gathered)
+        return gathered, out
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, weight: torch.Tensor, b_mn: bool, n: int, k: int) -> torch.Tensor:
+        """``reduce_scatter_rows(x @ op(weight))`` -> ``[M / tp, n]``."""
+        m = x.shape[0]
+        m_local = m // self.size
+        self._ensure("recv", self.size * m_local * n * 2)
+        out = torch.empty(m_local, n, dtype=torch.bfloat16, device=self.device)
+        self._launch(MODE_REDUCE_SCATTER, m, n, k, weight, b_mn, out, a=x)
+        return out
+
+    # ------------------------------------------------------------------ differentiable entry points
+    def gather_linear(self, x_local: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        if x_local.dtype != torch.bfloat16 or not self.supports(x_local.shape[0] * self.size):
+            from ajllm_b200 import ops
+            from ajllm_b200.parallel.tensor_parallel import _GatherRows
+            return ops.linear(_GatherRows.apply(x_local, self.group), weight)
+        return _GatherLinearFn.apply(x_local, weight, self)
+
+    def linear_scatter(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        if x.dtype != torch.bfloat16 or not self.supports(x.shape[0]):
+            from ajllm_b200 import ops
+            from ajllm_b200.parallel.tensor_parallel import _ScatterRows
+            return _ScatterRows.apply(ops.linear(x, weight), self.group)
+        return _LinearScatterFn.apply(x, weight, self)
+
+
+def _wgrad(grad_out: torch.Tensor, activations: torch.Tensor, weight: torch.Tensor):
+    """``dW[n, k] = grad_out[M, n]^T @ activations[M, k]`` into ``weight.main_grad`` or a new tensor."""
+    n, k = weight.shape
+    main = getattr(weight, "main_grad", None)
+    if main is not None:
+        gemm(grad_out, activations, main, n, k, grad_out.shape[0], a_mn_major=True, b_mn_major=True,
+             epilogue=EPI_ACCUM_F32)
+        weight.main_grad_written = True
+        return None
+    out = torch.empty(n, k, dtype=torch.bfloat16, device=grad_out.device)
+    gemm(grad_out, activations, out, n, k, grad_out.shape[0], a_mn_major=True, b_mn_major=True)
+    return out
+
+
+class _GatherLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local, weight, fused: FusedTensorParallel):
+        n, k = weight.shape
+        gathered, out = fused.all_gather_gemm(x_local.contiguous(), weight, False, n, k)
+        ctx.save_for_backward(gathered, weight)
+        ctx.fused = fused
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        gathered, weight = ctx.saved_tensors
+        n, k = weight.shape
+        grad_out = grad_out.contiguous()
+        # dX[M, k] = dY[M, n] @ W[n, k], reduce-scattered to this rank's tokens
+        grad_x = ctx.fused.gemm_reduce_scatter(grad_out, weight, True, k, n)
+        grad_w = _wgrad(grad_out, gathered, weight) if ctx.needs_input_grad[1] else None
+        return grad_x, grad_w, None
+
+
+class _LinearScatterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, fused: FusedTensorParallel):
+        n, k = weight.shape
+        x = x.contiguous()
+        out = fused.gemm_reduce_scatter(x, weight, False, n, k)
+        ctx.save_for_backward(x, weight)
+        ctx.fused = fused
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_local):
+        x, weight = ctx.saved_tensors
+        n, k = weight.shape
+        # dY is gathered over ranks while dX[M, k] = dY[M, n] @ W[n, k] runs on the shards already present
+        grad_full, grad_x = ctx.fused.all_gather_gemm(grad_local.contiguous(), weight, True, k, n)
+        grad_w = _wgrad(grad_full, x, weight) if ctx.needs_input_grad[1] else None
+        return grad_x, grad_w, None
