@@ -31,15 +31,18 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + 256;
+constexpr int kEpiRowPitch = BN * 2 + 16;               // staged output rows, padded against bank conflicts
+constexpr int kEpiBytes = BM * kEpiRowPitch;            // one bf16 output tile, staged for bulk row stores
+constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 512;
 constexpr int kMaxRanks = 8;
 constexpr int kGroupM = 16;
 constexpr int kCopyPiece = 32768;                       // bytes per bulk copy
-constexpr int kCopyBufs = kStages * kStageBytes / kCopyPiece;   // 6 pieces in flight per copy CTA
+constexpr int kCopyBufs = (kStages * kStageBytes + kEpiBytes) / kCopyPiece;   // 6 pieces in flight per copy CTA
+constexpr int kQueue = 4;                               // depth of the per-CTA tile queue
 
 enum Mode : int { kAllGather = 0, kReduceScatter = 1 };
 
@@ -64,6 +67,7 @@ struct Params {
   unsigned int* done_ptrs[kMaxRanks];    // done_ptrs[p][r]  : rank r no longer touches rank p's buffers for this call
   unsigned int epoch;
   unsigned int* local_cta_counter;       // local, zeroed by the host before launch
+  unsigned int* tile_counter;            // local, zeroed by the host before launch
   DeviceStatus* status;
 };
 
@@ -112,12 +116,14 @@ __device__ __forceinline__ bool wait_ge(const unsigned int* p, unsigned int want
 
 // Tile order: shard by shard (`first_shard`, then increasing modulo tp); inside a shard, groups of
 // kGroupM row-blocks sweep the column blocks so a wave of CTAs shares its panels through L2.
+// With `interleave` consecutive tiles rotate over the shards instead (reduce-scatter: the stores to the
+// peers are then spread over the whole kernel instead of bunched at its start).
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m_local, int tiles_n, int tp, int first_shard,
-                                            int& shard, int& tm, int& tn) {
+                                            bool interleave, int& shard, int& tm, int& tn) {
   const int per_shard = tiles_m_local * tiles_n;
-  const int s = tile / per_shard;
+  const int s = interleave ? tile % tp : tile / per_shard;
   shard = (first_shard + s) % tp;
-  const int within_shard = tile - s * per_shard;
+  const int within_shard = interleave ? tile / tp : tile - s * per_shard;
   const int group_span = kGroupM * tiles_n;
   const int group = within_shard / group_span;
   const int first_m = group * kGroupM;
@@ -142,6 +148,7 @@ __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, u
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all_but_latest() { asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); }
 
 // One copy CTA's share of the all-gather: thread 0 streams 32 KB pieces through a shared-memory ring.
 __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* bars, volatile uint32_t* abort_flag) {
@@ -155,9 +162,9 @@ __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* ba
   }
   uint32_t issued = 0, drained = 0;   // running counts over all shards (ring position / barrier phase)
   bool ok = true;
-  for (int s = 0; s < p.tp && ok; ++s) {
+  for (int s = 1; s < p.tp && ok; ++s) {      // the local shard was placed by the host before the launch
     const int shard = (p.rank + s) % p.tp;
-    if (shard != p.rank) ok = wait_ge(p.ready_ptrs[p.rank] + shard, p.epoch, true, abort_flag, p.status, 20);
+    ok = wait_ge(p.ready_ptrs[p.rank] + shard, p.epoch, true, abort_flag, p.status, 20);
     if (!ok) break;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(p.stage_ptrs[shard]);
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.gathered) + (long long)shard * shard_bytes;
@@ -204,38 +211,33 @@ __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* ba
   }
 }
 
+// Per-CTA tile queue: the TMA producer draws tile numbers from a grid-wide counter (so CTAs that spent
+// the first part of the kernel copying simply join in later) and hands them to the MMA and epilogue warps.
+struct TileQueue {
+  int tile[kQueue];
+};
+
 template <bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  if (smem_misaligned(smem, p.status, kCommGemm, reinterpret_cast<uint32_t*>(bars) + 60)) return;
-  uint64_t* full = bars;
-  uint64_t* empty = bars + kStages;
-  uint64_t* acc_full = bars + 2 * kStages;
-  uint64_t* acc_empty = acc_full + 2;
-  uint64_t* copy_bars = acc_empty + 2;                              // kCopyBufs
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(copy_bars + kCopyBufs);
+  uint8_t* epi_base = smem + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_base + kEpiBytes);
+  if (smem_misaligned(smem, p.status, kCommGemm, reinterpret_cast<uint32_t*>(bars) + 120)) return;
+  uint64_t* full = bars;                       // kStages
+  uint64_t* empty = full + kStages;            // kStages
+  uint64_t* acc_full = empty + kStages;        // 2
+  uint64_t* acc_empty = acc_full + 2;          // 2
+  uint64_t* copy_bars = acc_empty + 2;         // kCopyBufs
+  uint64_t* q_full = copy_bars + kCopyBufs;    // kQueue
+  uint64_t* q_empty = q_full + kQueue;         // kQueue
+  TileQueue* queue = reinterpret_cast<TileQueue*>(q_empty + kQueue);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(queue + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool is_copy_cta = p.mode == kAllGather && (int)blockIdx.x < p.copy_ctas;
-
-  if (is_copy_cta) {
-    if (threadIdx.x == 0) {
-      for (int i = 0; i < kCopyBufs; ++i) mbar_init(&copy_bars[i], 1);
-      *abort_flag = 0;
-      fence_barrier_init();
-    }
-    __syncthreads();
-    copy_cta_all_gather(p, smem, copy_bars, abort_flag);
-    return;
-  }
-
-  const int first_gemm_cta = p.mode == kAllGather ? p.copy_ctas : 0;
-  const int gemm_ctas = (int)gridDim.x - first_gemm_cta;
-  const int gemm_id = (int)blockIdx.x - first_gemm_cta;
   const int tiles_m_local = p.m_local / BM;
   const int tiles_n = (p.n + BN - 1) / BN;
   const int num_tiles = tiles_m_local * p.tp * tiles_n;
@@ -252,6 +254,11 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);
     }
+    for (int i = 0; i < kCopyBufs; ++i) mbar_init(&copy_bars[i], 1);
+    for (int i = 0; i < kQueue; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 5);      // MMA warp + four epilogue warps
+    }
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensor_map(&map_a);
@@ -266,15 +273,27 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (is_copy_cta) {
+    // phase 1 of a copy CTA: move remote shards (thread 0 drives the bulk copies), then compute like the rest
+    copy_cta_all_gather(p, smem, copy_bars, abort_flag);
+    __syncthreads();
+  }
+
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      int issued = 0, ready_shard = -1;
-      bool ok = true;
-      for (int tile = gemm_id; tile < num_tiles && ok; tile += gemm_ctas) {
+      int issued = 0, ready_shard = p.rank;
+      bool ok = *abort_flag == 0;
+      for (uint32_t qi = 0; ok; ++qi) {
+        const int slot = qi % kQueue;
+        if (!mbar_wait(&q_empty[slot], ((qi / kQueue) & 1) ^ 1, abort_flag, p.status, kCommGemm, 5)) { ok = false; break; }
+        const int tile = (int)atomicAdd(p.tile_counter, 1u);
+        queue->tile[slot] = tile < num_tiles ? tile : -1;
+        mbar_arrive(&q_full[slot]);
+        if (tile >= num_tiles) break;
         int shard, tm, tn;
-        tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, shard, tm, tn);
+        tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, p.mode == kReduceScatter, shard, tm, tn);
         if (p.mode == kAllGather && shard != ready_shard) {
           if (!wait_ge(p.shard_flags + shard, (unsigned)p.copy_ctas, false, abort_flag, p.status, 10)) { ok = false; break; }
           fence_proxy_async_all();      // copied rows were written through the async proxy of other CTAs
@@ -313,11 +332,16 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr uint32_t idesc = make_idesc(BM, BN, 1, false, B_MN);
     int stage = 0;
     uint32_t phase = 0;
-    int iter = 0;
     bool ok = true;
-    for (int tile = gemm_id; tile < num_tiles && ok; tile += gemm_ctas, ++iter) {
-      const int buf = iter & 1;
-      const uint32_t use = (uint32_t)(iter >> 1);
+    for (uint32_t qi = 0; ok; ++qi) {
+      const int slot = qi % kQueue;
+      if (!mbar_wait(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 6)) break;
+      const int tile = queue->tile[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_empty[slot]);
+      if (tile < 0) break;
+      const int buf = qi & 1;
+      const uint32_t use = qi >> 1;
       if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, kCommGemm, 2)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
@@ -343,59 +367,69 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else {
     const int quarter = warp & 3;
-    int iter = 0;
+    uint8_t* my_row = epi_base + (quarter * 32 + lane) * kEpiRowPitch;    // this lane's staged output row
     bool ok = true;
-    for (int tile = gemm_id; tile < num_tiles && ok; tile += gemm_ctas, ++iter) {
-      const int buf = iter & 1;
-      const uint32_t use = (uint32_t)(iter >> 1);
+    int pending_shard = -1;          // reduce-scatter: tile whose bulk stores are in flight and not yet announced
+    auto announce = [&](int shard_done) {
+      __syncwarp();                  // every lane's rows of that tile are complete in (peer) memory
+      if (shard_done >= 0 && lane == 0) red_release_sys_add(p.counter_ptrs[shard_done] + p.rank, 1u);
+    };
+    for (uint32_t qi = 0; ok; ++qi) {
+      const int slot = qi % kQueue;
+      if (!mbar_wait(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 7)) break;
+      const int tile = queue->tile[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_empty[slot]);
+      if (tile < 0) break;
+      const int buf = qi & 1;
+      const uint32_t use = qi >> 1;
       int shard, tm, tn;
-      tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, shard, tm, tn);
+      tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, p.mode == kReduceScatter, shard, tm, tn);
       if (!mbar_wait(&acc_full[buf], use & 1, abort_flag, p.status, kCommGemm, 4)) { ok = false; break; }
       tc_fence_after_sync();
-      const int row = tm * BM + quarter * 32 + lane;
-      const int col0 = tn * BN;
+      bulk_wait_read_all();          // the previous tile's store has read this lane's staging row
       const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
-      __nv_bfloat16* dst_row;
-      if (p.mode == kAllGather) {
-        dst_row = reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row * p.ldc;
-      } else {
-        // partial sums of shard `shard` go to that rank's receive buffer, slot = this rank
-        dst_row = reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[shard]) +
-                  ((long long)p.rank * p.m_local + (row - shard * p.m_local)) * p.n;
-      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + (uint32_t)c, v);
         tc_wait_ld();
-        const int col = col0 + c;
-        if (col >= p.n) continue;
-        const int valid = min(32, p.n - col);
-        __nv_bfloat16* dst = dst_row + col;
-        if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 q;
-            q.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-            q.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-            q.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-            q.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-            reinterpret_cast<uint4*>(dst)[j] = q;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid) dst[j] = __float2bfloat16(__uint_as_float(v[j]));
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+          q.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+          q.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+          q.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+          *reinterpret_cast<uint4*>(my_row + c * 2 + j * 16) = q;
         }
       }
+      // the accumulator is in shared memory now: hand the TMEM buffer back before the stores
       tc_fence_before_sync();
-      if (p.mode == kReduceScatter) __threadfence_system();   // partial tile visible to its owner before the count
+      fence_proxy_async_smem();      // the bulk store below reads this row through the async proxy
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&acc_empty[buf]);
-        if (p.mode == kReduceScatter) red_release_sys_add(p.counter_ptrs[shard] + p.rank, 1u);
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      // one bulk store per row: up to 512 contiguous bytes leave the SM without passing through registers
+      const int row = tm * BM + quarter * 32 + lane;
+      const int col0 = tn * BN;
+      const int bytes = min(BN, p.n - col0) * 2;
+      __nv_bfloat16* dst;
+      if (p.mode == kAllGather) {
+        dst = reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row * p.ldc + col0;
+      } else {
+        // partial sums of shard `shard` go to that rank's receive buffer, slot = this rank
+        dst = reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[shard]) +
+              ((long long)p.rank * p.m_local + (row - shard * p.m_local)) * p.n + col0;
       }
+      if (bytes > 0) bulk_s2g(dst, my_row, (uint32_t)bytes);
+      bulk_commit();
+      // the previous tile had a whole tile time to land: wait for it (not for the one just issued) and announce it
+      bulk_wait_all_but_latest();
+      announce(pending_shard);
+      pending_shard = p.mode == kReduceScatter ? shard : -1;
     }
+    bulk_wait_all();
+    announce(pending_shard);
   }
 
   tc_fence_before_sync();
@@ -407,15 +441,15 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (p.mode == kReduceScatter) {
     // ---- sum the tp partial copies of the rows this rank owns (fp32) into the local output
-    __shared__ int arrived;
+    int* arrived = reinterpret_cast<int*>(epi_base);
     if (threadIdx.x == 0) {
       bool ok = *abort_flag == 0;
       for (int r = 0; r < p.tp && ok; ++r)
         ok = wait_ge(p.counter_ptrs[p.rank] + r, p.expected_count, true, nullptr, p.status, 30);
-      arrived = ok ? 1 : 0;
+      *arrived = ok ? 1 : 0;
     }
     __syncthreads();
-    if (arrived) {
+    if (*arrived) {
       const long long vec_total = (long long)p.m_local * p.n / 8;
       const uint4* base = reinterpret_cast<const uint4*>(p.recv_ptrs[p.rank]);
       uint4* out = reinterpret_cast<uint4*>(p.out_local);
@@ -498,6 +532,7 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   p.gathered = a.gathered;
   p.shard_flags = a.shard_flags;
   p.local_cta_counter = a.shard_flags + 8;
+  p.tile_counter = a.shard_flags + 9;
   p.expected_count = a.expected_count;
   p.out_local = a.out;
   p.ldc = a.ldc;
@@ -521,7 +556,7 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   }
   // every CTA of this kernel must be resident at once (copy CTAs feed compute CTAs): one CTA per SM
   const int grid = sm_count();
-  AJB_REQUIRE(p.copy_ctas < grid, "comm_gemm: too many copy CTAs");
+  AJB_REQUIRE(p.copy_ctas < grid && (a.mode != kAllGather || p.copy_ctas >= 1), "comm_gemm: copy CTA count %d is out of range", p.copy_ctas);
   if (which) comm_gemm_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
   else       comm_gemm_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
   AJB_CUDA_OK(cudaGetLastError());

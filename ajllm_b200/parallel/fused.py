@@ -51,7 +51,7 @@ class FusedTensorParallel:
         self.rank = dist.get_rank(group)
         if not 2 <= self.size <= _MAX_RANKS:
             raise ValueError("fused tensor parallelism supports 2..8 ranks")
-        self.copy_ctas = int(copy_ctas or os.environ.get("AJB_COPY_CTAS", "16"))
+        self.copy_ctas = int(copy_ctas or os.environ.get("AJB_COPY_CTAS", "20"))
         self.epoch = 0
         self.expected_count = 0
         self._stage = self._recv = None
@@ -122,6 +122,7 @@ class FusedTensorParallel:
         stage = self._stage[: m_local * k * 2].view(torch.bfloat16).view(m_local, k)
         stage.copy_(x_local)
         gathered = torch.empty(m, k, dtype=torch.bfloat16, device=self.device)
+        gathered[self.rank * m_local:(self.rank + 1) * m_local].copy_(x_local)   # the kernel moves only remote shards
         out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
         self._launch(MODE_ALL_GATHER, m, n, k, weight, b_mn, out, gathered=gathered)
         return gathered, out
