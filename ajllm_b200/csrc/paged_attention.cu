@@ -1,0 +1,353 @@
+// Paged-KV attention for decoding and speculative verification on sm_100a.
+//
+// One CTA serves one (sequence, KV head): the `group * q_len` query rows that share this KV head
+// (group = Hq / Hkv query heads, q_len new tokens: 1 for plain decoding, k + 1 when verifying k draft
+// tokens) form the top rows of a 128-row tcgen05 tile, so every K/V byte of the sequence is read once
+// for all of them. K/V tiles of 128 tokens are assembled from the sequence's 16-token cache blocks by
+// TMA (one box per block, addressed through the block table); S = Q K^T and O += P V run on the tensor
+// cores with accumulators in tensor memory, exactly as in the training forward kernel, but only the
+// softmax warps whose 32-row quarter holds real rows do any work. Row (head h, new token i) may see
+// keys 0 .. context_len - q_len + i.
+//
+// Layouts: q [tokens, Hq, hd] bf16 (rows of a sequence are contiguous, `q_start[seq]` is its first
+// row); caches [num_blocks, block_size = 16, Hkv, hd] bf16; block_tables [num_seqs, max_blocks] int32;
+// out like q.
+#include "common.cuh"
+
+namespace ajb {
+namespace paged {
+
+constexpr int TILE = 128;          // keys per step
+constexpr int BLOCK_TOKENS = 16;   // tokens per cache block
+constexpr int kThreads = 192;
+constexpr int kMaxRows = 64;       // group * q_len
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kPagedKernelId = 5;
+
+template <int HD>
+struct Cfg {
+  static constexpr int kTile = TILE * HD * 2;
+  static constexpr int kP = TILE * TILE * 2;
+  static constexpr int kSmem = kTile /*Q*/ + 4 * kTile /*2 x (K,V)*/ + kP + 256;
+  static constexpr int kOCol = 256;
+};
+
+struct Params {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  const int* block_tables;
+  const int* context_lens;
+  const int* q_start;
+  int max_blocks;
+  int heads, kv_heads, q_len;
+  float scale;
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ void store_chunk(uint8_t* tile, int row, int ch, uint4 val) {
+  uint8_t* dst = tile + (ch >> 3) * (TILE * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+  *reinterpret_cast<uint4*>(dst) = val;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const Params p) {
+  using C = Cfg<HD>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + C::kTile;
+  uint8_t* sP = sKV + 4 * C::kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kP);
+  if (smem_misaligned(smem, p.status, kPagedKernelId, reinterpret_cast<uint32_t*>(bars) + 60)) return;
+  uint64_t* kv_full = bars;        // 2
+  uint64_t* kv_empty = bars + 2;   // 2
+  uint64_t* s_full = bars + 4;     // 2
+  uint64_t* s_free = bars + 6;     // 2
+  uint64_t* p_ready = bars + 8;    // 1
+  uint64_t* pv_done = bars + 9;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.x, kv_head = blockIdx.y;
+  const int group = p.heads / p.kv_heads;
+  const int rows = group * p.q_len;                 // real rows, packed head-major: row = h_in_group * q_len + i
+  const int ctx = p.context_lens[seq];
+  const int n_tiles = (ctx + TILE - 1) / TILE;
+  const int active_quarters = (rows + 31) / 32;
+  const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
+    }
+    mbar_init(p_ready, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensor_map(&map_k);
+    prefetch_tensor_map(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  // stage Q: rows beyond `rows` are zero (their scores are never used)
+  if (warp >= 2) {
+    const int t = threadIdx.x - 64;                 // 0..127 == tile row
+    const bool real = t < rows;
+    const int h = real ? t / p.q_len : 0, i = real ? t % p.q_len : 0;
+    const __nv_bfloat16* src = p.q + ((size_t)(p.q_start[seq] + i) * p.heads + kv_head * group + h) * HD;
+#pragma unroll
+    for (int ch = 0; ch < HD / 8; ++ch) {
+      const uint4 v = real ? reinterpret_cast<const uint4*>(src)[ch] : make_uint4(0, 0, 0, 0);
+      store_chunk(sQ, t, ch, v);
+    }
+    fence_proxy_async_smem();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], (((uint32_t)j >> 1) & 1) ^ 1, abort_flag, p.status, kPagedKernelId, 1)) break;
+        uint8_t* sK = sKV + s * 2 * C::kTile;
+        uint8_t* sV = sK + C::kTile;
+        mbar_arrive_expect_tx(&kv_full[s], 2 * C::kTile);
+        const int first_block = j * (TILE / BLOCK_TOKENS);
+        const int blocks_here = min(TILE / BLOCK_TOKENS, (ctx + BLOCK_TOKENS - 1) / BLOCK_TOKENS - first_block);
+#pragma unroll 1
+        for (int b = 0; b < TILE / BLOCK_TOKENS; ++b) {
+          // blocks past the end of the sequence re-read the last valid block (masked later); keeps the byte count fixed
+          const int id = table[first_block + min(b, blocks_here - 1)];
+#pragma unroll
+          for (int i = 0; i < HD / 64; ++i) {
+            tma_load_3d(sK + i * (TILE * 128) + b * (BLOCK_TOKENS * 128), &map_k, &kv_full[s], kv_head * HD + 64 * i, 0, id);
+            tma_load_3d(sV + i * (TILE * 128) + b * (BLOCK_TOKENS * 128), &map_v, &kv_full[s], kv_head * HD + 64 * i, 0, id);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc_s = make_idesc(TILE, TILE, 1, false, false);
+    constexpr uint32_t idesc_o = make_idesc(TILE, HD, 1, false, true);
+    const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+    bool ok = true;
+    auto issue_s = [&](int j) -> bool {
+      const int s = j & 1;
+      const uint32_t use = (uint32_t)j >> 1;
+      if (!mbar_wait(&kv_full[s], use & 1, abort_flag, p.status, kPagedKernelId, 3)) return false;
+      if (!mbar_wait(&s_free[s], (use & 1) ^ 1, abort_flag, p.status, kPagedKernelId, 4)) return false;
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t aK = smem_u32(sKV + s * 2 * C::kTile);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t box = (uint32_t)(k / 4) * (TILE * 128), off = (uint32_t)(k % 4) * 32;
+          umma_f16(tmem_base + (uint32_t)(s * TILE), desc_k_major(aQ + box, off), desc_k_major(aK + box, off), idesc_s, k != 0);
+        }
+        tc_commit(&s_full[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (n_tiles > 0) ok = issue_s(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) {
+        ok = issue_s(j + 1);
+        if (!ok) break;
+      }
+      if (!mbar_wait(p_ready, (uint32_t)j & 1, abort_flag, p.status, kPagedKernelId, 5)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t aV = smem_u32(sKV + (j & 1) * 2 * C::kTile + C::kTile);
+#pragma unroll
+        for (int k = 0; k < TILE / 16; ++k) {
+          const uint32_t pbox = (uint32_t)(k / 4) * (TILE * 128), poff = (uint32_t)(k % 4) * 32;
+          umma_f16(tmem_base + C::kOCol, desc_k_major(aP + pbox, poff), desc_mn_major(aV, TILE * 128, k * 16), idesc_o,
+                   (j | k) != 0);
+        }
+        tc_commit(pv_done);
+        tc_commit(&kv_empty[j & 1]);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const bool active = quarter < active_quarters;     // warp-uniform
+    const bool real = row < rows;
+    const int h = real ? row / p.q_len : 0, qi = real ? row % p.q_len : 0;
+    const int k_max = real ? ctx - p.q_len + qi : -1;   // last visible key
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float sl = p.scale * kLog2e;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kPagedKernelId, 6)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int k0 = j * TILE;
+      uint32_t pk[64];
+      float alpha = 1.0f;
+      bool moved = false;
+      if (active) {
+        uint32_t sv[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * TILE + c * 32), sv[c]);
+        tc_wait_ld();
+        float m_tile = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(sv[c][i]);
+            if (k0 + c * 32 + i > k_max) x = -INFINITY;
+            sv[c][i] = __float_as_uint(x);
+            m_tile = fmaxf(m_tile, x);
+          }
+        }
+        const float m_new = fmaxf(m_run, m_tile);
+        const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+        alpha = exp2f((m_run - m_safe) * sl);
+        const float neg = -m_safe * sl;
+        float l_tile = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[c][i]), sl, neg));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), sl, neg));
+            const __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
+            const float2 back = __bfloat1622float2(hb);
+            l_tile += back.x + back.y;
+            pk[c * 16 + i / 2] = *reinterpret_cast<const uint32_t*>(&hb);
+          }
+        }
+        l_run = l_run * alpha + l_tile;
+        moved = m_new != m_run;
+        m_run = m_new;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) pk[i] = 0u;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[s]);
+      if (j > 0 && !mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kPagedKernelId, 7)) { ok = false; break; }
+      tc_fence_after_sync();
+      // inactive quarters write their (zero) rows only once: they never change
+      if (active || j == 0) {
+#pragma unroll
+        for (int ch = 0; ch < 16; ++ch) store_chunk(sP, row, ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
+      }
+      if (active && j > 0 && __any_sync(0xffffffffu, moved)) {
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::kOCol + c * 32), ov);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::kOCol + c * 32), ov);
+        }
+        tc_wait_st();
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    if (ok && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
+      tc_fence_after_sync();
+      if (active) {
+        const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        __nv_bfloat16* dst = p.out + ((size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::kOCol + c * 32), ov);
+          tc_wait_ld();
+          if (real) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 q;
+              q.x = pack_bf16x2(__uint_as_float(ov[8 * i]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
+              q.y = pack_bf16x2(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
+              q.z = pack_bf16x2(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
+              q.w = pack_bf16x2(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
+              reinterpret_cast<uint4*>(dst + c * 32)[i] = q;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int HD>
+static int launch(const void* q, const void* k_cache, const void* v_cache, const void* block_tables,
+                  const void* context_lens, const void* q_start, void* out, int num_seqs, int num_blocks, int max_blocks,
+                  int heads, int kv_heads, int q_len, float scale, cudaStream_t stream) {
+  using C = Cfg<HD>;
+  CUtensorMap map_k, map_v;
+  const uint64_t row_pitch = (uint64_t)kv_heads * HD * 2;
+  int rc = make_tensor_map_3d(&map_k, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, num_blocks, BLOCK_TOKENS,
+                              (uint64_t)kv_heads * HD, row_pitch * BLOCK_TOKENS, row_pitch, BLOCK_TOKENS, 64);
+  if (rc) return rc;
+  rc = make_tensor_map_3d(&map_v, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, num_blocks, BLOCK_TOKENS,
+                          (uint64_t)kv_heads * HD, row_pitch * BLOCK_TOKENS, row_pitch, BLOCK_TOKENS, 64);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    configured = true;
+  }
+  Params p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_tables = (const int*)block_tables;
+  p.context_lens = (const int*)context_lens; p.q_start = (const int*)q_start; p.max_blocks = max_blocks;
+  p.heads = heads; p.kv_heads = kv_heads; p.q_len = q_len; p.scale = scale; p.status = device_status_buffer();
+  paged_attention_kernel<HD><<<dim3(num_seqs, kv_heads), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace paged
+}  // namespace ajb
+
+// Every sequence of the launch contributes exactly q_len new rows; (heads / kv_heads) * q_len <= 64.
+extern "C" int ajb_paged_attention(const void* q, const void* k_cache, const void* v_cache, const void* block_tables,
+                                   const void* context_lens, const void* q_start, void* out, int num_seqs,
+                                   int num_blocks, int block_size, int max_blocks, int heads, int kv_heads,
+                                   int head_dim, int q_len, float scale, void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(block_size == paged::BLOCK_TOKENS, "paged attention: cache block size must be %d", paged::BLOCK_TOKENS);
+  AJB_REQUIRE(heads % kv_heads == 0 && (heads / kv_heads) * q_len <= paged::kMaxRows && q_len >= 1,
+              "paged attention: (heads / kv_heads) * q_len = %d exceeds %d", (heads / kv_heads) * q_len, paged::kMaxRows);
+  if (num_seqs <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (head_dim == 128)
+    return paged::launch<128>(q, k_cache, v_cache, block_tables, context_lens, q_start, out, num_seqs, num_blocks,
+                              max_blocks, heads, kv_heads, q_len, scale, s);
+  if (head_dim == 64)
+    return paged::launch<64>(q, k_cache, v_cache, block_tables, context_lens, q_start, out, num_seqs, num_blocks,
+                             max_blocks, heads, kv_heads, q_len, scale, s);
+  set_error("paged attention: head_dim %d is not supported (64 and 128 are)", head_dim);
+  return 2;
+}

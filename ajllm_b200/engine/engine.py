@@ -79,6 +79,7 @@ class LLMEngine:
         self.stats = EngineStats()
         self.seed = seed
         self._generators: dict[int, torch.Generator] = {}
+        self._draws: dict[int, int] = {}
         self._finished: list[Sequence] = []
 
     # ---------------------------------------------------------------- requests
@@ -98,6 +99,32 @@ class LLMEngine:
         p = seq.params
         token = sample_next_token(logits_row[None].cpu(), p.temperature, p.top_p, self._generators[seq.request_id])
         return int(token[0, 0])
+
+    def _sample_rows(self, seqs: list[Sequence], logits: torch.Tensor) -> list[int]:
+        """One token per row of ``logits``. On the CPU every request draws from its own generator (results
+        do not depend on batch composition); on a GPU the whole batch is sampled on the device and read
+        back once, greedy rows by argmax and the rest from one device generator."""
+        if not seqs:
+            return []
+        if logits.device.type != "cuda":
+            return [self._sample(seq, logits[i]) for i, seq in enumerate(seqs)]
+        from ajllm_b200.ops import serving
+        temps, top_ps, seeds, counters = self._device_sampling_state(seqs, logits.device, draws=1)
+        return serving.sample_rows(logits.float(), temps, top_ps, seeds, counters).tolist()
+
+    def _device_sampling_state(self, seqs: list[Sequence], device, draws: int):
+        """Per-row temperature / top-p / (seed, counter) tensors; advances each request's draw counter."""
+        temps = torch.tensor([s.params.temperature for s in seqs], dtype=torch.float32, device=device)
+        top_ps = torch.tensor([(s.params.top_p if s.params.top_p is not None else 1.0) for s in seqs],
+                              dtype=torch.float32, device=device)
+        seeds, counters = [], []
+        for s in seqs:
+            seed = s.params.seed if s.params.seed is not None else self.seed * 1_000_003 + s.request_id
+            seeds.append(seed & 0x7FFFFFFFFFFFFFFF)
+            counters.append(self._draws.get(s.request_id, 0))
+            self._draws[s.request_id] = counters[-1] + draws
+        return (temps, top_ps, torch.tensor(seeds, dtype=torch.int64, device=device),
+                torch.tensor(counters, dtype=torch.int64, device=device))
 
     def _emit(self, seq: Sequence, token: int, now: float) -> bool:
         """Append a generated token; returns True when the sequence finished."""
@@ -122,6 +149,7 @@ class LLMEngine:
         if self.draft_runner is not None:
             self.draft_cache.free(seq.request_id)
         self._generators.pop(seq.request_id, None)
+        self._draws.pop(seq.request_id, None)
         self._finished.append(seq)
 
     def _sync_preempted(self) -> None:
@@ -157,6 +185,8 @@ class LLMEngine:
                 # keep the draft cache in step with the target for prompt tokens
                 self.draft_runner.forward([RunItem(i.seq_id, i.token_ids, 0) for i in items])
             now = time.perf_counter()
+            sampling = [item.seq for item in owners if item.samples]
+            tokens = self._sample_rows(sampling, logits)
             row = 0
             for item in owners:
                 seq = item.seq
@@ -164,13 +194,62 @@ class LLMEngine:
                 if item.is_prefill:
                     self.stats.prompt_tokens += item.num_new_tokens
                 if item.samples:
-                    self._emit(seq, self._sample(seq, logits[row]), now)
+                    self._emit(seq, tokens[row], now)
                     row += 1
         self.stats.steps += 1
         self.stats.busy_seconds += time.perf_counter() - tick
         return [self._to_output(seq) for seq in self._finished[done_before:]]
 
+    def _speculative_decode_gpu(self, decode: list[ScheduledSeq]) -> None:
+        """Same step with logits kept on the device: the sampler kernel proposes, the verify kernel decides,
+        and only the proposed tokens and the (accepted, next) pairs are read back."""
+        from ajllm_b200.ops import serving
+
+        k = self.k
+        seqs = [item.seq for item in decode]
+        device = next(self.model.parameters()).device
+        drafts: list[list[int]] = [[] for _ in seqs]
+        draft_logits = []
+        for _ in range(k):
+            items = []
+            for seq, proposed in zip(seqs, drafts):
+                have = self.draft_cache.length(seq.request_id)
+                items.append(RunItem(seq.request_id, (seq.tokens + proposed)[have:], 1))
+            logits = self.draft_runner.forward(items).float()
+            temps, top_ps, seeds, counters = self._device_sampling_state(seqs, device, draws=1)
+            top_ps.fill_(1.0)          # the accept rule below compares plain softmax distributions
+            tokens = serving.sample_rows(logits, temps, top_ps, seeds, counters)
+            draft_logits.append(logits)
+            for row, token in enumerate(tokens.tolist()):
+                drafts[row].append(token)
+        items = [RunItem(seq.request_id, seq.tokens[seq.computed:] + proposed, k + 1) for seq, proposed in zip(seqs, drafts)]
+        target = self.runner.forward(items).float().view(len(seqs), k + 1, -1)
+        temps, _, seeds, counters = self._device_sampling_state(seqs, device, draws=2 * k + 1)
+        verdict = serving.spec_verify(target, torch.stack(draft_logits, dim=1),
+                                      torch.tensor(drafts, dtype=torch.int32, device=device), temps, seeds,
+                                      counters).tolist()
+        now = time.perf_counter()
+        for row, seq in enumerate(seqs):
+            accepted, next_token = verdict[row]
+            self._apply_verdict(seq, drafts[row], accepted, next_token, now)
+
+    def _apply_verdict(self, seq: Sequence, proposed: list[int], accepted: int, next_token: int, now: float) -> None:
+        k = self.k
+        self.stats.draft_proposed += k
+        self.stats.draft_accepted += accepted
+        base = seq.total_len          # tokens known before this step
+        for token in proposed[:accepted] + [next_token]:
+            if self._emit(seq, token, now):
+                return
+        # keep K/V of the old tokens and of the accepted drafts; the new last token is fed next step
+        self.cache.truncate(seq.request_id, base + accepted)
+        self.draft_cache.truncate(seq.request_id, min(self.draft_cache.length(seq.request_id), base + accepted))
+        seq.computed = self.cache.length(seq.request_id)
+
     def _speculative_decode(self, decode: list[ScheduledSeq]) -> None:
+        if next(self.model.parameters()).is_cuda and all(
+                item.seq.params.temperature <= 0 or item.seq.params.top_p in (None, 1.0) for item in decode):
+            return self._speculative_decode_gpu(decode)
         k = self.k
         seqs = [item.seq for item in decode]
         drafts: list[list[int]] = [[] for _ in seqs]
@@ -208,20 +287,7 @@ class LLMEngine:
                 target = sampling_probabilities(block, p.temperature, p.top_p)
                 accepted, next_token = verify_rejection(proposal, torch.stack(draft_probs[row]), target,
                                                         self._generators[seq.request_id])
-            self.stats.draft_proposed += k
-            self.stats.draft_accepted += accepted
-            base = seq.total_len          # tokens known before this step
-            finished = False
-            for token in drafts[row][:accepted] + [next_token]:
-                if self._emit(seq, token, now):
-                    finished = True
-                    break
-            if finished:
-                continue
-            # keep K/V of the old tokens and of the accepted drafts; the new last token is fed next step
-            self.cache.truncate(seq.request_id, base + accepted)
-            self.draft_cache.truncate(seq.request_id, min(self.draft_cache.length(seq.request_id), base + accepted))
-            seq.computed = self.cache.length(seq.request_id)
+            self._apply_verdict(seq, drafts[row], accepted, next_token, now)
 
     # ---------------------------------------------------------------- batch API
     def _to_output(self, seq: Sequence) -> RequestOutput:

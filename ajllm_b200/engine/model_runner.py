@@ -93,6 +93,26 @@ class ModelRunner:
         ctx_t = torch.tensor(ctx_lens, dtype=torch.int32, device=dev)
         qlen_t = torch.tensor(q_lens, dtype=torch.int32, device=dev)
 
+        on_gpu = dev.type == "cuda" and self.dtype == torch.bfloat16
+        if on_gpu:
+            from ajllm_b200.ops import serving
+            pos32 = pos.to(torch.int32)
+            # split the batch: long prompts with nothing cached use the training flash kernel, the rest is paged
+            fresh, cached_idx, cached_qlens, cached_ctx, cached_items = [], [], [], [], []
+            cursor = 0
+            for i, (n, ctx) in enumerate(zip(q_lens, ctx_lens)):
+                if n == ctx and n > 16:
+                    fresh.append((cursor, cursor + n))
+                else:
+                    cached_idx.extend(range(cursor, cursor + n))
+                    cached_qlens.append(n)
+                    cached_ctx.append(ctx)
+                    cached_items.append(i)
+                cursor += n
+            cached_rows = cached_tables = None
+            if cached_idx:
+                cached_rows = torch.tensor(cached_idx, dtype=torch.long, device=dev)
+                cached_tables = tables.index_select(0, torch.tensor(cached_items, dtype=torch.long, device=dev)).contiguous()
         stream = model.token_embeddings(ids)
         if model.position_embeddings is not None:
             stream = stream + model.position_embeddings(pos)
@@ -101,13 +121,27 @@ class ModelRunner:
             attn = layer.attention
             stream, normed = layer.norm1.add_and_norm(stream, pending)
             qkv = _matmul(normed, w["qkv"])
-            q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
-            if attn.use_rope:
-                q = reference.rope_interleaved(q, attn.rope_cos, attn.rope_sin, pos)
-                k = reference.rope_interleaved(k, attn.rope_cos, attn.rope_sin, pos)
-            cache.write(index, slot_t, k, v)
-            attended = ops.paged_attention_ragged(q, cache.keys[index], cache.values[index], tables, ctx_t, qlen_t,
-                                                  q_lens, ctx_lens)
+            if on_gpu:
+                if attn.use_rope:
+                    serving.rope_packed_(qkv, attn.rope_cos, attn.rope_sin, pos32, attn.num_heads, attn.num_kv_heads,
+                                         attn.head_dim)
+                q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
+                cache.write(index, slot_t, k, v)
+                attended = torch.empty(ids.shape[0], attn.num_heads * attn.head_dim, dtype=qkv.dtype, device=dev)
+                for lo, hi in fresh:          # prompts starting from an empty cache: tiled kernel on the packed rows
+                    attended[lo:hi] = serving.prompt_attention(qkv[lo:hi], attn.num_heads, attn.num_kv_heads, attn.head_dim)
+                if cached_rows is not None:
+                    part = serving.paged_attention(q.index_select(0, cached_rows).contiguous(), cache.keys[index],
+                                                   cache.values[index], cached_tables, None, None, cached_qlens, cached_ctx)
+                    attended.index_copy_(0, cached_rows, part.reshape(part.shape[0], -1))
+            else:
+                q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
+                if attn.use_rope:
+                    q = reference.rope_interleaved(q, attn.rope_cos, attn.rope_sin, pos)
+                    k = reference.rope_interleaved(k, attn.rope_cos, attn.rope_sin, pos)
+                cache.write(index, slot_t, k, v)
+                attended = ops.paged_attention_ragged(q, cache.keys[index], cache.values[index], tables, ctx_t, qlen_t,
+                                                      q_lens, ctx_lens)
             attended = self._reduce(_matmul(attended.reshape(ids.shape[0], -1), w["out"]))
             stream, normed = layer.norm2.add_and_norm(stream, attended)
             if "moe" in w:

@@ -1,0 +1,30 @@
+"""GPU side of the block-scaled fp8 path: per-token activation quantisation and the fp8 GEMM."""
+
+from __future__ import annotations
+
+import torch
+
+from ajllm_b200.ops import native
+
+BLOCK = 128
+
+
+def quantize_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 ``[rows, cols]`` -> (e4m3 ``[rows, cols]``, fp32 scales ``[rows, ceil(cols / 128)]``)."""
+    rows, cols = x.shape
+    x = x.contiguous()
+    q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty(rows, (cols + BLOCK - 1) // BLOCK, dtype=torch.float32, device=x.device)
+    native.call("ajb_fp8_quantize_rows", x.data_ptr(), q.data_ptr(), scales.data_ptr(), rows, cols, native.stream_ptr())
+    return q, scales
+
+
+def fp8_block_gemm(x: torch.Tensor, weight) -> torch.Tensor:
+    """``x @ W.T`` with ``x`` quantised on the fly; ``weight`` is an ``engine.quant.Fp8Weight``."""
+    xq, sx = quantize_rows(x.to(torch.bfloat16))
+    rows, k = xq.shape
+    out = torch.empty(rows, weight.out_features, dtype=torch.bfloat16, device=x.device)
+    native.call("ajb_fp8_block_gemm", xq.data_ptr(), weight.q.data_ptr(), sx.data_ptr(), weight.scale.data_ptr(),
+                out.data_ptr(), rows, weight.out_features, k, xq.stride(0), weight.q.stride(0), out.stride(0),
+                native.stream_ptr())
+    return out.to(x.dtype)

@@ -42,6 +42,11 @@ _SIGNATURES: dict[str, list] = {
                        c_float, c_void, c_float, c_void],
     "ajb_add_bf16": [c_void, c_void, c_void, c_long, c_void],
     "ajb_flash_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_float, c_void],
+    "ajb_fp8_quantize_rows": [c_void, c_void, c_void, c_int, c_int, c_void],
+    "ajb_fp8_block_gemm": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_void],
+    "ajb_sample_rows": [c_void, c_long, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void],
+    "ajb_spec_verify": [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void],
+    "ajb_paged_attention": [c_void] * 7 + [c_int] * 8 + [c_float, c_void],
     "ajb_flash_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
                       c_long, c_int, c_float, c_void],
 }

@@ -1,0 +1,89 @@
+"""GPU entry points of the serving path: in-place RoPE on packed rows with explicit positions, paged
+attention for decode / verify rows, the training flash kernel for prompts that start from an empty
+cache, and the batched sampler."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ajllm_b200.ops import native
+
+_MAX_ROWS = 64
+
+
+def rope_packed_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor, num_heads: int,
+                 num_kv_heads: int, head_dim: int) -> None:
+    """Rotate the q and k heads of packed ``[tokens, (Hq + 2 Hkv) * hd]`` rows in place at ``positions``."""
+    native.call("ajb_rope_qk", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), qkv.shape[0], 1,
+                num_heads, num_kv_heads, head_dim, qkv.stride(0), 0, native.stream_ptr())
+
+
+def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, block_tables: torch.Tensor,
+                    context_lens: torch.Tensor, q_lens: torch.Tensor, q_lens_host: list[int],
+                    context_lens_host: list[int]) -> torch.Tensor:
+    """Ragged decode / verify attention. ``q`` is ``[total_rows, Hq, hd]``; launches are grouped by the
+    number of new rows per sequence, and long row runs are cut into chunks the kernel can hold."""
+    total, heads, head_dim = q.shape
+    kv_heads = key_cache.shape[2]
+    group = heads // kv_heads
+    max_q = max(1, _MAX_ROWS // group)
+    out = torch.empty_like(q)
+    # (q_len class) -> lists of (table row, q_start, effective context)
+    classes: dict[int, list[tuple[int, int, int]]] = {}
+    cursor = 0
+    for i, (n, ctx) in enumerate(zip(q_lens_host, context_lens_host)):
+        for a in range(0, n, max_q):
+            b = min(n, a + max_q)
+            classes.setdefault(b - a, []).append((i, cursor + a, ctx - (n - b)))
+        cursor += n
+    scale = 1.0 / math.sqrt(head_dim)
+    num_blocks, block_size = key_cache.shape[0], key_cache.shape[1]
+    for q_len, items in classes.items():
+        rows = torch.tensor([it[0] for it in items], dtype=torch.long, device=q.device)
+        tables = block_tables.index_select(0, rows).contiguous() if len(items) != block_tables.shape[0] or \
+            [it[0] for it in items] != list(range(block_tables.shape[0])) else block_tables
+        starts = torch.tensor([it[1] for it in items], dtype=torch.int32, device=q.device)
+        ctxs = torch.tensor([it[2] for it in items], dtype=torch.int32, device=q.device)
+        native.call("ajb_paged_attention", q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), tables.data_ptr(),
+                    ctxs.data_ptr(), starts.data_ptr(), out.data_ptr(), len(items), num_blocks, block_size,
+                    tables.shape[1], heads, kv_heads, head_dim, q_len, scale, native.stream_ptr())
+    return out
+
+
+def prompt_attention(qkv_rows: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Causal attention of one prompt that starts from an empty cache, read in place from its packed
+    (already rotated) ``[T, (Hq + 2 Hkv) * hd]`` rows. Returns ``[T, Hq * hd]``."""
+    T, width = qkv_rows.shape
+    out = torch.empty(T, num_heads * head_dim, dtype=torch.bfloat16, device=qkv_rows.device)
+    lse = torch.empty(num_heads, T, dtype=torch.float32, device=qkv_rows.device)
+    native.call("ajb_flash_fwd", qkv_rows.data_ptr(), out.data_ptr(), lse.data_ptr(), 1, T, num_heads, num_kv_heads,
+                head_dim, qkv_rows.stride(0), 1, 1.0 / math.sqrt(head_dim), native.stream_ptr())
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seeds: torch.Tensor,
+                counters: torch.Tensor) -> torch.Tensor:
+    """One token per row of fp32 ``logits`` ``[rows, vocab]``; per-row temperature (``<= 0`` = greedy),
+    top-p, and a counter-based random stream ``(seed, counter)``. Returns int32 ``[rows]`` on the device."""
+    logits = logits.contiguous()
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    native.call("ajb_sample_rows", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1],
+                temperature.data_ptr(), top_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(), out.data_ptr(),
+                native.stream_ptr())
+    return out
+
+
+def spec_verify(target_logits: torch.Tensor, draft_logits: torch.Tensor, draft_tokens: torch.Tensor,
+                temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor) -> torch.Tensor:
+    """Accept/reject step of speculative decoding for a batch of sequences.
+
+    ``target_logits [seqs, k + 1, vocab]``, ``draft_logits [seqs, k, vocab]`` (fp32), ``draft_tokens [seqs, k]``
+    (int32). Returns int32 ``[seqs, 2]`` = (accepted draft tokens, next token)."""
+    seqs, k1, vocab = target_logits.shape
+    result = torch.empty(seqs, 2, dtype=torch.int32, device=target_logits.device)
+    native.call("ajb_spec_verify", target_logits.contiguous().data_ptr(), draft_logits.contiguous().data_ptr(),
+                draft_tokens.contiguous().data_ptr(), seqs, k1 - 1, vocab, temperature.data_ptr(), seeds.data_ptr(),
+                counters.data_ptr(), result.data_ptr(), native.stream_ptr())
+    return result
