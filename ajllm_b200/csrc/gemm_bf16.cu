@@ -44,8 +44,18 @@ struct Params {
   long long ldc;
   int epilogue;
   int tiles_m, tiles_n;
+  // batched problems (one GEMM per expert): `batch` equal-shaped problems, outputs `c_batch_stride` elements apart.
+  // Rows of a problem may be cut into segments of `segment_rows`; valid_rows[b * segments + s] says how many
+  // leading rows of segment s hold data, and row blocks wholly past that count are skipped.
+  int batch;
+  long long c_batch_stride;
+  const int* valid_rows;
+  int segment_rows;
   DeviceStatus* status;
 };
+
+// Tile number -> (problem, row block, column block); returns false for a row block that holds no data.
+__device__ __forceinline__ bool decode_tile(const Params& p, int tile, int& b, int& tm, int& tn);
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int group_span = kGroupM * tiles_n;
@@ -57,7 +67,24 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = within / rows;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <bool BATCHED>
+__device__ __forceinline__ void load_box(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int b) {
+  if (BATCHED) tma_load_3d(dst, map, bar, c0, c1, b);
+  else tma_load_2d(dst, map, bar, c0, c1);
+}
+
+__device__ __forceinline__ bool decode_tile(const Params& p, int tile, int& b, int& tm, int& tn) {
+  const int per_problem = p.tiles_m * p.tiles_n;
+  b = tile / per_problem;
+  tile_coords(tile - b * per_problem, p.tiles_m, p.tiles_n, tm, tn);
+  if (p.valid_rows == nullptr) return true;
+  const int m0 = tm * BM;
+  const int seg = m0 / p.segment_rows;
+  const int segments = (p.m + p.segment_rows - 1) / p.segment_rows;
+  return m0 - seg * p.segment_rows < p.valid_rows[b * segments + seg];
+}
+
+template <int BN, bool A_MN, bool B_MN, bool BATCHED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   using Cfg = Config<BN>;
@@ -75,7 +102,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
   const int num_kb = (p.k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -109,8 +136,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       int issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        int b, tm, tn;
+        if (!decode_tile(p, tile, b, tm, tn)) continue;
         const int m0 = tm * BM, n0 = tn * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kGemm, 1)) { ok = false; break; }
@@ -120,15 +147,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &map_a, &full[stage], m0 + 64 * j, k0);
+            for (int j = 0; j < BM / 64; ++j) load_box<BATCHED>(sa + j * (BK * 128), &map_a, &full[stage], m0 + 64 * j, k0, b);
           } else {
-            tma_load_2d(sa, &map_a, &full[stage], k0, m0);
+            load_box<BATCHED>(sa, &map_a, &full[stage], k0, m0, b);
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0);
+            for (int j = 0; j < BN / 64; ++j) load_box<BATCHED>(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0, b);
           } else {
-            tma_load_2d(sb, &map_b, &full[stage], k0, n0);
+            load_box<BATCHED>(sb, &map_b, &full[stage], k0, n0, b);
           }
           ++issued;
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
@@ -153,9 +180,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t phase = 0;
     int iter = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      {
+        int b, tm, tn;
+        if (!decode_tile(p, tile, b, tm, tn)) continue;
+      }
       const int buf = iter & 1;
       const uint32_t use = (uint32_t)(iter >> 1);
+      ++iter;
       if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, kGemm, 2)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
@@ -184,11 +216,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     int iter = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int b, tm, tn;
+      if (!decode_tile(p, tile, b, tm, tn)) continue;
       const int buf = iter & 1;
       const uint32_t use = (uint32_t)(iter >> 1);
-      int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      ++iter;
       if (!mbar_wait(&acc_full[buf], use & 1, abort_flag, p.status, kGemm, 4)) { ok = false; break; }
       tc_fence_after_sync();
       const int row = tm * BM + quarter * 32 + lane;
@@ -204,7 +237,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!row_ok || col >= p.n) continue;
         const int valid = min(32, p.n - col);
         if (p.epilogue == kStoreBf16) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row * p.ldc + col;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + b * p.c_batch_stride + (long long)row * p.ldc + col;
           if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -221,7 +254,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               if (j < valid) dst[j] = __float2bfloat16(__uint_as_float(v[j]));
           }
         } else {
-          float* dst = reinterpret_cast<float*>(p.c) + (long long)row * p.ldc + col;
+          float* dst = reinterpret_cast<float*>(p.c) + b * p.c_batch_stride + (long long)row * p.ldc + col;
           const bool accumulate = p.epilogue == kAccumF32;
           if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -255,21 +288,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+struct BatchSpec {
+  int batch = 1;
+  long long a_stride = 0, b_stride = 0, c_stride = 0;   // elements between consecutive problems
+  const int* valid_rows = nullptr;
+  int segment_rows = 0;
+};
+
+template <int BN, bool A_MN, bool B_MN, bool BATCHED>
 static int launch(const void* a, const void* b, void* c, int m, int n, int k, long long lda, long long ldb,
-                  long long ldc, int epilogue, cudaStream_t stream) {
+                  long long ldc, int epilogue, const BatchSpec& spec, cudaStream_t stream) {
   using Cfg = Config<BN>;
   CUtensorMap map_a, map_b;
   int rc;
-  if (A_MN) rc = make_tensor_map_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, lda * 2, BK, 64);
-  else      rc = make_tensor_map_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, lda * 2, BM, 64);
-  if (rc) return rc;
-  if (B_MN) rc = make_tensor_map_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, ldb * 2, BK, 64);
-  else      rc = make_tensor_map_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, k, ldb * 2, BN, 64);
+  const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (BATCHED) {
+    if (A_MN) rc = make_tensor_map_3d(&map_a, a, bf, 2, spec.batch, k, m, spec.a_stride * 2, lda * 2, BK, 64);
+    else      rc = make_tensor_map_3d(&map_a, a, bf, 2, spec.batch, m, k, spec.a_stride * 2, lda * 2, BM, 64);
+    if (rc) return rc;
+    if (B_MN) rc = make_tensor_map_3d(&map_b, b, bf, 2, spec.batch, k, n, spec.b_stride * 2, ldb * 2, BK, 64);
+    else      rc = make_tensor_map_3d(&map_b, b, bf, 2, spec.batch, n, k, spec.b_stride * 2, ldb * 2, BN, 64);
+  } else {
+    if (A_MN) rc = make_tensor_map_2d(&map_a, a, bf, 2, k, m, lda * 2, BK, 64);
+    else      rc = make_tensor_map_2d(&map_a, a, bf, 2, m, k, lda * 2, BM, 64);
+    if (rc) return rc;
+    if (B_MN) rc = make_tensor_map_2d(&map_b, b, bf, 2, k, n, ldb * 2, BK, 64);
+    else      rc = make_tensor_map_2d(&map_b, b, bf, 2, n, k, ldb * 2, BN, 64);
+  }
   if (rc) return rc;
 
   static bool configured = false;
-  auto kernel = gemm_kernel<BN, A_MN, B_MN>;
+  auto kernel = gemm_kernel<BN, A_MN, B_MN, BATCHED>;
   if (!configured) {
     AJB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured = true;
@@ -278,12 +327,38 @@ static int launch(const void* a, const void* b, void* c, int m, int n, int k, lo
   p.c = c; p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.epilogue = epilogue;
   p.tiles_m = (m + BM - 1) / BM;
   p.tiles_n = (n + BN - 1) / BN;
+  p.batch = spec.batch;
+  p.c_batch_stride = spec.c_stride;
+  p.valid_rows = spec.valid_rows;
+  p.segment_rows = spec.segment_rows > 0 ? spec.segment_rows : m;
   p.status = device_status_buffer();
-  const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * spec.batch;
+  const int grid = tiles < sm_count() ? (int)tiles : sm_count();
   kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, p);
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+template <bool BATCHED>
+static int dispatch(const void* a, const void* b, void* c, int m, int n, int k, long long lda, long long ldb,
+                    long long ldc, int a_mn_major, int b_mn_major, int epilogue, const BatchSpec& spec, cudaStream_t s) {
+  // narrow outputs waste less of a 128-wide tile than of a 256-wide one
+  const bool narrow = (n % 256 != 0) && ((n + 127) / 128 * 128 < (n + 255) / 256 * 256);
+  const int sel = (a_mn_major ? 2 : 0) | (b_mn_major ? 1 : 0);
+  if (narrow) {
+    switch (sel) {
+      case 0: return launch<128, false, false, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+      case 1: return launch<128, false, true, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+      case 2: return launch<128, true, false, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+      default: return launch<128, true, true, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+    }
+  }
+  switch (sel) {
+    case 0: return launch<256, false, false, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+    case 1: return launch<256, false, true, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+    case 2: return launch<256, true, false, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+    default: return launch<256, true, true, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+  }
 }
 
 }  // namespace gemm
@@ -296,22 +371,26 @@ extern "C" int ajb_gemm_bf16(const void* a, const void* b, void* c, int m, int n
   using namespace ajb;
   AJB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm: empty problem %dx%dx%d", m, n, k);
   AJB_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm: unknown epilogue %d", epilogue);
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // narrow outputs waste less of a 128-wide tile than of a 256-wide one
-  const bool narrow = (n % 256 != 0) && ((n + 127) / 128 * 128 < (n + 255) / 256 * 256);
-  const int sel = (a_mn_major ? 2 : 0) | (b_mn_major ? 1 : 0);
-  if (narrow) {
-    switch (sel) {
-      case 0: return gemm::launch<128, false, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-      case 1: return gemm::launch<128, false, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-      case 2: return gemm::launch<128, true, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-      default: return gemm::launch<128, true, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-    }
-  }
-  switch (sel) {
-    case 0: return gemm::launch<256, false, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-    case 1: return gemm::launch<256, false, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-    case 2: return gemm::launch<256, true, false>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-    default: return gemm::launch<256, true, true>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, s);
-  }
+  return gemm::dispatch<false>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, gemm::BatchSpec(),
+                               reinterpret_cast<cudaStream_t>(stream));
+}
+
+// `batch` equal-shaped problems (one per expert), operands / outputs `*_stride` elements apart. When valid_rows is
+// given, the rows of each problem are cut into segments of `segment_rows` rows and valid_rows[problem * segments +
+// segment] (device memory) tells how many leading rows of that segment hold data: row blocks past it are skipped,
+// their outputs are left untouched.
+extern "C" int ajb_gemm_bf16_batched(const void* a, const void* b, void* c, int batch, int m, int n, int k, long long lda,
+                                     long long ldb, long long ldc, long long a_stride, long long b_stride,
+                                     long long c_stride, int a_mn_major, int b_mn_major, int epilogue,
+                                     const void* valid_rows, int segment_rows, void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(batch > 0 && m > 0 && n > 0 && k > 0, "batched gemm: empty problem");
+  AJB_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm: unknown epilogue %d", epilogue);
+  AJB_REQUIRE(valid_rows == nullptr || (segment_rows > 0 && segment_rows % gemm::BM == 0),
+              "batched gemm: segment_rows must be a positive multiple of %d", gemm::BM);
+  gemm::BatchSpec spec;
+  spec.batch = batch; spec.a_stride = a_stride; spec.b_stride = b_stride; spec.c_stride = c_stride;
+  spec.valid_rows = (const int*)valid_rows; spec.segment_rows = segment_rows;
+  return gemm::dispatch<true>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, spec,
+                              reinterpret_cast<cudaStream_t>(stream));
 }

@@ -95,12 +95,11 @@ class ExpertBank(nn.Module):
         self.w13 = nn.Parameter(w13)
         self.w2 = nn.Parameter(w2)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        outs = []
-        for e in range(self.w13.shape[0]):
-            hidden = ops.swiglu_interleaved(ops.linear(x[e], self.w13[e]))
-            outs.append(ops.linear(hidden, self.w2[e]))
-        return torch.stack(outs, dim=0)
+    def forward(self, x: torch.Tensor, valid_rows: torch.Tensor | None = None, segment_rows: int = 0) -> torch.Tensor:
+        """All local experts in one batched GEMM per projection; with ``valid_rows`` (rows in use per
+        capacity segment) the kernels skip row blocks that hold only padding."""
+        hidden = ops.swiglu_interleaved(ops.linear_batched(x, self.w13, valid_rows, segment_rows))
+        return ops.linear_batched(hidden, self.w2, valid_rows, segment_rows)
 
 
 class MoEFeedForward(nn.Module):

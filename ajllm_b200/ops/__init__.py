@@ -6,7 +6,9 @@ from ajllm_b200.ops.functional import (
     cross_entropy,
     embedding,
     gemm,
+    gemm_batched,
     linear,
+    linear_batched,
     linear_cross_entropy,
     paged_attention_ragged,
     rms_norm,

@@ -43,6 +43,67 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, m: int, n: int, k:
     return out
 
 
+def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, m: int, n: int, k: int, *,
+                 a_mn_major: bool = False, b_mn_major: bool = False, epilogue: int = EPI_STORE_BF16,
+                 valid_rows: torch.Tensor | None = None, segment_rows: int = 0) -> torch.Tensor:
+    """``batch`` equal-shaped GEMMs in one launch: ``a``, ``b``, ``out`` are 3-D with the problem index first.
+    ``valid_rows`` (int32 ``[batch, m / segment_rows]`` on the device) marks how many leading rows of each row
+    segment hold data; row blocks past that are skipped and their outputs left untouched."""
+    batch = a.shape[0]
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+    native.call("ajb_gemm_bf16_batched", a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, m, n, k,
+                a.stride(1), b.stride(1), out.stride(1), a.stride(0), b.stride(0), out.stride(0),
+                int(a_mn_major), int(b_mn_major), epilogue, native.ptr(valid_rows), segment_rows, native.stream_ptr())
+    return out
+
+
+class _BatchedLinearFn(torch.autograd.Function):
+    """``y[e] = x[e] @ w[e].T`` for stacked experts, with optional per-segment row counts."""
+
+    @staticmethod
+    def forward(ctx, x, weight, valid_rows, segment_rows):
+        e, rows, k = x.shape
+        n = weight.shape[1]
+        x = x.contiguous()
+        out = torch.zeros(e, rows, n, dtype=torch.bfloat16, device=x.device) if valid_rows is not None else \
+            torch.empty(e, rows, n, dtype=torch.bfloat16, device=x.device)
+        gemm_batched(x, weight, out, rows, n, k, valid_rows=valid_rows, segment_rows=segment_rows)
+        ctx.save_for_backward(x, weight, valid_rows)
+        ctx.segment_rows = segment_rows
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight, valid_rows = ctx.saved_tensors
+        e, rows, k = x.shape
+        n = weight.shape[1]
+        g = grad_out.contiguous()
+        grad_x = grad_w = None
+        if ctx.needs_input_grad[0]:
+            grad_x = torch.zeros_like(x) if valid_rows is not None else torch.empty_like(x)
+            gemm_batched(g, weight, grad_x, rows, k, n, b_mn_major=True, valid_rows=valid_rows,
+                         segment_rows=ctx.segment_rows)
+        if ctx.needs_input_grad[1]:
+            # rows past the valid count hold zeros in both operands (padded dispatch buffer), so the full
+            # contraction over rows is exact
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                gemm_batched(g, x, main, n, k, rows, a_mn_major=True, b_mn_major=True, epilogue=EPI_ACCUM_F32)
+                weight.main_grad_written = True
+            else:
+                grad_w = torch.empty(e, n, k, dtype=torch.bfloat16, device=x.device)
+                gemm_batched(g, x, grad_w, n, k, rows, a_mn_major=True, b_mn_major=True)
+        return grad_x, grad_w, None, None
+
+
+def linear_batched(x: torch.Tensor, weight: torch.Tensor, valid_rows: torch.Tensor | None = None,
+                   segment_rows: int = 0) -> torch.Tensor:
+    """Stacked-expert projection ``[E, rows, in] x [E, out, in] -> [E, rows, out]``."""
+    if _is_cuda(x) and x.dtype == torch.bfloat16:
+        return _BatchedLinearFn.apply(x, weight, valid_rows, segment_rows)
+    return torch.einsum("erk,enk->ern", x, weight)
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight):

@@ -28,6 +28,8 @@ c_float = ctypes.c_float
 _SIGNATURES: dict[str, list] = {
     "ajb_gemm_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long,
                       c_int, c_int, c_int, c_void],
+    "ajb_gemm_bf16_batched": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_long, c_long,
+                              c_long, c_int, c_int, c_int, c_void, c_int, c_void],
     "ajb_rmsnorm_fwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float, c_void],
     "ajb_rmsnorm_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_void],
     "ajb_colsum_f32": [c_void, c_void, c_int, c_int, c_int, c_void],

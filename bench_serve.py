@@ -1,0 +1,158 @@
+"""Serving benchmark: output tokens/s of the 8B-class decoder (32 layers, d_model 4096, 32 heads x 128,
+8 KV heads, SwiGLU 14336, vocab 128256) behind the paged-KV continuous-batching engine, tensor-parallel
+over N GPUs. Requests: prompt lengths uniform in [128, 2048], output lengths uniform in [64, 512], uniform
+random token ids (seed 0), at most 256 concurrent sequences, random-init bf16 weights.
+
+    python bench_serve.py --gpus 1 --requests 256
+    python -m torch.distributed.run --nproc-per-node 8 ... bench_serve.py --gpus 8 --requests 1024 \
+        [--quantization fp8] [--speculative 4] [--temperature 1.0]
+    python bench_serve.py --impl reference --requests 2      # the reference's generate(): batch 1, no KV cache
+
+Rank 0 prints one JSON line; throughput is generated tokens divided by the wall time of the whole run
+(submission to last token), bracketed by device synchronisation, max over ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+MODEL = {"name": "dense_8b", "context_length": 4096, "d_model": 4096, "num_layers": 32, "num_heads": 32,
+         "num_kv_heads": 8, "d_ff": 14336, "position_encoding": {"type": "rope", "theta": 500000.0},
+         "init": {"type": "normal", "std": 0.02}}
+VOCAB = 128256
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-batched-tokens", type=int, default=8192)
+    ap.add_argument("--quantization", default=None)
+    ap.add_argument("--speculative", type=int, default=0, help="k draft tokens per step (2-layer random-init draft)")
+    ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    return ap.parse_args()
+
+
+def make_requests(count: int):
+    import numpy as np
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, VOCAB, size=int(rng.integers(128, 2049))).tolist() for _ in range(count)]
+    outputs = [int(rng.integers(64, 513)) for _ in range(count)]
+    return prompts, outputs
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from ajllm_b200.engine import LLMEngine, SamplingParams
+    from ajllm_b200.models import build_model
+    from ajllm_b200.ops import native
+    from ajllm_b200.parallel import ParallelMesh, TensorParallel, init_distributed
+
+    rank, world, device = init_distributed("cuda")
+    tp = None
+    if world > 1:
+        mesh = ParallelMesh(tp=world)
+        tp = TensorParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size)
+    torch.manual_seed(0)
+    config = dict(MODEL)
+    if args.layers:
+        config["num_layers"] = args.layers
+    with torch.device(device):
+        model = build_model(config, VOCAB, tp=tp).to(dtype=torch.bfloat16)
+        draft = None
+        if args.speculative:
+            draft = build_model({**config, "num_layers": 2}, VOCAB, tp=tp).to(dtype=torch.bfloat16)
+    prompts, outputs = make_requests(args.requests)
+    blocks = (args.max_num_seqs * (2048 + 512 + 64)) // 16
+    engine = LLMEngine(model, block_size=16, num_blocks=blocks, max_num_seqs=args.max_num_seqs,
+                       max_batched_tokens=args.max_batched_tokens, quantization=args.quantization, draft_model=draft,
+                       num_speculative_tokens=args.speculative or 4, seed=0)
+    params = [SamplingParams(n, args.temperature, None, None, seed=i) for i, n in enumerate(outputs)]
+    # warm-up: a few short requests through every code path
+    engine.generate([p[:160] for p in prompts[:4]], [SamplingParams(8, args.temperature, None) for _ in range(4)])
+    engine.stats = type(engine.stats)()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches0 = native.launch_count
+    t0 = time.perf_counter()
+    results = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    if world > 1:
+        box = torch.tensor([elapsed], device=device, dtype=torch.float64)
+        dist.all_reduce(box, op=dist.ReduceOp.MAX)
+        elapsed = float(box)
+    generated = sum(len(r.output) for r in results)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "serve output tokens/sec", "value": generated / elapsed, "unit": "tokens/s", "n_gpus": world,
+            "impl": "ours", "dtype": "bf16" if not args.quantization else args.quantization, "data": "synthetic",
+            "higher_is_better": True,
+            "config": {"model": "dense-8B (32L d4096 32h/8kv hd128 ffn14336 vocab128256)", "requests": args.requests,
+                       "prompt_len": "U[128,2048]", "output_len": "U[64,512]", "max_num_seqs": args.max_num_seqs,
+                       "parallelism": f"tp{world}", "speculative_k": args.speculative, "temperature": args.temperature,
+                       "layers_override": args.layers or None},
+            "elapsed_s": elapsed, "output_tokens": generated, "prompt_tokens": sum(len(p) for p in prompts),
+            "engine_steps": engine.stats.steps, "preemptions": engine.stats.preemptions,
+            "draft_acceptance_rate": engine.stats.acceptance_rate if args.speculative else None,
+            "gpu_launches": native.launch_count - launches0, "kernel_status": native.lib().ajb_check_status(),
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "ajllm" / "__init__.py").is_file():
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no reference install"}))
+        return
+    sys.path.insert(0, str(ref_root))
+    import torch
+    from ajllm.generation.generator import generate
+    from ajllm.modeling.factory import build_model
+
+    device = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    config = {"name": "dense_8b_mha", "context_length": 4096, "d_model": 4096, "num_layers": args.layers or 32,
+              "num_heads": 32, "d_ff": 14336, "position_encoding": {"type": "rope", "theta": 500000.0}}
+    try:
+        with torch.device(device):
+            model = build_model(config, VOCAB).to(dtype=torch.bfloat16)
+        prompts, outputs = make_requests(args.requests)
+        generated, t0 = 0, None
+        for i, (p, n) in enumerate(zip(prompts, outputs)):
+            if i == 1 or (i == 0 and len(prompts) == 1):
+                torch.cuda.synchronize()
+                t0, generated = time.perf_counter(), 0          # first request is the warm-up when there are several
+            out = generate(model, torch.tensor(p, device=device), n, args.temperature, None, None)
+            generated += out.numel() - len(p)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+        print(json.dumps({"metric": "serve output tokens/sec", "value": generated / elapsed, "unit": "tokens/s",
+                          "n_gpus": 1, "impl": "reference", "dtype": "bf16", "data": "synthetic",
+                          "config": {"model": "dense-8B as the reference can express it: MHA, generate() batch 1, no KV cache",
+                                     "requests_timed": max(1, len(prompts) - 1)},
+                          "elapsed_s": elapsed, "output_tokens": generated}))
+    except Exception as error:  # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(error).__name__}: {error}"[:300]}))
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    run_reference(a) if a.impl == "reference" else run_ours(a)

@@ -200,3 +200,31 @@ def test_flash_attention_forward_backward(B, T, Hq, Hkv, hd):
 def test_no_wait_expired():
     """Every bounded wait in the kernels above completed; a status word would mean a protocol bug."""
     assert native.lib().ajb_check_status() == 0
+
+
+def test_batched_gemm_with_row_counts():
+    torch.manual_seed(12)
+    e, rows, k, n, seg = 3, 512, 256, 384, 256
+    x = torch.randn(e, rows, k, device=_dev(), dtype=torch.bfloat16)
+    w = (torch.randn(e, n, k, device=_dev()) * 0.1).to(torch.bfloat16)
+    out = torch.empty(e, rows, n, device=_dev(), dtype=torch.bfloat16)
+    ops.gemm_batched(x, w, out, rows, n, k)
+    want = torch.einsum("erk,enk->ern", x.float(), w.float())
+    assert _rel_err(out, want) < 5e-3
+    counts = torch.tensor([[256, 100], [0, 129], [17, 0]], dtype=torch.int32, device=_dev())
+    sentinel = torch.full_like(out, 7.0)
+    ops.gemm_batched(x, w, sentinel, rows, n, k, valid_rows=counts, segment_rows=seg)
+    for b in range(e):
+        for s in range(2):
+            c = int(counts[b, s])
+            blocks = (c + 127) // 128 * 128
+            got = sentinel[b, s * seg:(s + 1) * seg]
+            assert _rel_err(got[:blocks], want[b, s * seg:s * seg + blocks]) < 5e-3 if blocks else True
+            assert bool((got[blocks:] == 7.0).all())
+    xg = x.clone().requires_grad_()
+    wg = w.clone().requires_grad_()
+    y = ops.linear_batched(xg, wg)
+    g = torch.randn_like(y)
+    y.backward(g)
+    assert _rel_err(xg.grad, torch.einsum("ern,enk->erk", g.float(), w.float())) < 5e-3
+    assert _rel_err(wg.grad, torch.einsum("ern,erk->enk", g.float(), x.float())) < 5e-3
