@@ -30,27 +30,41 @@ from torch import nn
 from ajllm_b200 import ops
 from ajllm_b200.models.feed_forward import SwiGLU, deinterleave_rows, interleave_rows
 from ajllm_b200.models.layers import InitSpec, init_matrix_
+from ajllm_b200.ops import native
 
 
-def route_tokens(logits: torch.Tensor, top_k: int, capacity: int, normalize_gates: bool = True):
+def route_tokens(logits: torch.Tensor, top_k: int, capacity: int, normalize_gates: bool = True,
+                 stride: int | None = None):
     """Routing decision for ``[N, E]`` router logits.
 
     Returns ``(gates [N,k] fp32, experts [N,k], slots [N,k], aux_terms)`` where ``slots`` is the row of
-    the ``[E*C]`` dispatch buffer an assignment lands in, or ``-1`` when it was dropped, and
-    ``aux_terms = (f [E], P [E])``.
+    the ``[E * stride]`` dispatch buffer an assignment lands in (``stride`` defaults to ``capacity``; a
+    larger stride pads every expert's region), or ``-1`` when it was dropped, and
+    ``aux_terms = (f [E], P [E])``. On a GPU the slot assignment is one kernel (one CTA per expert scans
+    the assignments in order); gates and probabilities stay in autograd.
     """
     tokens, num_experts = logits.shape
+    stride = capacity if stride is None else stride
     probs = torch.softmax(logits.float(), dim=-1)
     gates, experts = torch.topk(probs, top_k, dim=-1)
     if normalize_gates:
         gates = gates / gates.sum(dim=-1, keepdim=True)
     flat_expert = experts.reshape(-1)
-    order = torch.argsort(flat_expert, stable=True)
-    counts = torch.bincount(flat_expert, minlength=num_experts)
-    starts = torch.cumsum(counts, 0) - counts
-    position = torch.empty_like(flat_expert)
-    position[order] = torch.arange(flat_expert.numel(), device=logits.device) - starts[flat_expert[order]]
-    slots = torch.where(position < capacity, flat_expert * capacity + position, torch.full_like(position, -1))
+    if logits.is_cuda and native.available():
+        flat32 = flat_expert.to(torch.int32).contiguous()
+        slots = torch.empty_like(flat32)
+        kept = torch.empty(num_experts, dtype=torch.int32, device=logits.device)
+        native.call("ajb_moe_assign_slots", flat32.data_ptr(), flat32.numel(), num_experts, capacity, stride,
+                    slots.data_ptr(), kept.data_ptr(), native.stream_ptr())
+        counts = torch.bincount(flat_expert, minlength=num_experts)
+        slots = slots.long()
+    else:
+        order = torch.argsort(flat_expert, stable=True)
+        counts = torch.bincount(flat_expert, minlength=num_experts)
+        starts = torch.cumsum(counts, 0) - counts
+        position = torch.empty_like(flat_expert)
+        position[order] = torch.arange(flat_expert.numel(), device=logits.device) - starts[flat_expert[order]]
+        slots = torch.where(position < capacity, flat_expert * stride + position, torch.full_like(position, -1))
     fraction = counts.float() / float(tokens * top_k)
     mean_prob = probs.mean(dim=0)
     return gates, experts, slots.reshape(tokens, top_k), (fraction, mean_prob)
@@ -156,17 +170,39 @@ class MoEFeedForward(nn.Module):
         if k2 in state:
             state[prefix + "experts.w2"] = state.pop(k2)[mine].contiguous()
 
+    def _forward_fused(self, flat, gates, experts, slots, kept, capacity, stride, exchange) -> torch.Tensor:
+        """Expert-parallel path over symmetric memory: rows go straight to the owning rank's expert-major buffer,
+        experts run as batched GEMMs that skip padding, outputs are read back and gate-weighted in one kernel."""
+        from ajllm_b200.parallel import moe_exchange
+
+        counts = torch.bincount(experts[kept], minlength=self.num_experts).to(torch.int32)
+        slots32 = slots.to(torch.int32).contiguous()
+        grouped = moe_exchange.dispatch(flat, slots32, counts, exchange, self.num_local, stride)
+        valid = exchange.received_counts(self.num_local)
+        result = self.experts(grouped, valid, stride)
+        combined = moe_exchange.combine(result, gates.float().contiguous(), slots32, exchange, self.num_local, stride)
+        if self.shared is not None:
+            combined = combined + self.shared(flat)
+        return combined
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         flat = x.reshape(-1, shape[-1])
         tokens, dim = flat.shape
         capacity = capacity_for(tokens, self.top_k, self.num_experts, self.capacity_factor)
+        on_gpu = flat.is_cuda and flat.dtype == torch.bfloat16
+        # on a GPU every expert's region is padded to whole 128-row tiles so the batched GEMM can skip padding
+        stride = (capacity + 127) // 128 * 128 if on_gpu else capacity
         logits = ops.reference.linear(flat.float(), self.router.float())
         gates, experts, slots, (fraction, mean_prob) = route_tokens(logits, self.top_k, capacity,
-                                                                  self.normalize_gates)
+                                                                  self.normalize_gates, stride)
         self.last_aux_loss = self.aux_loss_coef * self.num_experts * torch.sum(fraction.detach() * mean_prob)
         kept = slots >= 0
         self.last_dropped_fraction = float(1.0 - kept.float().mean()) if not x.requires_grad else None
+        exchange = getattr(self.ep, "exchange", None) if self.ep is not None else None
+        if exchange is not None and on_gpu:
+            return self._forward_fused(flat, gates, experts, slots, kept, capacity, stride, exchange).reshape(shape)
+        capacity = stride          # buffer rows per expert from here on
 
         # dispatch: row s of the buffer holds the token assigned to slot s (zeros where unused)
         token_of = torch.arange(tokens, device=x.device)[:, None].expand(-1, self.top_k)[kept]

@@ -1,0 +1,121 @@
+"""Mixture-of-experts kernels: routing and slot assignment on one GPU, the fused expert-parallel exchange
+against the NCCL all-to-all path on two GPUs."""
+
+import os
+
+import pytest
+import torch
+
+from ajllm_b200.models import build_model
+from ajllm_b200.models.moe import capacity_for, route_tokens
+from ajllm_b200.ops import native
+from tests.conftest import free_port
+
+pytestmark = pytest.mark.gpu
+
+MOE = {"name": "m", "context_length": 256, "d_model": 256, "num_layers": 2, "num_heads": 4, "num_kv_heads": 2, "d_ff": 256,
+       "moe": {"num_experts": 8, "top_k": 2, "shared_experts": 1, "d_ff": 256, "aux_loss_coef": 0.01,
+               "capacity_factor": 1.25}, "init": {"type": "normal", "std": 0.05}}
+
+
+def test_route_kernel_and_slot_assignment_match_cpu():
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    logits = torch.randn(1000, 64, device=dev)
+    experts = torch.empty(1000, 6, dtype=torch.int32, device=dev)
+    gates = torch.empty(1000, 6, dtype=torch.float32, device=dev)
+    probs = torch.empty(1000, 64, dtype=torch.float32, device=dev)
+    native.call("ajb_moe_route_fwd", logits.data_ptr(), 1000, 64, 6, 1, experts.data_ptr(), gates.data_ptr(),
+                probs.data_ptr(), native.stream_ptr())
+    want_p = torch.softmax(logits, -1)
+    want_g, want_e = torch.topk(want_p, 6, dim=-1)
+    assert torch.allclose(probs, want_p, atol=1e-6)
+    assert torch.equal(experts.long(), want_e)
+    assert torch.allclose(gates, want_g / want_g.sum(-1, keepdim=True), atol=1e-6)
+    cap = capacity_for(1000, 6, 64, 1.0)
+    g_gpu, e_gpu, s_gpu, _ = route_tokens(logits, 6, cap, True, stride=128)
+    g_cpu, e_cpu, s_cpu, _ = route_tokens(logits.cpu(), 6, cap, True, stride=128)
+    assert torch.equal(e_gpu.cpu(), e_cpu) and torch.equal(s_gpu.cpu(), s_cpu)
+    assert int((s_cpu < 0).sum()) > 0          # the case exercises dropped assignments
+
+
+def test_moe_model_gpu_matches_cpu_reference():
+    torch.manual_seed(0)
+    cpu = build_model(MOE, 512)
+    gpu = build_model(MOE, 512).to(device="cuda", dtype=torch.bfloat16)
+    gpu.load_state_dict(cpu.state_dict())
+    cpu.load_state_dict({k: v.float() for k, v in gpu.state_dict().items()})     # same bf16-rounded weights
+    tokens = torch.randint(0, 512, (2, 257))
+    want = cpu.loss(tokens[:, :-1], tokens[:, 1:])
+    got = gpu.loss(tokens[:, :-1].cuda(), tokens[:, 1:].cuda())
+    assert abs(float(got) - float(want)) < 3e-2
+    got.backward()
+    want.backward()
+    g1 = gpu.layers[0].feed_forward.experts.w2.grad.float().cpu()
+    g2 = cpu.layers[0].feed_forward.experts.w2.grad
+    assert float((g1 - g2).norm() / g2.norm()) < 0.12
+    assert native.lib().ajb_check_status() == 0
+
+
+def _worker(rank, world, port, results):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from ajllm_b200.parallel import ParallelMesh, TensorParallel
+        from ajllm_b200.parallel.moe_exchange import FusedExpertExchange
+
+        mesh = ParallelMesh(tp=1, fsdp=world, ep=world)
+        outs = {}
+        torch.manual_seed(0)
+        reference_state = build_model(MOE, 512).state_dict()
+        tokens = torch.randint(0, 512, (2 * world, 129), generator=torch.Generator().manual_seed(5))
+        mine = tokens[rank * 2:(rank + 1) * 2].to(device)
+        for tag in ("nccl", "fused"):
+            ep = TensorParallel(mesh.ep.group, mesh.ep.rank, mesh.ep.size)
+            if tag == "fused":
+                ep.exchange = FusedExpertExchange(mesh.ep.group, device)
+            model = build_model(MOE, 512, ep=ep).to(device=device, dtype=torch.bfloat16)
+            model.load_state_dict(reference_state)
+            for _ in range(2):             # twice: buffers, flags and epochs are reused
+                model.zero_grad()
+                loss = model.loss(mine[:, :-1], mine[:, 1:])
+                loss.backward()
+            ff = model.layers[0].feed_forward
+            outs[tag] = (float(loss), ff.experts.w13.grad.float().clone(), ff.router.grad.float().clone(),
+                         model.token_embeddings.weight.grad.float().clone())
+        torch.cuda.synchronize()
+
+        def rel(a, b):
+            return float((a - b).norm() / b.norm().clamp_min(1e-12))
+        results[rank] = {"loss": (outs["fused"][0], outs["nccl"][0]),
+                         "w13": rel(outs["fused"][1], outs["nccl"][1]), "router": rel(outs["fused"][2], outs["nccl"][2]),
+                         "emb": rel(outs["fused"][3], outs["nccl"][3]), "status": native.lib().ajb_check_status()}
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_expert_exchange_matches_all_to_all_path():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive and all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for rank in range(2):
+        out = results[rank]
+        assert out["status"] == 0, out
+        assert abs(out["loss"][0] - out["loss"][1]) < 2e-2, out
+        assert out["w13"] < 3e-2 and out["router"] < 6e-2 and out["emb"] < 3e-2, out
