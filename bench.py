@@ -33,6 +33,16 @@ GLOBAL_BATCH = 32
 SEQ = 4096
 METRIC = "train tokens/sec"
 
+# Secondary workloads (`--workload`): the flagship line above stays the default.
+DENSE_8B = {"name": "dense_8b", "context_length": 8192, "d_model": 4096, "num_layers": 32, "num_heads": 32,
+            "num_kv_heads": 8, "d_ff": 14336, "position_encoding": {"type": "rope", "theta": 500000.0},
+            "init": {"type": "normal", "std": 0.02}}
+MOE_64E = {"name": "moe_64e", "context_length": 4096, "d_model": 2048, "num_layers": 24, "num_heads": 16,
+           "num_kv_heads": 4, "d_ff": 1408,
+           "moe": {"num_experts": 64, "top_k": 6, "shared_experts": 2, "d_ff": 1408, "aux_loss_coef": 0.01,
+                   "capacity_factor": 1.25},
+           "position_encoding": {"type": "rope", "theta": 10000.0}, "init": {"type": "normal", "std": 0.02}}
+
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -44,6 +54,9 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
     ap.add_argument("--seq", type=int, default=SEQ)
+    ap.add_argument("--workload", default="dense1p3b_tp", choices=["dense1p3b_tp", "dense8b_fsdp", "moe64e_ep"],
+                    help="dense8b_fsdp: 8B, FSDP over N, micro-batch 2 x 8192 per GPU, accumulation 4, per-layer "
+                         "checkpointing; moe64e_ep: 64-expert top-6 MoE, EP = N with FSDP, 8 x 4096 per GPU")
     return ap.parse_args()
 
 
@@ -320,9 +333,114 @@ def run_reference(args) -> None:
         dist.destroy_process_group()
 
 
+def run_sharded(args) -> None:
+    """Weak-scaling workloads on the fully-sharded runtime (8B dense; 64-expert MoE with expert parallelism)."""
+    import torch
+    import torch.distributed as dist
+
+    from ajllm_b200.models import build_model
+    from ajllm_b200.ops import native
+    from ajllm_b200.parallel import ParallelMesh, TensorParallel, init_distributed
+    from ajllm_b200.training import FlatAdamW, optimizer_step
+    from ajllm_b200.utils.timing import ClockSampler, max_over_ranks
+
+    rank, world, device = init_distributed("cuda")
+    moe = args.workload == "moe64e_ep"
+    config = dict(MOE_64E if moe else DENSE_8B)
+    vocab = 32000 if moe else 128256
+    if args.layers:
+        config["num_layers"] = args.layers
+    seq = config["context_length"]
+    per_gpu_batch, accumulation = (8, 1) if moe else (2, 4)
+    micro = args.micro_batch or (4 if moe else 2)
+    accumulation = accumulation * (per_gpu_batch // micro)
+    torch.manual_seed(0)
+    ep = None
+    mesh = None
+    fused_ep = False
+    if world > 1:
+        mesh = ParallelMesh(tp=1, fsdp=world, ep=world if moe else 1)
+        if moe:
+            ep = TensorParallel(mesh.ep.group, mesh.ep.rank, mesh.ep.size)
+            if os.environ.get("AJB_FUSED_EP", "1") != "0":
+                from ajllm_b200.parallel.moe_exchange import FusedExpertExchange
+                ep.exchange = FusedExpertExchange(mesh.ep.group, device)
+                fused_ep = True
+    with torch.device(device):
+        model = build_model(config, vocab, ep=ep, activation_checkpointing="layer" if world == 1 else "none")
+    model = model.to(device=device, dtype=torch.bfloat16)
+    params_local = sum(p.numel() for p in model.parameters())
+    if world > 1:
+        from ajllm_b200.parallel.fsdp import ShardedDataParallel
+        model = ShardedDataParallel(model, mesh.dp.group, learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8,
+                                    weight_decay=0.1)
+        optimizer = model.optimizer
+    else:
+        optimizer = FlatAdamW(model, learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1)
+    gen = torch.Generator().manual_seed(rank)
+    total_steps = args.warmup + args.steps
+    host = [[torch.randint(0, vocab, (micro, seq + 1), generator=gen).pin_memory() for _ in range(accumulation)]
+            for _ in range(total_steps)]
+
+    def feed(step_batches):
+        it = iter(step_batches)
+
+        def next_batch():
+            t = next(it).to(device, non_blocking=True)
+            return t[:, :-1], t[:, 1:]
+        return next_batch
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for s in range(args.warmup):
+        optimizer_step(model, optimizer, feed(host[s]), accumulation, 1.0)
+    barrier()
+    sampler = ClockSampler(device.index or 0).start()
+    launches0 = native.launch_count
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    begin.record()
+    losses = []
+    for s in range(args.warmup, total_steps):
+        loss, norm = optimizer_step(model, optimizer, feed(host[s]), accumulation, 1.0)
+        losses.append(float(loss))
+    end.record()
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop()
+    ms = max_over_ranks(begin.elapsed_time(end), device)
+    wall_ms = max_over_ranks(wall_ms, device)
+    tokens = world * per_gpu_batch * (4 if not moe else 1) * seq * args.steps
+    peak = torch.cuda.max_memory_allocated(device) / 2**30
+    if rank == 0:
+        emit({
+            "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {"model": config["name"], "params_on_rank": params_local, "per_gpu_batch": per_gpu_batch,
+                       "seq_len": seq, "micro_batch": micro, "grad_accumulation": accumulation,
+                       "parallelism": (f"ep{world} x fsdp{world}" if moe else f"fsdp{world}") if world > 1 else "single",
+                       "expert_exchange": ("fused-symmetric-memory" if fused_ep else "nccl-all-to-all") if moe else None,
+                       "activation_checkpointing": "per layer", "layers_override": args.layers or None},
+            "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons")},
+            "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": accumulation * micro * (seq + 1) * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": native.launch_count - launches0, "final_loss": losses[-1], "peak_memory_gib": peak,
+            "kernel_status": native.lib().ajb_check_status(),
+        })
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     arguments = parse_args()
     if arguments.impl == "reference":
         run_reference(arguments)
+    elif arguments.workload != "dense1p3b_tp":
+        run_sharded(arguments)
     else:
         run_ours(arguments)

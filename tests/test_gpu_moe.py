@@ -68,32 +68,43 @@ def _worker(rank, world, port, results):
         from ajllm_b200.parallel import ParallelMesh, TensorParallel
         from ajllm_b200.parallel.moe_exchange import FusedExpertExchange
 
+        config = {**MOE, "moe": {**MOE["moe"], "capacity_factor": 8.0}}     # nothing dropped: one global answer
         mesh = ParallelMesh(tp=1, fsdp=world, ep=world)
-        outs = {}
         torch.manual_seed(0)
-        reference_state = build_model(MOE, 512).state_dict()
+        oracle = build_model(config, 512)
+        state = {k: v.to(torch.bfloat16) for k, v in oracle.state_dict().items()}
+        oracle.load_state_dict({k: v.float() for k, v in state.items()})
         tokens = torch.randint(0, 512, (2 * world, 129), generator=torch.Generator().manual_seed(5))
+        want_loss = oracle.loss(tokens[:, :-1], tokens[:, 1:])
+        want_loss.backward()
+        per = config["moe"]["num_experts"] // world
+        want_w13 = oracle.layers[0].feed_forward.experts.w13.grad[rank * per:(rank + 1) * per]
+        want_router = oracle.layers[0].feed_forward.router.grad
         mine = tokens[rank * 2:(rank + 1) * 2].to(device)
+
+        def rel(a, b):
+            return float((a.float().cpu() - b).norm() / b.norm().clamp_min(1e-12))
+
+        report = {}
         for tag in ("nccl", "fused"):
             ep = TensorParallel(mesh.ep.group, mesh.ep.rank, mesh.ep.size)
             if tag == "fused":
                 ep.exchange = FusedExpertExchange(mesh.ep.group, device)
-            model = build_model(MOE, 512, ep=ep).to(device=device, dtype=torch.bfloat16)
-            model.load_state_dict(reference_state)
+            model = build_model(config, 512, ep=ep).to(device=device, dtype=torch.bfloat16)
+            model.load_state_dict(state)
             for _ in range(2):             # twice: buffers, flags and epochs are reused
                 model.zero_grad()
                 loss = model.loss(mine[:, :-1], mine[:, 1:])
                 loss.backward()
             ff = model.layers[0].feed_forward
-            outs[tag] = (float(loss), ff.experts.w13.grad.float().clone(), ff.router.grad.float().clone(),
-                         model.token_embeddings.weight.grad.float().clone())
+            total = loss.detach().float().clone()
+            dist.all_reduce(total)
+            router = ff.router.grad.float().clone()
+            dist.all_reduce(router)             # the router is replicated: its gradient is the sum over ranks
+            report[tag] = {"loss": abs(float(total) / world - float(want_loss)),
+                           "w13": rel(ff.experts.w13.grad / world, want_w13), "router": rel(router / world, want_router)}
         torch.cuda.synchronize()
-
-        def rel(a, b):
-            return float((a - b).norm() / b.norm().clamp_min(1e-12))
-        results[rank] = {"loss": (outs["fused"][0], outs["nccl"][0]),
-                         "w13": rel(outs["fused"][1], outs["nccl"][1]), "router": rel(outs["fused"][2], outs["nccl"][2]),
-                         "emb": rel(outs["fused"][3], outs["nccl"][3]), "status": native.lib().ajb_check_status()}
+        results[rank] = {"report": report, "status": native.lib().ajb_check_status()}
     finally:
         dist.destroy_process_group()
 
@@ -117,5 +128,8 @@ def test_fused_expert_exchange_matches_all_to_all_path():
     for rank in range(2):
         out = results[rank]
         assert out["status"] == 0, out
-        assert abs(out["loss"][0] - out["loss"][1]) < 2e-2, out
-        assert out["w13"] < 3e-2 and out["router"] < 6e-2 and out["emb"] < 3e-2, out
+        fused, nccl = out["report"]["fused"], out["report"]["nccl"]
+        assert fused["loss"] < 3e-2 and nccl["loss"] < 3e-2, out
+        for key in ("w13", "router"):
+            assert fused[key] < 0.25 and nccl[key] < 0.25, out        # bf16 noise of this tiny model vs the fp32 oracle
+            assert fused[key] < 1.5 * nccl[key] + 0.02, out        # fp32 combine is at least as accurate as bf16 index_add
