@@ -51,6 +51,10 @@ struct Params {
   long long c_batch_stride;
   const int* valid_rows;
   int segment_rows;
+  // split-K (skinny problems): the K range is cut into `split_k` slices, slice s writes its partial product to
+  // c + s * split_stride (fp32 store epilogue) and a small kernel sums the slices afterwards.
+  int split_k;
+  long long split_stride;
   DeviceStatus* status;
 };
 
@@ -75,6 +79,11 @@ __device__ __forceinline__ void load_box(void* dst, const CUtensorMap* map, uint
 
 __device__ __forceinline__ bool decode_tile(const Params& p, int tile, int& b, int& tm, int& tn) {
   const int per_problem = p.tiles_m * p.tiles_n;
+  if (p.split_k > 1) {          // b carries the K slice
+    b = tile / per_problem;
+    tile_coords(tile - b * per_problem, p.tiles_m, p.tiles_n, tm, tn);
+    return true;
+  }
   b = tile / per_problem;
   tile_coords(tile - b * per_problem, p.tiles_m, p.tiles_n, tm, tn);
   if (p.valid_rows == nullptr) return true;
@@ -102,8 +111,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
-  const int num_kb = (p.k + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.batch * p.split_k;
+  const int total_kb = (p.k + BK - 1) / BK;
+  const int kb_per_split = (total_kb + p.split_k - 1) / p.split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -139,7 +149,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         int b, tm, tn;
         if (!decode_tile(p, tile, b, tm, tn)) continue;
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_begin = p.split_k > 1 ? b * kb_per_split : 0;
+        const int kb_end = p.split_k > 1 ? min(total_kb, kb_begin + kb_per_split) : total_kb;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kGemm, 1)) { ok = false; break; }
           uint8_t* sa = stage_base + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
@@ -147,15 +159,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) load_box<BATCHED>(sa + j * (BK * 128), &map_a, &full[stage], m0 + 64 * j, k0, b);
+            for (int j = 0; j < BM / 64; ++j) load_box<BATCHED>(sa + j * (BK * 128), &map_a, &full[stage], m0 + 64 * j, k0, p.split_k > 1 ? 0 : b);
           } else {
-            load_box<BATCHED>(sa, &map_a, &full[stage], k0, m0, b);
+            load_box<BATCHED>(sa, &map_a, &full[stage], k0, m0, p.split_k > 1 ? 0 : b);
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) load_box<BATCHED>(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0, b);
+            for (int j = 0; j < BN / 64; ++j) load_box<BATCHED>(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0, p.split_k > 1 ? 0 : b);
           } else {
-            load_box<BATCHED>(sb, &map_b, &full[stage], k0, n0, b);
+            load_box<BATCHED>(sb, &map_b, &full[stage], k0, n0, p.split_k > 1 ? 0 : b);
           }
           ++issued;
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
@@ -181,9 +193,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     int iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int num_kb = total_kb;
       {
         int b, tm, tn;
         if (!decode_tile(p, tile, b, tm, tn)) continue;
+        if (p.split_k > 1) num_kb = min(total_kb, (b + 1) * kb_per_split) - b * kb_per_split;
       }
       const int buf = iter & 1;
       const uint32_t use = (uint32_t)(iter >> 1);
@@ -237,7 +251,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!row_ok || col >= p.n) continue;
         const int valid = min(32, p.n - col);
         if (p.epilogue == kStoreBf16) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + b * p.c_batch_stride + (long long)row * p.ldc + col;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + b * (p.split_k > 1 ? p.split_stride : p.c_batch_stride) + (long long)row * p.ldc + col;
           if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -254,7 +268,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               if (j < valid) dst[j] = __float2bfloat16(__uint_as_float(v[j]));
           }
         } else {
-          float* dst = reinterpret_cast<float*>(p.c) + b * p.c_batch_stride + (long long)row * p.ldc + col;
+          float* dst = reinterpret_cast<float*>(p.c) + b * (p.split_k > 1 ? p.split_stride : p.c_batch_stride) + (long long)row * p.ldc + col;
           const bool accumulate = p.epilogue == kAccumF32;
           if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -293,6 +307,8 @@ struct BatchSpec {
   long long a_stride = 0, b_stride = 0, c_stride = 0;   // elements between consecutive problems
   const int* valid_rows = nullptr;
   int segment_rows = 0;
+  int split_k = 1;
+  long long split_stride = 0;
 };
 
 template <int BN, bool A_MN, bool B_MN, bool BATCHED>
@@ -331,8 +347,10 @@ static int launch(const void* a, const void* b, void* c, int m, int n, int k, lo
   p.c_batch_stride = spec.c_stride;
   p.valid_rows = spec.valid_rows;
   p.segment_rows = spec.segment_rows > 0 ? spec.segment_rows : m;
+  p.split_k = spec.split_k;
+  p.split_stride = spec.split_stride;
   p.status = device_status_buffer();
-  const long long tiles = (long long)p.tiles_m * p.tiles_n * spec.batch;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * spec.batch * spec.split_k;
   const int grid = tiles < sm_count() ? (int)tiles : sm_count();
   kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, p);
   AJB_CUDA_OK(cudaGetLastError());
@@ -358,6 +376,26 @@ static int dispatch(const void* a, const void* b, void* c, int m, int n, int k, 
     case 1: return launch<256, false, true, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
     case 2: return launch<256, true, false, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
     default: return launch<256, true, true, BATCHED>(a, b, c, m, n, k, lda, ldb, ldc, epilogue, spec, s);
+  }
+}
+
+// out[i] = sum_s partial[s * stride + i], fp32 -> bf16 (8 elements per thread)
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, long long vecs,
+                                     long long stride, int splits) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < splits; ++s) {
+      const float4 a = reinterpret_cast<const float4*>(partial + s * stride)[2 * i];
+      const float4 b = reinterpret_cast<const float4*>(partial + s * stride)[2 * i + 1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 q;
+    q.x = pack_bf16x2(acc[0], acc[1]);
+    q.y = pack_bf16x2(acc[2], acc[3]);
+    q.z = pack_bf16x2(acc[4], acc[5]);
+    q.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = q;
   }
 }
 
@@ -393,4 +431,26 @@ extern "C" int ajb_gemm_bf16_batched(const void* a, const void* b, void* c, int 
   spec.valid_rows = (const int*)valid_rows; spec.segment_rows = segment_rows;
   return gemm::dispatch<true>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, spec,
                               reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Skinny problems (few rows, e.g. decoding): C[m,n] bf16 = A[m,k] B[n,k]^T with the K range split over `split_k`
+// CTAs per output tile so that all SMs stream the weights. workspace: split_k * m * n floats. c must be contiguous.
+extern "C" int ajb_gemm_bf16_splitk(const void* a, const void* b, void* c, void* workspace, int m, int n, int k,
+                                    long long lda, long long ldb, int split_k, void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(m > 0 && n > 0 && k > 0 && split_k >= 1, "split-k gemm: bad problem");
+  AJB_REQUIRE(n % 8 == 0, "split-k gemm: n must be a multiple of 8");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (split_k == 1)
+    return gemm::dispatch<false>(a, b, c, m, n, k, lda, ldb, n, 0, 0, 0, gemm::BatchSpec(), s);
+  gemm::BatchSpec spec;
+  spec.split_k = split_k;
+  spec.split_stride = (long long)m * n;
+  int rc = gemm::dispatch<false>(a, b, workspace, m, n, k, lda, ldb, n, 0, 0, /*fp32 store*/ 2, spec, s);
+  if (rc) return rc;
+  const long long vecs = (long long)m * n / 8;
+  const int blocks = (int)((vecs + 255) / 256 < (long long)sm_count() * 8 ? (vecs + 255) / 256 : (long long)sm_count() * 8);
+  gemm::splitk_reduce_kernel<<<blocks, 256, 0, s>>>((const float*)workspace, (__nv_bfloat16*)c, vecs, (long long)m * n, split_k);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
 }

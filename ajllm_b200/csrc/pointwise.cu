@@ -59,9 +59,10 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 // ------------------------------------------------------------------------------------------ RMSNorm
 constexpr int kNormThreads = 256;
-constexpr int kNormMaxVec = 4;  // row cached in registers up to 256*4*8 = 8192 features
+constexpr int kNormVecLimit = 4;  // row cached in registers up to 256*4*8 = 8192 features (template: 1, 2 or 4 vectors per thread)
 
 // h = x (+ delta); y = h * rsqrt(mean(h^2) + eps) * gain. Writes h only when delta is given.
+template <int kNormMaxVec>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
                    const __nv_bfloat16* __restrict__ gain, __nv_bfloat16* __restrict__ y,
@@ -111,6 +112,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 
 // dx = rstd * (gain*dy - xhat * mean(gain*dy*xhat)) (+ dh), xhat = h * rstd.
 // Block b accumulates sum_rows dy*xhat for its rows into partial[b, :].
+template <int kNormMaxVec>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                    const __nv_bfloat16* __restrict__ gain, const float* __restrict__ rstd_in,
@@ -458,13 +460,16 @@ typedef __nv_bfloat16 bf16;
 
 extern "C" int ajb_rmsnorm_fwd(const void* x, const void* delta, const void* gain, void* y, void* h_out, void* rstd,
                                int rows, int dim, float eps, void* stream) {
-  AJB_REQUIRE(dim % 8 == 0 && dim <= kNormThreads * kNormMaxVec * 8, "rmsnorm: dim %d must be a multiple of 8 and <= %d",
-              dim, kNormThreads * kNormMaxVec * 8);
+  AJB_REQUIRE(dim % 8 == 0 && dim <= kNormThreads * kNormVecLimit * 8, "rmsnorm: dim %d must be a multiple of 8 and <= %d",
+              dim, kNormThreads * kNormVecLimit * 8);
   AJB_REQUIRE(delta == nullptr || h_out != nullptr, "rmsnorm: h_out is required when delta is given");
   if (rows <= 0) return 0;
   const int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
-  rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)delta, (const bf16*)gain,
-                                                                 (bf16*)y, (bf16*)h_out, (float*)rstd, rows, dim, eps);
+  const int vecs = (dim / 8 + kNormThreads - 1) / kNormThreads;
+#define AJB_NORM_FWD(V) rmsnorm_fwd_kernel<V><<<grid, kNormThreads, 0, STREAM(stream)>>>( \
+      (const bf16*)x, (const bf16*)delta, (const bf16*)gain, (bf16*)y, (bf16*)h_out, (float*)rstd, rows, dim, eps)
+  if (vecs <= 1) AJB_NORM_FWD(1); else if (vecs == 2) AJB_NORM_FWD(2); else AJB_NORM_FWD(4);
+#undef AJB_NORM_FWD
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -472,12 +477,14 @@ extern "C" int ajb_rmsnorm_fwd(const void* x, const void* delta, const void* gai
 // partial must hold nparts * dim floats; the launch uses exactly nparts blocks.
 extern "C" int ajb_rmsnorm_bwd(const void* dy, const void* h, const void* gain, const void* rstd, const void* dh,
                                void* dx, void* partial, int rows, int dim, int nparts, void* stream) {
-  AJB_REQUIRE(dim % 8 == 0 && dim <= kNormThreads * kNormMaxVec * 8, "rmsnorm_bwd: unsupported dim %d", dim);
+  AJB_REQUIRE(dim % 8 == 0 && dim <= kNormThreads * kNormVecLimit * 8, "rmsnorm_bwd: unsupported dim %d", dim);
   AJB_REQUIRE(nparts >= 1, "rmsnorm_bwd: nparts must be positive");
   if (rows <= 0) return 0;
-  rmsnorm_bwd_kernel<<<nparts, kNormThreads, 0, STREAM(stream)>>>((const bf16*)dy, (const bf16*)h, (const bf16*)gain,
-                                                                   (const float*)rstd, (const bf16*)dh, (bf16*)dx,
-                                                                   (float*)partial, rows, dim);
+  const int vecs = (dim / 8 + kNormThreads - 1) / kNormThreads;
+#define AJB_NORM_BWD(V) rmsnorm_bwd_kernel<V><<<nparts, kNormThreads, 0, STREAM(stream)>>>( \
+      (const bf16*)dy, (const bf16*)h, (const bf16*)gain, (const float*)rstd, (const bf16*)dh, (bf16*)dx, (float*)partial, rows, dim)
+  if (vecs <= 1) AJB_NORM_BWD(1); else if (vecs == 2) AJB_NORM_BWD(2); else AJB_NORM_BWD(4);
+#undef AJB_NORM_BWD
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }

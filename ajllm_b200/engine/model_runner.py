@@ -112,7 +112,11 @@ class ModelRunner:
             cached_rows = cached_tables = None
             if cached_idx:
                 cached_rows = torch.tensor(cached_idx, dtype=torch.long, device=dev)
-                cached_tables = tables.index_select(0, torch.tensor(cached_items, dtype=torch.long, device=dev)).contiguous()
+                cached_tables = tables if len(cached_items) == len(q_lens) else \
+                    tables.index_select(0, torch.tensor(cached_items, dtype=torch.long, device=dev)).contiguous()
+                attn0 = model.layers[0].attention
+                paged_plan = serving.PagedPlan(cached_tables, cached_qlens, cached_ctx, attn0.num_heads, attn0.num_kv_heads)
+                all_cached = len(cached_idx) == len(tokens)
         stream = model.token_embeddings(ids)
         if model.position_embeddings is not None:
             stream = stream + model.position_embeddings(pos)
@@ -131,9 +135,13 @@ class ModelRunner:
                 for lo, hi in fresh:          # prompts starting from an empty cache: tiled kernel on the packed rows
                     attended[lo:hi] = serving.prompt_attention(qkv[lo:hi], attn.num_heads, attn.num_kv_heads, attn.head_dim)
                 if cached_rows is not None:
-                    part = serving.paged_attention(q.index_select(0, cached_rows).contiguous(), cache.keys[index],
-                                                   cache.values[index], cached_tables, None, None, cached_qlens, cached_ctx)
-                    attended.index_copy_(0, cached_rows, part.reshape(part.shape[0], -1))
+                    if all_cached:          # pure decode / verify step: no gather, no scatter
+                        attended = serving.paged_attention_planned(q.contiguous(), cache.keys[index], cache.values[index],
+                                                                   paged_plan).reshape(ids.shape[0], -1)
+                    else:
+                        part = serving.paged_attention_planned(q.index_select(0, cached_rows).contiguous(), cache.keys[index],
+                                                               cache.values[index], paged_plan)
+                        attended.index_copy_(0, cached_rows, part.reshape(part.shape[0], -1))
             else:
                 q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
                 if attn.use_rope:

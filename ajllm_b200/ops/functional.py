@@ -143,16 +143,48 @@ class _LinearFn(torch.autograd.Function):
         return grad_x, grad_w
 
 
+_SPLITK_WORKSPACE: dict = {}
+_SKINNY_ROWS = 512
+
+
+def linear_skinny(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Forward-only ``x2 @ weight.T`` for few rows (decoding): the K range is split over enough CTAs to keep
+    every SM streaming weights; fp32 partial products are summed by a second small kernel."""
+    m, k = x2.shape
+    n = weight.shape[0]
+    tiles = ((m + 127) // 128) * ((n + 255) // 256)
+    k_blocks = (k + 63) // 64
+    want = max(1, min(k_blocks // 4, (148 + tiles - 1) // tiles))
+    per = (k_blocks + want - 1) // want
+    split = (k_blocks + per - 1) // per
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=x2.device)
+    workspace = None
+    if split > 1:
+        key = (x2.device.index, )
+        need = split * m * n
+        workspace = _SPLITK_WORKSPACE.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.float32, device=x2.device)
+            _SPLITK_WORKSPACE[key] = workspace
+    native.call("ajb_gemm_bf16_splitk", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), native.ptr(workspace), m, n, k,
+                x2.stride(0), weight.stride(0), split, native.stream_ptr())
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``x @ weight.T`` for a bias-free ``[out, in]`` weight (``ajllm/modeling/layers.py:33``)."""
     if _is_cuda(x) and x.dtype == torch.bfloat16:
+        if not torch.is_grad_enabled() and weight.shape[0] % 8 == 0:
+            x2 = x.reshape(-1, x.shape[-1])
+            if x2.shape[0] <= _SKINNY_ROWS and x2.stride(-1) == 1 and weight.stride(-1) == 1:
+                return linear_skinny(x2, weight).view(*x.shape[:-1], weight.shape[0])
         return _LinearFn.apply(x, weight)
     return reference.linear(x, weight)
 
 
 # ----------------------------------------------------------------------------- RMSNorm (+ residual)
 
-_NORM_BWD_ROWS_PER_BLOCK = 64
+_NORM_BWD_ROWS_PER_BLOCK = 16
 
 
 def _norm_bwd_partials(rows: int) -> int:

@@ -30,6 +30,7 @@ _SIGNATURES: dict[str, list] = {
                       c_int, c_int, c_int, c_void],
     "ajb_gemm_bf16_batched": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_long, c_long,
                               c_long, c_int, c_int, c_int, c_void, c_int, c_void],
+    "ajb_gemm_bf16_splitk": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_int, c_void],
     "ajb_rmsnorm_fwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float, c_void],
     "ajb_rmsnorm_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_void],
     "ajb_colsum_f32": [c_void, c_void, c_int, c_int, c_int, c_void],

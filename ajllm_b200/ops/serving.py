@@ -20,36 +20,53 @@ def rope_packed_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positi
                 num_heads, num_kv_heads, head_dim, qkv.stride(0), 0, native.stream_ptr())
 
 
-def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, block_tables: torch.Tensor,
-                    context_lens: torch.Tensor, q_lens: torch.Tensor, q_lens_host: list[int],
-                    context_lens_host: list[int]) -> torch.Tensor:
-    """Ragged decode / verify attention. ``q`` is ``[total_rows, Hq, hd]``; launches are grouped by the
-    number of new rows per sequence, and long row runs are cut into chunks the kernel can hold."""
+class PagedPlan:
+    """Launch plan of one ragged decode / verify batch: sequences grouped by their number of new rows, with the
+    block tables, row offsets and context lengths of every group already on the device. Built once per engine
+    step and reused by every layer."""
+
+    def __init__(self, block_tables: torch.Tensor, q_lens_host: list[int], context_lens_host: list[int], heads: int,
+                 kv_heads: int) -> None:
+        group = heads // kv_heads
+        max_q = max(1, _MAX_ROWS // group)
+        classes: dict[int, list[tuple[int, int, int]]] = {}
+        cursor = 0
+        for i, (n, ctx) in enumerate(zip(q_lens_host, context_lens_host)):
+            for a in range(0, n, max_q):
+                b = min(n, a + max_q)
+                classes.setdefault(b - a, []).append((i, cursor + a, ctx - (n - b)))
+            cursor += n
+        self.total_rows = cursor
+        device = block_tables.device
+        self.launches = []
+        identity = list(range(block_tables.shape[0]))
+        for q_len, items in classes.items():
+            rows = [it[0] for it in items]
+            tables = block_tables if rows == identity else \
+                block_tables.index_select(0, torch.tensor(rows, dtype=torch.long, device=device)).contiguous()
+            packed = torch.tensor([[it[1] for it in items], [it[2] for it in items]], dtype=torch.int32, device=device)
+            self.launches.append((q_len, len(items), tables, packed[0], packed[1]))
+
+
+def paged_attention_planned(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, plan: PagedPlan) -> torch.Tensor:
     total, heads, head_dim = q.shape
     kv_heads = key_cache.shape[2]
-    group = heads // kv_heads
-    max_q = max(1, _MAX_ROWS // group)
     out = torch.empty_like(q)
-    # (q_len class) -> lists of (table row, q_start, effective context)
-    classes: dict[int, list[tuple[int, int, int]]] = {}
-    cursor = 0
-    for i, (n, ctx) in enumerate(zip(q_lens_host, context_lens_host)):
-        for a in range(0, n, max_q):
-            b = min(n, a + max_q)
-            classes.setdefault(b - a, []).append((i, cursor + a, ctx - (n - b)))
-        cursor += n
     scale = 1.0 / math.sqrt(head_dim)
     num_blocks, block_size = key_cache.shape[0], key_cache.shape[1]
-    for q_len, items in classes.items():
-        rows = torch.tensor([it[0] for it in items], dtype=torch.long, device=q.device)
-        tables = block_tables.index_select(0, rows).contiguous() if len(items) != block_tables.shape[0] or \
-            [it[0] for it in items] != list(range(block_tables.shape[0])) else block_tables
-        starts = torch.tensor([it[1] for it in items], dtype=torch.int32, device=q.device)
-        ctxs = torch.tensor([it[2] for it in items], dtype=torch.int32, device=q.device)
+    for q_len, count, tables, starts, ctxs in plan.launches:
         native.call("ajb_paged_attention", q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), tables.data_ptr(),
-                    ctxs.data_ptr(), starts.data_ptr(), out.data_ptr(), len(items), num_blocks, block_size,
+                    ctxs.data_ptr(), starts.data_ptr(), out.data_ptr(), count, num_blocks, block_size,
                     tables.shape[1], heads, kv_heads, head_dim, q_len, scale, native.stream_ptr())
     return out
+
+
+def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, block_tables: torch.Tensor,
+                    context_lens, q_lens, q_lens_host: list[int], context_lens_host: list[int]) -> torch.Tensor:
+    """Ragged decode / verify attention. ``q`` is ``[total_rows, Hq, hd]``; launches are grouped by the
+    number of new rows per sequence, and long row runs are cut into chunks the kernel can hold."""
+    plan = PagedPlan(block_tables, q_lens_host, context_lens_host, q.shape[1], key_cache.shape[2])
+    return paged_attention_planned(q, key_cache, value_cache, plan)
 
 
 def prompt_attention(qkv_rows: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int) -> torch.Tensor:

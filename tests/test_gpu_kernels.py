@@ -228,3 +228,16 @@ def test_batched_gemm_with_row_counts():
     y.backward(g)
     assert _rel_err(xg.grad, torch.einsum("ern,enk->erk", g.float(), w.float())) < 5e-3
     assert _rel_err(wg.grad, torch.einsum("ern,erk->enk", g.float(), x.float())) < 5e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (128, 6144, 4096), (256, 4096, 14336), (40, 1000, 264)])
+def test_split_k_linear_for_few_rows(m, n, k):
+    from ajllm_b200.ops.functional import linear_skinny
+
+    torch.manual_seed(13)
+    x = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    w = (torch.randn(n, k, device=_dev()) * 0.05).to(torch.bfloat16)
+    got = linear_skinny(x, w)
+    assert _rel_err(got, x.float() @ w.float().t()) < 5e-3
+    with torch.no_grad():
+        assert _rel_err(ops.linear(x, w), x.float() @ w.float().t()) < 5e-3
