@@ -1,7 +1,8 @@
 // FlashAttention forward for sm_100a: S = Q K^T and O += P V run on tcgen05 with S (double
 // buffered) and O resident in tensor memory; K/V tiles arrive by TMA; four softmax warps own one
 // query row per thread (online max / sum in registers), write P as a swizzled bf16 operand tile in
-// shared memory and rescale O in tensor memory only when a row maximum moved.
+// shared memory (double buffered) and rescale O in tensor memory only when a row's reference maximum has to
+// move by more than 2^8.
 //
 // Inputs are the packed projection rows [B, T, (Hq + 2 Hkv) * hd] (q heads | k heads | v heads) after
 // RoPE; query head h reads KV head h / (Hq / Hkv). Outputs: O [B, T, Hq * hd] (bf16) and the row
@@ -20,7 +21,7 @@ template <int HD>
 struct FwdCfg {
   static constexpr int kTileBytes = BLOCK_N * HD * 2;       // one Q, K or V tile
   static constexpr int kPBytes = BLOCK_M * BLOCK_N * 2;
-  static constexpr int kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*2 x (K,V)*/ + kPBytes + 256;
+  static constexpr int kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*2 x (K,V)*/ + 2 * kPBytes + 256;
   static constexpr int kTmemCols = 512;
   static constexpr int kOCol = 256;  // S0 at 0, S1 at 128, O at 256
 };
@@ -50,7 +51,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Cfg::kTileBytes;               // stage s: K at sKV + s*2*tile, V right after
   uint8_t* sP = sKV + 4 * Cfg::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::kPBytes);
   if (smem_misaligned(smem, p.status, kFlashFwd, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* q_full = bars;            // 1
   uint64_t* kv_full = bars + 1;       // 2
@@ -148,7 +149,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
 #pragma unroll
         for (int k = 0; k < BLOCK_N / 16; ++k) {
           const uint32_t pbox = (uint32_t)(k / 4) * (BLOCK_M * 128), poff = (uint32_t)(k % 4) * 32;
-          umma_f16(tmem_base + Cfg::kOCol, desc_k_major(aP + pbox, poff), desc_mn_major(aV, BLOCK_N * 128, k * 16),
+          umma_f16(tmem_base + Cfg::kOCol, desc_k_major(aP + (uint32_t)((j & 1) * Cfg::kPBytes) + pbox, poff), desc_mn_major(aV, BLOCK_N * 128, k * 16),
                    idesc_o, (j | k) != 0);
         }
         tc_commit(pv_done);
@@ -183,22 +184,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[s]);   // S(j) is in registers; its TMEM buffer may be overwritten
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sv[c][i]);
-          if (need_mask && (k0 + c * 32 + i > k_max)) x = -INFINITY;
-          sv[c][i] = __float_as_uint(x);
-          m_tile = fmaxf(m_tile, x);
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(sv[c][i]);
+            if (k0 + c * 32 + i > k_max) x = -INFINITY;
+            sv[c][i] = __float_as_uint(x);
+            m_tile = fmaxf(m_tile, x);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sv[c][i]));
         }
       }
-      const float m_new = fmaxf(m_run, m_tile);
+      // The reference point m_run of the exponentials only follows the true maximum when it would otherwise
+      // fall behind by more than kLazyBits powers of two: exp2((s - m_run) * scale) then stays below 2^kLazyBits,
+      // harmless in bf16 / fp32, and the rescaling of O in tensor memory (a round trip through registers, and
+      // a wait for the previous P V product) becomes rare. The final O / l is exact either way.
+      constexpr float kLazyBits = 8.0f;
+      const bool moved = (m_tile - m_run) * sl > kLazyBits;       // first tile: m_run = -inf -> true
+      const float m_new = moved ? m_tile : m_run;
       const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;   // fully masked row (only when q_pos >= seq)
-      const float alpha = exp2f((m_run - m_safe) * sl);            // m_run = -inf -> 0
+      const float alpha = moved ? exp2f((m_run - m_safe) * sl) : 1.0f;   // m_run = -inf -> 0
       const float neg = -m_safe * sl;
       float l_tile = 0.0f;
-      // pass 2: probabilities, packed to bf16 (the rounded values feed both the sum and the PV product)
+      // pass 2: probabilities, packed to bf16
       uint32_t pk[64];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -206,28 +221,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
         for (int i = 0; i < 32; i += 2) {
           const float p0 = exp2f(fmaf(__uint_as_float(sv[c][i]), sl, neg));
           const float p1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), sl, neg));
-          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          const float2 back = __bfloat1622float2(h);
-          l_tile += back.x + back.y;
-          pk[c * 16 + i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          l_tile += p0 + p1;
+          pk[c * 16 + i / 2] = pack_bf16x2(p0, p1);
         }
       }
       l_run = l_run * alpha + l_tile;
-      const bool moved = m_new != m_run;
       m_run = m_new;
-      // P and O belong to the previous PV product until it has completed
-      if (j > 0 && !mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kFlashFwd, 7)) { ok = false; break; }
-      tc_fence_after_sync();
-      // P -> shared memory, K-major 128-byte-swizzled operand tile: 2 boxes of [128 rows x 64 keys]
+      // P(j) goes to buffer j & 1. Its previous reader, the product P V of tile j - 2, finished before S(j) did
+      // (the tensor core executes in issue order), so no wait is needed here.
+      uint8_t* sPj = sP + (j & 1) * Cfg::kPBytes;
 #pragma unroll
       for (int ch = 0; ch < 16; ++ch) {
         const int box = ch >> 3, chunk = ch & 7;
         uint4 val = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        uint8_t* dst = sP + box * (BLOCK_M * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
+        uint8_t* dst = sPj + box * (BLOCK_M * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
         *reinterpret_cast<uint4*>(dst) = val;
       }
-      // rescale O when some row of this warp moved its maximum
+      // rescale O when some row of this warp moved its reference point; O belongs to the previous P V product
+      // until that has completed
       if (j > 0 && __any_sync(0xffffffffu, moved)) {
+        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kFlashFwd, 7)) { ok = false; break; }
+        tc_fence_after_sync();
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t ov[32];
