@@ -216,9 +216,11 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             m_tile = fmaxf(m_tile, x);
           }
         }
-        const float m_new = fmaxf(m_run, m_tile);
+        // lazy reference maximum (see flash_fwd.cu): O is rescaled only when a row would overflow 2^8
+        moved = (m_tile - m_run) * sl > 8.0f;
+        const float m_new = moved ? m_tile : m_run;
         const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
-        alpha = exp2f((m_run - m_safe) * sl);
+        alpha = moved ? exp2f((m_run - m_safe) * sl) : 1.0f;
         const float neg = -m_safe * sl;
         float l_tile = 0.0f;
 #pragma unroll
@@ -227,14 +229,11 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           for (int i = 0; i < 32; i += 2) {
             const float p0 = exp2f(fmaf(__uint_as_float(sv[c][i]), sl, neg));
             const float p1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), sl, neg));
-            const __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
-            const float2 back = __bfloat1622float2(hb);
-            l_tile += back.x + back.y;
-            pk[c * 16 + i / 2] = *reinterpret_cast<const uint32_t*>(&hb);
+            l_tile += p0 + p1;
+            pk[c * 16 + i / 2] = pack_bf16x2(p0, p1);
           }
         }
         l_run = l_run * alpha + l_tile;
-        moved = m_new != m_run;
         m_run = m_new;
       } else {
 #pragma unroll
