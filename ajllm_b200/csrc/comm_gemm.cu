@@ -2,6 +2,7 @@
 //
 //   ag_gemm : C[M, N] = gather_rows(A_shards)[M, K] * op(B)      (column-parallel: all-gather -> GEMM)
 //   gemm_rs : C_local[M/tp, N] = reduce_scatter_rows(A[M, K] * op(B))   (row-parallel: GEMM -> reduce-scatter)
+//   gemm_ar : C[M, N] = sum over ranks of A[M, K] * op(B)                (row-parallel: GEMM -> all-reduce)
 //
 // Both are one persistent kernel per rank built on the same tcgen05 main loop as gemm_bf16.cu
 // (TMA ring -> tcgen05.mma -> TMEM -> epilogue warps).
@@ -16,6 +17,10 @@
 // each bf16 partial tile straight into the owning rank's symmetric receive buffer (slot = this rank)
 // and bumps a counter there; after its last tile every CTA waits until all partials of its own rows
 // have arrived and sums them in fp32 into the local output.
+//
+// gemm_ar (decoding, where M is a few hundred rows at most): the same epilogue stores each partial tile
+// into every rank's receive buffer (slot = this rank), and the closing reduction sums all tp slots over
+// the whole [M, N] output, so the partial products cross NVLink once and no separate collective runs.
 //
 // Every wait on another CTA or another GPU is bounded (see common.cuh); on expiry the kernel records a
 // status word, skips the dependent work and exits through the normal teardown.
@@ -44,7 +49,7 @@ constexpr int kCopyPiece = 32768;                       // bytes per bulk copy
 constexpr int kCopyBufs = (kStages * kStageBytes + kEpiBytes) / kCopyPiece;   // 6 pieces in flight per copy CTA
 constexpr int kQueue = 4;                               // depth of the per-CTA tile queue
 
-enum Mode : int { kAllGather = 0, kReduceScatter = 1 };
+enum Mode : int { kAllGather = 0, kReduceScatter = 1, kAllReduce = 2 };
 
 struct Params {
   int mode;
@@ -57,7 +62,7 @@ struct Params {
   void* gathered;                        // local [m, k]
   unsigned int* shard_flags;             // local, zeroed by the host before launch, one per shard
   // reduce-scatter
-  void* recv_ptrs[kMaxRanks];            // each rank's symmetric [tp, m_local, n] receive buffer
+  void* recv_ptrs[kMaxRanks];            // each rank's symmetric [tp, m_local, n] receive buffer (all-reduce: m_local = m)
   unsigned int* counter_ptrs[kMaxRanks]; // each rank's symmetric arrival counters, one per source rank
   unsigned int expected_count;           // counter value that means "all partials of this call arrived"
   void* out_local;                       // [m_local, n] bf16 (reduce-scatter) / [m, n] bf16 (all-gather)
@@ -240,10 +245,11 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const bool is_copy_cta = p.mode == kAllGather && (int)blockIdx.x < p.copy_ctas;
   const int tiles_m_local = p.m_local / BM;
   const int tiles_n = (p.n + BN - 1) / BN;
-  const int num_tiles = tiles_m_local * p.tp * tiles_n;
+  const int shards = p.mode == kAllReduce ? 1 : p.tp;     // all-reduce: one "shard" of m_local = m rows
+  const int num_tiles = tiles_m_local * shards * tiles_n;
   const int num_kb = (p.k + BK - 1) / BK;
   // all-gather: the local shard is ready first. reduce-scatter: the rows this rank owns come last.
-  const int first_shard = p.mode == kAllGather ? p.rank : (p.rank + 1) % p.tp;
+  const int first_shard = p.mode == kAllGather ? p.rank : (p.mode == kAllReduce ? 0 : (p.rank + 1) % p.tp);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -293,7 +299,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         mbar_arrive(&q_full[slot]);
         if (tile >= num_tiles) break;
         int shard, tm, tn;
-        tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, p.mode == kReduceScatter, shard, tm, tn);
+        tile_coords(tile, tiles_m_local, tiles_n, shards, first_shard, p.mode == kReduceScatter, shard, tm, tn);
         if (p.mode == kAllGather && shard != ready_shard) {
           if (!wait_ge(p.shard_flags + shard, (unsigned)p.copy_ctas, false, abort_flag, p.status, 10)) { ok = false; break; }
           fence_proxy_async_all();      // copied rows were written through the async proxy of other CTAs
@@ -369,10 +375,15 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quarter = warp & 3;
     uint8_t* my_row = epi_base + (quarter * 32 + lane) * kEpiRowPitch;    // this lane's staged output row
     bool ok = true;
-    int pending_shard = -1;          // reduce-scatter: tile whose bulk stores are in flight and not yet announced
+    int pending_shard = -1;          // tile whose bulk stores are in flight and not yet announced (-1: none, tp: to all ranks)
     auto announce = [&](int shard_done) {
       __syncwarp();                  // every lane's rows of that tile are complete in (peer) memory
-      if (shard_done >= 0 && lane == 0) red_release_sys_add(p.counter_ptrs[shard_done] + p.rank, 1u);
+      if (shard_done < 0 || lane != 0) return;
+      if (shard_done < p.tp) {
+        red_release_sys_add(p.counter_ptrs[shard_done] + p.rank, 1u);
+      } else {
+        for (int r = 0; r < p.tp; ++r) red_release_sys_add(p.counter_ptrs[r] + p.rank, 1u);
+      }
     };
     for (uint32_t qi = 0; ok; ++qi) {
       const int slot = qi % kQueue;
@@ -384,7 +395,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int buf = qi & 1;
       const uint32_t use = qi >> 1;
       int shard, tm, tn;
-      tile_coords(tile, tiles_m_local, tiles_n, p.tp, first_shard, p.mode == kReduceScatter, shard, tm, tn);
+      tile_coords(tile, tiles_m_local, tiles_n, shards, first_shard, p.mode == kReduceScatter, shard, tm, tn);
       if (!mbar_wait(&acc_full[buf], use & 1, abort_flag, p.status, kCommGemm, 4)) { ok = false; break; }
       tc_fence_after_sync();
       bulk_wait_read_all();          // the previous tile's store has read this lane's staging row
@@ -413,20 +424,31 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int row = tm * BM + quarter * 32 + lane;
       const int col0 = tn * BN;
       const int bytes = min(BN, p.n - col0) * 2;
-      __nv_bfloat16* dst;
-      if (p.mode == kAllGather) {
-        dst = reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row * p.ldc + col0;
+      if (p.mode == kAllReduce) {
+        // the partial tile goes to every rank's receive buffer (own included), slot = this rank
+        if (bytes > 0) {
+          for (int r = 0; r < p.tp; ++r) {
+            const int peer = (p.rank + r) % p.tp;
+            bulk_s2g(reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[peer]) + ((long long)p.rank * p.m_local + row) * p.n + col0,
+                     my_row, (uint32_t)bytes);
+          }
+        }
       } else {
-        // partial sums of shard `shard` go to that rank's receive buffer, slot = this rank
-        dst = reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[shard]) +
-              ((long long)p.rank * p.m_local + (row - shard * p.m_local)) * p.n + col0;
+        __nv_bfloat16* dst;
+        if (p.mode == kAllGather) {
+          dst = reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row * p.ldc + col0;
+        } else {
+          // partial sums of shard `shard` go to that rank's receive buffer, slot = this rank
+          dst = reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[shard]) +
+                ((long long)p.rank * p.m_local + (row - shard * p.m_local)) * p.n + col0;
+        }
+        if (bytes > 0) bulk_s2g(dst, my_row, (uint32_t)bytes);
       }
-      if (bytes > 0) bulk_s2g(dst, my_row, (uint32_t)bytes);
       bulk_commit();
       // the previous tile had a whole tile time to land: wait for it (not for the one just issued) and announce it
       bulk_wait_all_but_latest();
       announce(pending_shard);
-      pending_shard = p.mode == kReduceScatter ? shard : -1;
+      pending_shard = p.mode == kReduceScatter ? shard : (p.mode == kAllReduce ? p.tp : -1);
     }
     bulk_wait_all();
     announce(pending_shard);
@@ -439,8 +461,8 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tmem_dealloc(tmem_base, 2 * BN);
   }
 
-  if (p.mode == kReduceScatter) {
-    // ---- sum the tp partial copies of the rows this rank owns (fp32) into the local output
+  if (p.mode != kAllGather) {
+    // ---- sum the tp partial copies of the rows this rank owns (all-reduce: of all rows) (fp32) into the local output
     int* arrived = reinterpret_cast<int*>(epi_base);
     if (threadIdx.x == 0) {
       bool ok = *abort_flag == 0;
@@ -494,9 +516,9 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 struct AjbCommArgs {
   int mode, m, n, k, tp, rank, b_mn_major, copy_ctas;
   long long ldb, ldc;
-  const void* a;                 // reduce-scatter: local [m, k] activations; all-gather: unused
+  const void* a;                 // reduce-scatter, all-reduce: local [m, k] activations; all-gather: unused
   const void* b;                 // local weight shard
-  void* out;                     // all-gather: [m, n]; reduce-scatter: [m / tp, n]
+  void* out;                     // all-gather, all-reduce: [m, n]; reduce-scatter: [m / tp, n]
   void* gathered;                // all-gather: local [m, k] buffer that receives every shard
   const void* stage_ptrs[8];
   void* recv_ptrs[8];
@@ -506,6 +528,7 @@ struct AjbCommArgs {
   unsigned int* shard_flags;     // local scratch (>= 8 words) + 1 word CTA counter at index 8
   unsigned int expected_count;
   unsigned int epoch;
+  int a_rows;                    // all-reduce: rows of `a` that exist (<= m; the tiles above them read zeros); 0 means m
 };
 
 extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
@@ -513,14 +536,18 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   using namespace ajb::comm;
   const AjbCommArgs& a = *args;
   AJB_REQUIRE(a.tp >= 2 && a.tp <= kMaxRanks, "comm_gemm: tp must be in [2, %d]", kMaxRanks);
-  AJB_REQUIRE(a.m % a.tp == 0 && (a.m / a.tp) % BM == 0, "comm_gemm: rows per rank (%d / %d) must be a multiple of %d",
-              a.m, a.tp, BM);
+  if (a.mode == kAllReduce) {
+    AJB_REQUIRE(a.m % BM == 0, "comm_gemm: all-reduce rows (%d) must be a multiple of %d", a.m, BM);
+  } else {
+    AJB_REQUIRE(a.m % a.tp == 0 && (a.m / a.tp) % BM == 0, "comm_gemm: rows per rank (%d / %d) must be a multiple of %d",
+                a.m, a.tp, BM);
+  }
   AJB_REQUIRE(a.k % 8 == 0 && a.n % 8 == 0, "comm_gemm: n and k must be multiples of 8");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   Params p;
   memset(&p, 0, sizeof(p));
   p.mode = a.mode; p.m = a.m; p.n = a.n; p.k = a.k; p.tp = a.tp; p.rank = a.rank;
-  p.m_local = a.m / a.tp;
+  p.m_local = a.mode == kAllReduce ? a.m : a.m / a.tp;
   p.copy_ctas = a.mode == kAllGather ? a.copy_ctas : 0;
   for (int r = 0; r < a.tp; ++r) {
     p.stage_ptrs[r] = a.stage_ptrs[r];
@@ -542,7 +569,9 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
 
   const void* a_ptr = a.mode == kAllGather ? a.gathered : a.a;
   CUtensorMap map_a, map_b;
-  int rc = make_tensor_map_2d(&map_a, a_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.m, a.k, (uint64_t)a.k * 2, BM, 64);
+  const int a_rows = (a.mode == kAllReduce && a.a_rows > 0) ? a.a_rows : a.m;
+  AJB_REQUIRE(a_rows <= a.m, "comm_gemm: a_rows (%d) exceeds m (%d)", a_rows, a.m);
+  int rc = make_tensor_map_2d(&map_a, a_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, a.k, (uint64_t)a.k * 2, BM, 64);
   if (rc) return rc;
   if (a.b_mn_major) rc = make_tensor_map_2d(&map_b, a.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.k, a.n, a.ldb * 2, BK, 64);
   else              rc = make_tensor_map_2d(&map_b, a.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.k, a.ldb * 2, BN, 64);

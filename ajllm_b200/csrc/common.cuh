@@ -38,7 +38,7 @@ const char* last_error();
   } while (0)
 
 // Device status words written by kernels whose bounded waits expired. Index = kernel id.
-enum KernelId : int { kGemm = 0, kFlashFwd = 1, kFlashBwdKV = 2, kFlashBwdQ = 3, kCommGemm = 4, kNumKernelIds = 16 };
+enum KernelId : int { kGemm = 0, kFlashFwd = 1, kFlashBwdKV = 2, kFlashBwdQ = 3, kCommGemm = 4, kFlashBwdFused = 8, kNumKernelIds = 16 };
 struct DeviceStatus {
   unsigned int code;    // 0 = ok, otherwise (stage << 8) | kernel id + 1
   unsigned int block;
@@ -214,6 +214,19 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// A operand read from tensor memory (lane = row of A; 16-bit elements packed two per 32-bit column along K,
+// even k in the low half), B from shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Same for e4m3/e5m2 inputs.
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                         uint32_t accumulate) {
@@ -239,6 +252,28 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// Vector reduction into global memory: four consecutive fp32 values (16-byte aligned address).
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -278,6 +313,48 @@ __device__ __forceinline__ uint64_t desc_k_major(uint32_t tile_addr, uint32_t k_
 // (box_bytes = k rows * 128). `k_index` is the first k row of this MMA (multiple of 8).
 __device__ __forceinline__ uint64_t desc_mn_major(uint32_t tile_addr, uint32_t box_bytes, uint32_t k_index) {
   return make_smem_desc(tile_addr + k_index * 128, box_bytes, 1024);
+}
+
+// ---- lean descriptor arithmetic for MMA issue loops
+// One thread issues every tcgen05.mma of a CTA, and a 128 x 128 x 16 product takes only 64 cycles, so the
+// issue loop has a budget of a handful of instructions per product. All tiles here share the upper
+// descriptor word (1024-byte row groups, version 1, 128-byte swizzle); the lower word is the start
+// address in 16-byte units plus the leading-dimension offset, so stepping through a tile is one add.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_k_major(uint32_t tile_addr) {
+  return ((tile_addr & 0x3ffff) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t desc_lo_mn_major(uint32_t tile_addr, uint32_t box_bytes) {
+  return ((tile_addr & 0x3ffff) >> 4) | ((box_bytes >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t desc_at(uint32_t lo, uint32_t byte_offset) {
+  return (uint64_t(kDescHi) << 32) | (lo + (byte_offset >> 4));
+}
+// Byte offset of k-step `k` (16 elements) inside a K-major tile whose 64-element boxes are `box_bytes` apart.
+__host__ __device__ constexpr uint32_t k_major_step(int k, uint32_t box_bytes) {
+  return uint32_t(k / 4) * box_bytes + uint32_t(k % 4) * 32u;
+}
+// Byte offset of k-step `k` inside an MN-major tile (16 rows of 128 bytes per step).
+__host__ __device__ constexpr uint32_t mn_major_step(int k) { return uint32_t(k) * 2048u; }
+
+// Products with the accumulate flag fixed at compile time (no predicate set-up from a register).
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_f16_c(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+  if (kAccumulate)
+    asm volatile("{\n.reg .pred p;\nsetp.eq.u32 p, 1, 1;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+                 "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
+  else
+    asm volatile("{\n.reg .pred p;\nsetp.eq.u32 p, 1, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+                 "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_f16_ts_c(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
+  if (kAccumulate)
+    asm volatile("{\n.reg .pred p;\nsetp.eq.u32 p, 1, 1;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+                 "r"(tmem_a), "l"(desc_b), "r"(idesc) : "memory");
+  else
+    asm volatile("{\n.reg .pred p;\nsetp.eq.u32 p, 1, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+                 "r"(tmem_a), "l"(desc_b), "r"(idesc) : "memory");
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -1,8 +1,9 @@
 // FlashAttention forward for sm_100a: S = Q K^T and O += P V run on tcgen05 with S (double
-// buffered) and O resident in tensor memory; K/V tiles arrive by TMA; four softmax warps own one
-// query row per thread (online max / sum in registers), write P as a swizzled bf16 operand tile in
-// shared memory (double buffered) and rescale O in tensor memory only when a row's reference maximum has to
-// move by more than 2^8.
+// buffered) and O resident in tensor memory; K/V tiles arrive by TMA; two groups of four softmax
+// warps each own one half of the 128 key columns of a tile (one query row per thread, online max /
+// sum in registers, the row maximum of the two halves exchanged through shared memory), write P as a
+// swizzled bf16 operand tile in shared memory (double buffered) and rescale O in tensor memory only
+// when a row's reference maximum has to move by more than 2^8.
 //
 // Inputs are the packed projection rows [B, T, (Hq + 2 Hkv) * hd] (q heads | k heads | v heads) after
 // RoPE; query head h reads KV head h / (Hq / Hkv). Outputs: O [B, T, Hq * hd] (bf16) and the row
@@ -14,14 +15,15 @@ namespace flash {
 
 constexpr int BLOCK_M = 128;  // queries per CTA
 constexpr int BLOCK_N = 128;  // keys per step
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // TMA warp, MMA warp, 2 x 4 softmax warps
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int HD>
 struct FwdCfg {
   static constexpr int kTileBytes = BLOCK_N * HD * 2;       // one Q, K or V tile
   static constexpr int kPBytes = BLOCK_M * BLOCK_N * 2;
-  static constexpr int kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*2 x (K,V)*/ + 2 * kPBytes + 256;
+  static constexpr int kExchangeBytes = 2 * 2 * BLOCK_M * 4;   // [parity][column half][row] partial row maxima
+  static constexpr int kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*2 x (K,V)*/ + 2 * kPBytes + kExchangeBytes + 256;
   static constexpr int kTmemCols = 512;
   static constexpr int kOCol = 256;  // S0 at 0, S1 at 128, O at 256
 };
@@ -51,7 +53,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Cfg::kTileBytes;               // stage s: K at sKV + s*2*tile, V right after
   uint8_t* sP = sKV + 4 * Cfg::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::kPBytes);
+  float* sExchange = reinterpret_cast<float*>(sP + 2 * Cfg::kPBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sExchange + 2 * 2 * BLOCK_M);
   if (smem_misaligned(smem, p.status, kFlashFwd, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* q_full = bars;            // 1
   uint64_t* kv_full = bars + 1;       // 2
@@ -60,7 +63,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
   uint64_t* s_free = bars + 7;        // 2
   uint64_t* p_ready = bars + 9;       // 1
   uint64_t* pv_done = bars + 10;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* pair_bar = bars + 11;     // 4: the two warps that share a 32-row quarter
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,9 +84,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 4);
+      mbar_init(&s_free[i], 8);
     }
-    mbar_init(p_ready, 4);
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+    mbar_init(p_ready, 8);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -160,52 +165,66 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
   } else {
     // ---------------------------------------------------------------- softmax / correction / epilogue
     const int quarter = warp & 3;
+    const int wg = (warp - 2) >> 2;               // which half of the key columns this warp handles
+    const int col_base = wg * 64;
     const int row = quarter * 32 + lane;          // row of the tile == TMEM lane
     const int q_pos = q0 + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float sl = p.scale * kLog2e;
-    float m_run = -INFINITY, l_run = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;        // l_run: sum over this warp group's columns only
     bool ok = true;
+    // exchange one float per row with the warp that holds the other column half (bounded, like every wait)
+    auto exchange = [&](uint32_t phase, float mine, float& theirs) -> bool {
+      float* slot = sExchange + (phase & 1) * 2 * BLOCK_M;
+      slot[wg * BLOCK_M + row] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pair_bar[quarter]);
+      if (!mbar_wait(&pair_bar[quarter], phase & 1, abort_flag, p.status, kFlashFwd, 9)) return false;
+      theirs = slot[(wg ^ 1) * BLOCK_M + row];
+      return true;
+    };
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j & 1;
       if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kFlashFwd, 6)) { ok = false; break; }
       tc_fence_after_sync();
-      const int k0 = j * BLOCK_N;
-      const bool need_mask = (p.causal && k0 + BLOCK_N > q0) || (k0 + BLOCK_N > p.seq);
+      const int k0 = j * BLOCK_N + col_base;
+      const bool need_mask = (p.causal && j * BLOCK_N + BLOCK_N > q0) || (j * BLOCK_N + BLOCK_N > p.seq);
       const int k_max = p.causal ? min(q_pos, p.seq - 1) : p.seq - 1;  // last visible key of this row
-      // pass 1: row maximum
-      uint32_t sv[4][32];
-      float m_tile = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * BLOCK_N + c * 32), sv[c]);
-      }
+      // pass 1: row maximum over this group's 64 columns
+      uint32_t sv[2][32];
+      tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * BLOCK_N + col_base), sv[0]);
+      tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * BLOCK_N + col_base + 32), sv[1]);
       tc_wait_ld();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);   // S(j) is in registers; its TMEM buffer may be overwritten
+      if (lane == 0) mbar_arrive(&s_free[s]);   // this warp's part of S(j) is in registers
+      float m_loc = -INFINITY;
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float x = __uint_as_float(sv[c][i]);
             if (k0 + c * 32 + i > k_max) x = -INFINITY;
             sv[c][i] = __float_as_uint(x);
-            m_tile = fmaxf(m_tile, x);
+            m_loc = fmaxf(m_loc, x);
           }
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sv[c][i]));
+          for (int i = 0; i < 32; ++i) m_loc = fmaxf(m_loc, __uint_as_float(sv[c][i]));
         }
       }
+      float m_other;
+      if (!exchange((uint32_t)j, m_loc, m_other)) { ok = false; break; }
+      const float m_tile = fmaxf(m_loc, m_other);
       // The reference point m_run of the exponentials only follows the true maximum when it would otherwise
       // fall behind by more than kLazyBits powers of two: exp2((s - m_run) * scale) then stays below 2^kLazyBits,
       // harmless in bf16 / fp32, and the rescaling of O in tensor memory (a round trip through registers, and
-      // a wait for the previous P V product) becomes rare. The final O / l is exact either way.
+      // a wait for the previous P V product) becomes rare. The final O / l is exact either way. Both column
+      // halves see the same m_tile, hence take the same decision.
       constexpr float kLazyBits = 8.0f;
       const bool moved = (m_tile - m_run) * sl > kLazyBits;       // first tile: m_run = -inf -> true
       const float m_new = moved ? m_tile : m_run;
@@ -214,9 +233,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
       const float neg = -m_safe * sl;
       float l_tile = 0.0f;
       // pass 2: probabilities, packed to bf16
-      uint32_t pk[64];
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float p0 = exp2f(fmaf(__uint_as_float(sv[c][i]), sl, neg));
@@ -227,23 +246,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
       }
       l_run = l_run * alpha + l_tile;
       m_run = m_new;
-      // P(j) goes to buffer j & 1. Its previous reader, the product P V of tile j - 2, finished before S(j) did
-      // (the tensor core executes in issue order), so no wait is needed here.
-      uint8_t* sPj = sP + (j & 1) * Cfg::kPBytes;
+      // P(j) goes to buffer j & 1 (this group's 64 columns are one 64-element box). Its previous reader, the
+      // product P V of tile j - 2, finished before S(j) did (the tensor core executes in issue order).
+      uint8_t* sPj = sP + (j & 1) * Cfg::kPBytes + wg * (BLOCK_M * 128);
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const int box = ch >> 3, chunk = ch & 7;
-        uint4 val = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        uint8_t* dst = sPj + box * (BLOCK_M * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
-        *reinterpret_cast<uint4*>(dst) = val;
+      for (int chunk = 0; chunk < 8; ++chunk) {
+        uint4 val = make_uint4(pk[chunk * 4], pk[chunk * 4 + 1], pk[chunk * 4 + 2], pk[chunk * 4 + 3]);
+        *reinterpret_cast<uint4*>(sPj + row * 128 + ((chunk ^ (row & 7)) << 4)) = val;
       }
-      // rescale O when some row of this warp moved its reference point; O belongs to the previous P V product
-      // until that has completed
+      // rescale O when some row of this warp moved its reference point (each group takes half of the head
+      // dimension); O belongs to the previous P V product until that has completed
       if (j > 0 && __any_sync(0xffffffffu, moved)) {
         if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kFlashFwd, 7)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = wg * (HD / 64); c < (wg + 1) * (HD / 64); ++c) {
           uint32_t ov[32];
           tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(Cfg::kOCol + c * 32), ov);
           tc_wait_ld();
@@ -258,14 +275,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
     }
-    // epilogue: O / l -> global, LSE
+    // epilogue: O / l -> global (each group stores half of the head dimension), LSE
+    float l_other = 0.0f;
+    if (ok && n_tiles > 0) ok = exchange((uint32_t)n_tiles, l_run, l_other);
     if (ok && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kFlashFwd, 8)) {
       tc_fence_after_sync();
-      const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      const float l_all = l_run + l_other;
+      const float inv_l = l_all > 0.0f ? 1.0f / l_all : 0.0f;
       const bool row_ok = q_pos < p.seq;
       __nv_bfloat16* dst = p.out + ((size_t)b * p.seq + q_pos) * ((size_t)p.heads * HD) + (size_t)head * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = wg * (HD / 64); c < (wg + 1) * (HD / 64); ++c) {
         uint32_t ov[32];
         tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(Cfg::kOCol + c * 32), ov);
         tc_wait_ld();
@@ -281,9 +301,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
           }
         }
       }
-      if (row_ok) {
+      if (row_ok && wg == 0) {
         p.lse[((size_t)b * p.heads + head) * p.seq + q_pos] =
-            (l_run > 0.0f) ? m_run * p.scale + __logf(l_run) : -INFINITY;
+            (l_all > 0.0f) ? m_run * p.scale + __logf(l_all) : -INFINITY;
       }
     }
   }

@@ -35,6 +35,8 @@ def _matmul(x: torch.Tensor, weight) -> torch.Tensor:
 
 
 class ModelRunner:
+    FUSED_ALL_REDUCE_MAX_ROWS = 2048     # beyond this the partial tiles (tp copies per rank) outgrow the win
+
     def __init__(self, model, cache: PagedKVCache, quantization: str | None = None) -> None:
         self.model = model
         self.cache = cache
@@ -65,6 +67,17 @@ class ModelRunner:
         if self.tp is not None and self.tp.size > 1:
             self.tp.all_reduce_sum_(x)
         return x
+
+    def _row_parallel(self, x: torch.Tensor, weight) -> torch.Tensor:
+        """Row-parallel projection summed over the tensor-parallel ranks.
+
+        With a fused tensor-parallel context and a bf16 weight the partial products are exchanged by the
+        GEMM kernel itself (GEMM -> all-reduce over peer memory); otherwise GEMM, then a NCCL all-reduce."""
+        fused = getattr(self.tp, "fused", None) if self.tp is not None else None
+        if (fused is not None and x.is_cuda and x.dtype == torch.bfloat16 and not isinstance(weight, Fp8Weight)
+                and x.shape[0] <= self.FUSED_ALL_REDUCE_MAX_ROWS):
+            return fused.gemm_all_reduce(x, weight)
+        return self._reduce(_matmul(x, weight))
 
     @torch.no_grad()
     def forward(self, items: list[RunItem]) -> torch.Tensor:
@@ -150,14 +163,14 @@ class ModelRunner:
                 cache.write(index, slot_t, k, v)
                 attended = ops.paged_attention_ragged(q, cache.keys[index], cache.values[index], tables, ctx_t, qlen_t,
                                                       q_lens, ctx_lens)
-            attended = self._reduce(_matmul(attended.reshape(ids.shape[0], -1), w["out"]))
+            attended = self._row_parallel(attended.reshape(ids.shape[0], -1), w["out"])
             stream, normed = layer.norm2.add_and_norm(stream, attended)
             if "moe" in w:
                 pending = w["moe"](normed)
             elif "w13" in w:
-                pending = self._reduce(_matmul(ops.swiglu_interleaved(_matmul(normed, w["w13"])), w["w2"]))
+                pending = self._row_parallel(ops.swiglu_interleaved(_matmul(normed, w["w13"])), w["w2"])
             else:
-                pending = self._reduce(_matmul(ops.silu(_matmul(normed, w["w1"])), w["w2"]))
+                pending = self._row_parallel(ops.silu(_matmul(normed, w["w1"])), w["w2"])
         hidden = model.final_norm.add_and_norm(stream, pending)[1]
         if not logit_rows:
             return hidden.new_zeros(0, model.vocab_size)

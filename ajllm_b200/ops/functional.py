@@ -10,6 +10,7 @@ interleaves gate (even) and up (odd) columns so the activation pairs sit side by
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -18,6 +19,10 @@ from ajllm_b200.ops import native, reference
 EPI_STORE_BF16 = 0
 EPI_ACCUM_F32 = 1
 EPI_STORE_F32 = 2
+
+# Attention backward: False selects the fused single-pass kernel (dQ summed with fp32 reductions, last
+# bits may differ between runs); True (or AJB_DETERMINISTIC_ATTENTION=1) the bit-reproducible two-kernel path.
+DETERMINISTIC_ATTENTION_BACKWARD = os.environ.get("AJB_DETERMINISTIC_ATTENTION", "0") == "1"
 
 
 def _is_cuda(t: torch.Tensor) -> bool:
@@ -283,9 +288,13 @@ class _RopeAttentionFn(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         dqkv = torch.empty_like(qkv)
         delta = torch.empty(B, num_heads, T, dtype=torch.float32, device=qkv.device)
+        # the fused kernel adds dQ tiles into an fp32 buffer (sum order varies between runs); the
+        # bit-reproducible two-kernel path is selected by passing no buffer
+        dq_acc = None if DETERMINISTIC_ATTENTION_BACKWARD else \
+            torch.empty(B * num_heads * (-(-T // 64) * 64) * head_dim, dtype=torch.float32, device=qkv.device)
         native.call("ajb_flash_bwd", qkv.data_ptr(), out.data_ptr(), grad_out.data_ptr(), lse.data_ptr(),
-                    delta.data_ptr(), dqkv.data_ptr(), B, T, num_heads, num_kv_heads, head_dim, width,
-                    int(causal), scale, stream)
+                    delta.data_ptr(), dqkv.data_ptr(), dq_acc.data_ptr() if dq_acc is not None else None,
+                    B, T, num_heads, num_kv_heads, head_dim, width, int(causal), scale, stream)
         if use_rope:
             native.call("ajb_rope_qk", dqkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), None, B * T, T,
                         num_heads, num_kv_heads, head_dim, width, 1, stream)

@@ -52,7 +52,7 @@ _SIGNATURES: dict[str, list] = {
     "ajb_sample_rows": [c_void, c_long, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void],
     "ajb_spec_verify": [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void],
     "ajb_paged_attention": [c_void] * 7 + [c_int] * 8 + [c_float, c_void],
-    "ajb_flash_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
+    "ajb_flash_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
                       c_long, c_int, c_float, c_void],
 }
 

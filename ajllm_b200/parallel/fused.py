@@ -22,7 +22,7 @@ from ajllm_b200.ops import native
 from ajllm_b200.ops.functional import EPI_ACCUM_F32, gemm
 
 _MAX_RANKS = 8
-MODE_ALL_GATHER, MODE_REDUCE_SCATTER = 0, 1
+MODE_ALL_GATHER, MODE_REDUCE_SCATTER, MODE_ALL_REDUCE = 0, 1, 2
 
 
 class _CommArgs(ctypes.Structure):
@@ -35,6 +35,7 @@ class _CommArgs(ctypes.Structure):
         ("counter_ptrs", ctypes.c_void_p * _MAX_RANKS), ("ready_ptrs", ctypes.c_void_p * _MAX_RANKS),
         ("done_ptrs", ctypes.c_void_p * _MAX_RANKS),
         ("shard_flags", ctypes.c_void_p), ("expected_count", ctypes.c_uint), ("epoch", ctypes.c_uint),
+        ("a_rows", ctypes.c_int),
     ]
 
 
@@ -87,7 +88,7 @@ class FusedTensorParallel:
         return rows_total % self.size == 0 and (rows_total // self.size) % self.BLOCK_M == 0
 
     def _launch(self, mode: int, m: int, n: int, k: int, b: torch.Tensor, b_mn: bool, out: torch.Tensor,
-                a: torch.Tensor | None = None, gathered: torch.Tensor | None = None) -> None:
+                a: torch.Tensor | None = None, gathered: torch.Tensor | None = None, a_rows: int = 0) -> None:
         self.epoch += 1
         args = _CommArgs()
         args.mode, args.m, args.n, args.k = mode, m, n, k
@@ -96,8 +97,10 @@ class FusedTensorParallel:
         args.a = a.data_ptr() if a is not None else None
         args.b, args.out = b.data_ptr(), out.data_ptr()
         args.gathered = gathered.data_ptr() if gathered is not None else None
-        if mode == MODE_REDUCE_SCATTER:
-            tiles = (m // self.size // self.BLOCK_M) * ((n + self.BLOCK_N - 1) // self.BLOCK_N)
+        args.a_rows = a_rows
+        if mode != MODE_ALL_GATHER:
+            rows = m if mode == MODE_ALL_REDUCE else m // self.size
+            tiles = (rows // self.BLOCK_M) * ((n + self.BLOCK_N - 1) // self.BLOCK_N)
             self.expected_count += tiles * 4          # one count per epilogue warp per tile
         for r in range(self.size):
             args.stage_ptrs[r] = self._stage_ptrs[r] if self._stage_ptrs else None
@@ -135,6 +138,19 @@ class FusedTensorParallel:
         out = torch.empty(m_local, n, dtype=torch.bfloat16, device=self.device)
         self._launch(MODE_REDUCE_SCATTER, m, n, k, weight, b_mn, out, a=x)
         return out
+
+    def gemm_all_reduce(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """``sum over ranks of x @ weight^T`` -> ``[rows, n]`` on every rank (inference; no autograd).
+
+        Meant for decoding, where ``rows`` is small: every rank's partial tiles are stored into every
+        peer's receive buffer by the GEMM epilogue and summed at the end of the same kernel."""
+        rows, k = x.shape
+        n = weight.shape[0]
+        m = -(-rows // self.BLOCK_M) * self.BLOCK_M
+        self._ensure("recv", self.size * m * n * 2)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
+        self._launch(MODE_ALL_REDUCE, m, n, k, weight, False, out, a=x.contiguous(), a_rows=rows)
+        return out[:rows]
 
     # ------------------------------------------------------------------ differentiable entry points
     def gather_linear(self, x_local: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -66,7 +66,11 @@ def run_ours(args):
     tp = None
     if world > 1:
         mesh = ParallelMesh(tp=world)
-        tp = TensorParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size)
+        fused = None
+        if os.environ.get("AJB_FUSED_TP", "1") != "0":
+            from ajllm_b200.parallel.fused import FusedTensorParallel
+            fused = FusedTensorParallel(mesh.tp.group, device)
+        tp = TensorParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size, fused=fused)
     torch.manual_seed(0)
     config = dict(MODEL)
     if args.layers:
@@ -105,7 +109,7 @@ def run_ours(args):
             "higher_is_better": True,
             "config": {"model": "dense-8B (32L d4096 32h/8kv hd128 ffn14336 vocab128256)", "requests": args.requests,
                        "prompt_len": "U[128,2048]", "output_len": "U[64,512]", "max_num_seqs": args.max_num_seqs,
-                       "parallelism": f"tp{world}", "speculative_k": args.speculative, "temperature": args.temperature,
+                       "parallelism": f"tp{world}", "tp_backend": ("fused-gemm-all-reduce" if (tp is not None and tp.fused is not None) else ("nccl" if tp else "none")), "speculative_k": args.speculative, "temperature": args.temperature,
                        "layers_override": args.layers or None},
             "elapsed_s": elapsed, "output_tokens": generated, "prompt_tokens": sum(len(p) for p in prompts),
             "engine_steps": engine.stats.steps, "preemptions": engine.stats.preemptions,

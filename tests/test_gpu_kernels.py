@@ -173,8 +173,12 @@ def test_sumsq_and_adamw_flat():
     assert torch.equal(work, master.to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("deterministic", [False, True])
 @pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 256, 4, 2, 128), (1, 200, 2, 2, 128), (2, 384, 8, 2, 64), (1, 1024, 2, 1, 128)])
-def test_flash_attention_forward_backward(B, T, Hq, Hkv, hd):
+def test_flash_attention_forward_backward(B, T, Hq, Hkv, hd, deterministic, monkeypatch):
+    """Both backward paths (fused single pass with reduced dQ; two reproducible kernels) against fp32 math."""
+    from ajllm_b200.ops import functional
+    monkeypatch.setattr(functional, "DETERMINISTIC_ATTENTION_BACKWARD", deterministic)
     torch.manual_seed(10)
     width = (Hq + 2 * Hkv) * hd
     qkv = (torch.randn(B, T, width, device=_dev()) * 0.5).to(torch.bfloat16).requires_grad_()
