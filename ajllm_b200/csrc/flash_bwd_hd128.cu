@@ -20,8 +20,10 @@
 // additions, and with it the last bits of dQ, may differ between runs; dK and dV are exact sums in
 // a fixed order. A small kernel afterwards scales the buffer and writes bf16 dQ rows.
 //
-// 14 warps: 0 = TMA producer (+ lse / delta rows), 1 = MMA issuer, 2..9 = two softmax groups (32
-// query columns each, one key row per thread), 10..13 = dQ drain.
+// 15 warps: 0 = TMA producer (+ lse / delta rows), 1 = issuer of S^T and dP^T, 2..9 = two softmax
+// groups (32 query columns each, one key row per thread), 10..13 = dQ drain, 14 = issuer of dV, dK
+// and dQ^T. Issuing a tcgen05.mma holds the issuing thread for about as long as the product occupies
+// the tensor pipe, so a single issuer, with its waits in between, would be the critical path.
 #include "common.cuh"
 
 namespace ajb {
@@ -33,7 +35,7 @@ constexpr int HD = 128;
 constexpr int BKV = 128;           // keys per CTA
 constexpr int BQ = 64;             // queries per step
 constexpr int kStages = 3;         // Q / dO ring
-constexpr int kThreads = 448;
+constexpr int kThreads = 480;
 constexpr float kLog2e = 1.4426950408889634f;
 
 constexpr int kKvTile = BKV * HD * 2;          // 32 KB
@@ -91,7 +93,8 @@ flash_bwd_hd128_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
   uint64_t* dq_full = ds_free + 2;             // 1
   uint64_t* dq_drained = dq_full + 1;          // 1 (4 warps)
   uint64_t* acc_done = dq_drained + 1;         // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* p_consumed = acc_done + 1;         // 1: dV of this iteration has been handed to the tensor pipe
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_consumed + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,6 +123,7 @@ flash_bwd_hd128_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
     mbar_init(dq_full, 1);
     mbar_init(dq_drained, 4);
     mbar_init(acc_done, 1);
+    mbar_init(p_consumed, 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensor_map(&map_kv);
@@ -173,24 +177,23 @@ flash_bwd_hd128_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
       if (++stage == kStages) { stage = 0; phase ^= 1; }
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    constexpr uint32_t idesc_s = make_idesc(BKV, BQ, 1, false, false);    // K Q^T, V dO^T
-    constexpr uint32_t idesc_g = make_idesc(BKV, HD, 1, false, true);     // P^T dO, dS^T Q
-    constexpr uint32_t idesc_q = make_idesc(HD, BQ, 1, true, true);       // K^T dS
-    // descriptor low words of every tile; a k-step is a compile-time offset added to one of these
+    // ---------------------------------------------------------------- issuer A: S^T = K Q^T and dP^T = V dO^T
+    constexpr uint32_t idesc_s = make_idesc(BKV, BQ, 1, false, false);
+    // descriptor low words of the tiles; a k-step is a compile-time offset added to one of these
     const uint32_t k_km = desc_lo_k_major(smem_u32(sK)), v_km = desc_lo_k_major(smem_u32(sV));
-    const uint32_t k_mn = desc_lo_mn_major(smem_u32(sK), BKV * 128);
-    const uint32_t q_km0 = desc_lo_k_major(smem_u32(sQdO)), q_mn0 = desc_lo_mn_major(smem_u32(sQdO), BQ * 128);
-    const uint32_t ds_km0 = desc_lo_k_major(smem_u32(sDS)), ds_mn0 = desc_lo_mn_major(smem_u32(sDS), BKV * 128);
-    constexpr uint32_t kStageStep = (2 * kQTile) >> 4, kDoStep = kQTile >> 4, kDsStep = kDsTile >> 4;
+    const uint32_t q_km0 = desc_lo_k_major(smem_u32(sQdO));
+    constexpr uint32_t kStageStep = (2 * kQTile) >> 4, kDoStep = kQTile >> 4;
     bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kFlashBwdFused, 2);
-    int load_stage = 0;          // stage / phase of the next S^T product
-    uint32_t load_phase = 0;
-    auto issue_s = [&]() -> bool {          // S^T of the next iteration (its Q / dO stage = load_stage)
-      if (!mbar_wait(&qdo_full[load_stage], load_phase, abort_flag, p.status, kFlashBwdFused, 3)) return false;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      if (!mbar_wait(&qdo_full[stage], phase, abort_flag, p.status, kFlashBwdFused, 3)) break;
+      // S^T overwrites P^T of the previous iteration: its dV product must have been issued (the tensor pipe
+      // executes in issue order)
+      if (it > 0 && !mbar_wait(p_consumed, (uint32_t)(it - 1) & 1, abort_flag, p.status, kFlashBwdFused, 4)) break;
       tc_fence_after_sync();
+      const uint32_t q_km = q_km0 + (uint32_t)stage * kStageStep, do_km = q_km + kDoStep;
       if (lane == 0) {
-        const uint32_t q_km = q_km0 + (uint32_t)load_stage * kStageStep;
         umma_f16_c<false>(tmem_base + kSCol, desc_at(k_km, 0), desc_at(q_km, 0), idesc_s);
 #pragma unroll
         for (int k = 1; k < HD / 16; ++k)
@@ -199,11 +202,10 @@ flash_bwd_hd128_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         tc_commit(s_full);
       }
       __syncwarp();
-      return true;
-    };
-    auto issue_dp = [&](int stage) {        // dP^T from the dO tile of `stage`
+      // dP^T of the previous iteration must have been read by the softmax warps
+      if (it > 0 && !mbar_wait(ds_ready, (uint32_t)(it - 1) & 1, abort_flag, p.status, kFlashBwdFused, 5)) break;
+      tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t do_km = q_km0 + (uint32_t)stage * kStageStep + kDoStep;
         umma_f16_c<false>(tmem_base + kDpCol, desc_at(v_km, 0), desc_at(do_km, 0), idesc_s);
 #pragma unroll
         for (int k = 1; k < HD / 16; ++k)
@@ -212,62 +214,8 @@ flash_bwd_hd128_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         tc_commit(dp_full);
       }
       __syncwarp();
-    };
-    auto advance = [&]() { if (++load_stage == kStages) { load_stage = 0; load_phase ^= 1; } };
-    if (ok && n_iter > 0) {
-      ok = issue_s();
-      if (ok) issue_dp(load_stage);
-      advance();
+      if (++stage == kStages) { stage = 0; phase ^= 1; }
     }
-    int stage = 0;               // stage of the iteration being consumed
-    for (int it = 0; it < n_iter && ok; ++it) {
-      const uint32_t q_mn = q_mn0 + (uint32_t)stage * kStageStep, do_mn = q_mn + kDoStep;
-      const uint32_t ds_km = ds_km0 + (uint32_t)(it & 1) * kDsStep, ds_mn = ds_mn0 + (uint32_t)(it & 1) * kDsStep;
-      // dV += P^T dO. P^T lives in tensor memory: queries 0..31 in columns [256, 272), 32..63 in [288, 304)
-      if (!mbar_wait(p_ready, (uint32_t)it & 1, abort_flag, p.status, kFlashBwdFused, 4)) { ok = false; break; }
-      tc_fence_after_sync();
-      if (lane == 0) {
-        umma_f16_ts(tmem_base + kDvCol, tmem_base + kSCol, desc_at(do_mn, 0), idesc_g, it != 0);
-#pragma unroll
-        for (int k = 1; k < BQ / 16; ++k) {
-          const uint32_t a_col = (uint32_t)(kSCol + (k < 2 ? k * 8 : 32 + (k - 2) * 8));
-          umma_f16_ts_c<true>(tmem_base + kDvCol, tmem_base + a_col, desc_at(do_mn, mn_major_step(k)), idesc_g);
-        }
-      }
-      __syncwarp();
-      // the tensor pipe executes in order: the next S^T may overwrite P^T right behind the dV product
-      const int next_stage = load_stage;
-      if (it + 1 < n_iter) {
-        ok = issue_s();
-        if (!ok) break;
-        advance();
-      }
-      if (!mbar_wait(ds_ready, (uint32_t)it & 1, abort_flag, p.status, kFlashBwdFused, 5)) { ok = false; break; }
-      tc_fence_after_sync();
-      if (it + 1 < n_iter) issue_dp(next_stage);      // dP^T of this iteration has been consumed (ds_ready)
-      if (lane == 0) {
-        umma_f16(tmem_base + kDkCol, desc_at(ds_km, 0), desc_at(q_mn, 0), idesc_g, it != 0);
-#pragma unroll
-        for (int k = 1; k < BQ / 16; ++k)
-          umma_f16_c<true>(tmem_base + kDkCol, desc_at(ds_km, (uint32_t)k * 32), desc_at(q_mn, mn_major_step(k)), idesc_g);
-      }
-      __syncwarp();
-      if (it > 0 && !mbar_wait(dq_drained, (uint32_t)(it - 1) & 1, abort_flag, p.status, kFlashBwdFused, 6)) { ok = false; break; }
-      tc_fence_after_sync();
-      if (lane == 0) {
-        umma_f16_c<false>(tmem_base + kDqCol, desc_at(k_mn, 0), desc_at(ds_mn, 0), idesc_q);
-#pragma unroll
-        for (int k = 1; k < BKV / 16; ++k)
-          umma_f16_c<true>(tmem_base + kDqCol, desc_at(k_mn, mn_major_step(k)), desc_at(ds_mn, mn_major_step(k)), idesc_q);
-        tc_commit(dq_full);
-        tc_commit(&ds_free[it & 1]);
-        tc_commit(&qdo_empty[stage]);
-      }
-      __syncwarp();
-      if (++stage == kStages) stage = 0;
-    }
-    if (ok && lane == 0) tc_commit(acc_done);
-    __syncwarp();
   } else if (warp < 10) {
     // ---------------------------------------------------------------- P^T / dS^T: thread = key row, group = 32 query columns
     const int quarter = warp & 3;
@@ -375,7 +323,7 @@ flash_bwd_hd128_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         }
       }
     }
-  } else {
+  } else if (warp < 14) {
     // ---------------------------------------------------------------- dQ^T tiles: tensor memory -> shared memory -> bulk reduce-add
     const int quarter = warp & 3;                     // head-dim elements [32 * quarter, 32 * quarter + 32)
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
@@ -409,6 +357,57 @@ flash_bwd_hd128_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
       }
     }
     if (lane == 0) bulk_wait_group0();    // reductions complete before the CTA (and its shared memory) goes away
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- issuer B: dV += P^T dO, dK += dS^T Q, dQ^T = K^T dS
+    constexpr uint32_t idesc_g = make_idesc(BKV, HD, 1, false, true);
+    constexpr uint32_t idesc_q = make_idesc(HD, BQ, 1, true, true);
+    const uint32_t k_mn = desc_lo_mn_major(smem_u32(sK), BKV * 128);
+    const uint32_t q_mn0 = desc_lo_mn_major(smem_u32(sQdO), BQ * 128);
+    const uint32_t ds_km0 = desc_lo_k_major(smem_u32(sDS)), ds_mn0 = desc_lo_mn_major(smem_u32(sDS), BKV * 128);
+    constexpr uint32_t kStageStep = (2 * kQTile) >> 4, kDoStep = kQTile >> 4, kDsStep = kDsTile >> 4;
+    bool ok = true;
+    int stage = 0;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const uint32_t q_mn = q_mn0 + (uint32_t)stage * kStageStep, do_mn = q_mn + kDoStep;
+      const uint32_t ds_km = ds_km0 + (uint32_t)(it & 1) * kDsStep, ds_mn = ds_mn0 + (uint32_t)(it & 1) * kDsStep;
+      // P^T lives in tensor memory: queries 0..31 in columns [256, 272), 32..63 in [288, 304)
+      if (!mbar_wait(p_ready, (uint32_t)it & 1, abort_flag, p.status, kFlashBwdFused, 6)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        umma_f16_ts(tmem_base + kDvCol, tmem_base + kSCol, desc_at(do_mn, 0), idesc_g, it != 0);
+#pragma unroll
+        for (int k = 1; k < BQ / 16; ++k) {
+          const uint32_t a_col = (uint32_t)(kSCol + (k < 2 ? k * 8 : 32 + (k - 2) * 8));
+          umma_f16_ts_c<true>(tmem_base + kDvCol, tmem_base + a_col, desc_at(do_mn, mn_major_step(k)), idesc_g);
+        }
+        mbar_arrive(p_consumed);
+      }
+      __syncwarp();
+      if (!mbar_wait(ds_ready, (uint32_t)it & 1, abort_flag, p.status, kFlashBwdFused, 13)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        umma_f16(tmem_base + kDkCol, desc_at(ds_km, 0), desc_at(q_mn, 0), idesc_g, it != 0);
+#pragma unroll
+        for (int k = 1; k < BQ / 16; ++k)
+          umma_f16_c<true>(tmem_base + kDkCol, desc_at(ds_km, (uint32_t)k * 32), desc_at(q_mn, mn_major_step(k)), idesc_g);
+      }
+      __syncwarp();
+      if (it > 0 && !mbar_wait(dq_drained, (uint32_t)(it - 1) & 1, abort_flag, p.status, kFlashBwdFused, 14)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        umma_f16_c<false>(tmem_base + kDqCol, desc_at(k_mn, 0), desc_at(ds_mn, 0), idesc_q);
+#pragma unroll
+        for (int k = 1; k < BKV / 16; ++k)
+          umma_f16_c<true>(tmem_base + kDqCol, desc_at(k_mn, mn_major_step(k)), desc_at(ds_mn, mn_major_step(k)), idesc_q);
+        tc_commit(dq_full);
+        tc_commit(&ds_free[it & 1]);
+        tc_commit(&qdo_empty[stage]);
+      }
+      __syncwarp();
+      if (++stage == kStages) stage = 0;
+    }
+    if (ok && lane == 0) tc_commit(acc_done);
     __syncwarp();
   }
 

@@ -1,9 +1,13 @@
 // FlashAttention forward for sm_100a: S = Q K^T and O += P V run on tcgen05 with S (double
 // buffered) and O resident in tensor memory; K/V tiles arrive by TMA; two groups of four softmax
 // warps each own one half of the 128 key columns of a tile (one query row per thread, online max /
-// sum in registers, the row maximum of the two halves exchanged through shared memory), write P as a
-// swizzled bf16 operand tile in shared memory (double buffered) and rescale O in tensor memory only
-// when a row's reference maximum has to move by more than 2^8.
+// sum in registers, the row maximum of the two halves exchanged through shared memory), write P as
+// packed bf16 back into the tensor-memory columns of the S buffer they have just read (the P V
+// product takes its A operand from tensor memory, so P never touches shared memory) and rescale O
+// in tensor memory only when a row's reference maximum has to move by more than 2^8. The two
+// products of a step are issued by two different warps: issuing a tcgen05.mma holds the issuing
+// thread for about as long as the product occupies the tensor pipe, so one issuer doing S(j + 1),
+// then waiting for P(j), then P(j) V, would itself be the critical path of the loop.
 //
 // Inputs are the packed projection rows [B, T, (Hq + 2 Hkv) * hd] (q heads | k heads | v heads) after
 // RoPE; query head h reads KV head h / (Hq / Hkv). Outputs: O [B, T, Hq * hd] (bf16) and the row
@@ -15,15 +19,15 @@ namespace flash {
 
 constexpr int BLOCK_M = 128;  // queries per CTA
 constexpr int BLOCK_N = 128;  // keys per step
-constexpr int kThreads = 320;   // TMA warp, MMA warp, 2 x 4 softmax warps
+constexpr int kThreads = 352;   // TMA warp, S-product issuer, 2 x 4 softmax warps, P V-product issuer
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int HD>
 struct FwdCfg {
   static constexpr int kTileBytes = BLOCK_N * HD * 2;       // one Q, K or V tile
-  static constexpr int kPBytes = BLOCK_M * BLOCK_N * 2;
+  static constexpr int kStages = HD == 128 ? 3 : 4;            // K/V ring
   static constexpr int kExchangeBytes = 2 * 2 * BLOCK_M * 4;   // [parity][column half][row] partial row maxima
-  static constexpr int kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*2 x (K,V)*/ + 2 * kPBytes + kExchangeBytes + 256;
+  static constexpr int kSmemBytes = kTileBytes /*Q*/ + kStages * 2 * kTileBytes /*(K,V) ring*/ + kExchangeBytes + 256;
   static constexpr int kTmemCols = 512;
   static constexpr int kOCol = 256;  // S0 at 0, S1 at 128, O at 256
 };
@@ -52,19 +56,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
   uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Cfg::kTileBytes;               // stage s: K at sKV + s*2*tile, V right after
-  uint8_t* sP = sKV + 4 * Cfg::kTileBytes;
-  float* sExchange = reinterpret_cast<float*>(sP + 2 * Cfg::kPBytes);
+  constexpr int kStages = Cfg::kStages;
+  float* sExchange = reinterpret_cast<float*>(sKV + kStages * 2 * Cfg::kTileBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sExchange + 2 * 2 * BLOCK_M);
   if (smem_misaligned(smem, p.status, kFlashFwd, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* q_full = bars;            // 1
-  uint64_t* kv_full = bars + 1;       // 2
-  uint64_t* kv_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;        // 2
-  uint64_t* s_free = bars + 7;        // 2
-  uint64_t* p_ready = bars + 9;       // 1
-  uint64_t* pv_done = bars + 10;      // 1
-  uint64_t* pair_bar = bars + 11;     // 4: the two warps that share a 32-row quarter
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* kv_full = bars + 1;       // kStages (<= 4)
+  uint64_t* kv_empty = bars + 5;      // kStages
+  uint64_t* s_full = bars + 9;        // 2
+  uint64_t* p_ready = bars + 11;      // 1
+  uint64_t* pv_done = bars + 12;      // 1
+  uint64_t* pair_bar = bars + 13;     // 4: the two warps that share a 32-row quarter
+  uint64_t* pv_issued = bars + 17;    // 2: P V of the tile in S buffer b has been handed to the tensor pipe
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,12 +84,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kStages; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 8);
     }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(&pv_issued[0], 1);
+    mbar_init(&pv_issued[1], 1);
     for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
     mbar_init(p_ready, 8);
     mbar_init(pv_done, 1);
@@ -107,65 +113,74 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
       load_tile<HD>(sQ, &map_qkv, q_full, q_col, q0, b);
+      int s = 0;
+      uint32_t phase = 0;
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], (((uint32_t)j >> 1) & 1) ^ 1, abort_flag, p.status, kFlashFwd, 1)) break;
+        if (!mbar_wait(&kv_empty[s], phase ^ 1, abort_flag, p.status, kFlashFwd, 1)) break;
         uint8_t* sK = sKV + s * 2 * Cfg::kTileBytes;
         mbar_arrive_expect_tx(&kv_full[s], 2 * Cfg::kTileBytes);
         load_tile<HD>(sK, &map_qkv, &kv_full[s], k_col, j * BLOCK_N, b);
         load_tile<HD>(sK + Cfg::kTileBytes, &map_qkv, &kv_full[s], v_col, j * BLOCK_N, b);
+        if (++s == kStages) { s = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    constexpr uint32_t idesc_s = make_idesc(BLOCK_M, BLOCK_N, 1, false, false);  // Q K^T
-    constexpr uint32_t idesc_o = make_idesc(BLOCK_M, HD, 1, false, true);        // P V (V is N-contiguous)
-    const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+    // ---- S(j) = Q K(j)^T into S buffer j & 1
+    constexpr uint32_t idesc_s = make_idesc(BLOCK_M, BLOCK_N, 1, false, false);
+    // descriptor low words; a k-step is a compile-time offset added to one of these (see common.cuh)
+    const uint32_t q_km = desc_lo_k_major(smem_u32(sQ));
+    const uint32_t k_km0 = desc_lo_k_major(smem_u32(sKV));
+    constexpr uint32_t kStageStep = (2 * Cfg::kTileBytes) >> 4;
     bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kFlashFwd, 2);
-    auto issue_s = [&](int j) -> bool {
-      const int s = j & 1;
-      const uint32_t use = (uint32_t)j >> 1;
-      if (!mbar_wait(&kv_full[s], use & 1, abort_flag, p.status, kFlashFwd, 3)) return false;
-      if (!mbar_wait(&s_free[s], (use & 1) ^ 1, abort_flag, p.status, kFlashFwd, 4)) return false;
-      tc_fence_after_sync();
-      if (lane == 0) {
-        const uint32_t aK = smem_u32(sKV + s * 2 * Cfg::kTileBytes);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t box = (uint32_t)(k / 4) * (BLOCK_N * 128), off = (uint32_t)(k % 4) * 32;
-          umma_f16(tmem_base + (uint32_t)(s * BLOCK_N), desc_k_major(aQ + box, off), desc_k_major(aK + box, off),
-                   idesc_s, k != 0);
-        }
-        tc_commit(&s_full[s]);
-      }
-      __syncwarp();
-      return true;
-    };
-    if (ok && n_tiles > 0) ok = issue_s(0);
+    int stage = 0;
+    uint32_t phase = 0;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (j + 1 < n_tiles) {
-        ok = issue_s(j + 1);
-        if (!ok) break;
-      }
-      if (!mbar_wait(p_ready, (uint32_t)j & 1, abort_flag, p.status, kFlashFwd, 5)) { ok = false; break; }
+      if (!mbar_wait(&kv_full[stage], phase, abort_flag, p.status, kFlashFwd, 3)) break;
+      // S buffer j & 1 still holds P(j - 2) until the product P(j - 2) V has been issued: the tensor pipe
+      // executes in issue order, so being issued first is enough
+      if (!mbar_wait(&pv_issued[j & 1], (((uint32_t)j >> 1) & 1) ^ 1, abort_flag, p.status, kFlashFwd, 4)) break;
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t aV = smem_u32(sKV + (j & 1) * 2 * Cfg::kTileBytes + Cfg::kTileBytes);
+        const uint32_t k_km = k_km0 + (uint32_t)stage * kStageStep;
+        const uint32_t d = tmem_base + (uint32_t)((j & 1) * BLOCK_N);
+        umma_f16_c<false>(d, desc_at(q_km, 0), desc_at(k_km, 0), idesc_s);
 #pragma unroll
-        for (int k = 0; k < BLOCK_N / 16; ++k) {
-          const uint32_t pbox = (uint32_t)(k / 4) * (BLOCK_M * 128), poff = (uint32_t)(k % 4) * 32;
-          umma_f16(tmem_base + Cfg::kOCol, desc_k_major(aP + (uint32_t)((j & 1) * Cfg::kPBytes) + pbox, poff), desc_mn_major(aV, BLOCK_N * 128, k * 16),
-                   idesc_o, (j | k) != 0);
-        }
-        tc_commit(pv_done);
-        tc_commit(&kv_empty[j & 1]);
+        for (int k = 1; k < HD / 16; ++k)
+          umma_f16_c<true>(d, desc_at(q_km, k_major_step(k, BLOCK_M * 128)), desc_at(k_km, k_major_step(k, BLOCK_N * 128)), idesc_s);
+        tc_commit(&s_full[j & 1]);
       }
       __syncwarp();
+      if (++stage == kStages) { stage = 0; phase ^= 1; }
+    }
+  } else if (warp == 10) {
+    // ---- O += P(j) V(j): P from tensor memory (keys 0..63 in columns [0, 32) of S buffer j & 1, 64..127 in [64, 96))
+    constexpr uint32_t idesc_o = make_idesc(BLOCK_M, HD, 1, false, true);
+    const uint32_t v_mn0 = desc_lo_mn_major(smem_u32(sKV) + Cfg::kTileBytes, BLOCK_N * 128);
+    constexpr uint32_t kStageStep = (2 * Cfg::kTileBytes) >> 4;
+    int stage = 0;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait(p_ready, (uint32_t)j & 1, abort_flag, p.status, kFlashFwd, 5)) break;
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t v_mn = v_mn0 + (uint32_t)stage * kStageStep;
+        const uint32_t p_base = tmem_base + (uint32_t)((j & 1) * BLOCK_N);
+        umma_f16_ts(tmem_base + Cfg::kOCol, p_base, desc_at(v_mn, 0), idesc_o, j != 0);
+#pragma unroll
+        for (int k = 1; k < BLOCK_N / 16; ++k)
+          umma_f16_ts_c<true>(tmem_base + Cfg::kOCol, p_base + (uint32_t)(k < 4 ? k * 8 : 64 + (k - 4) * 8),
+                              desc_at(v_mn, mn_major_step(k)), idesc_o);
+        tc_commit(pv_done);
+        tc_commit(&kv_empty[stage]);
+        mbar_arrive(&pv_issued[j & 1]);
+      }
+      __syncwarp();
+      if (++stage == kStages) stage = 0;
     }
   } else {
     // ---------------------------------------------------------------- softmax / correction / epilogue
     const int quarter = warp & 3;
-    const int wg = (warp - 2) >> 2;               // which half of the key columns this warp handles
+    const int wg = (warp - 2) >> 2;               // which half of the key columns this warp handles (warps 2..9)
     const int col_base = wg * 64;
     const int row = quarter * 32 + lane;          // row of the tile == TMEM lane
     const int q_pos = q0 + row;
@@ -195,9 +210,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
       tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * BLOCK_N + col_base), sv[0]);
       tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * BLOCK_N + col_base + 32), sv[1]);
       tc_wait_ld();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);   // this warp's part of S(j) is in registers
       float m_loc = -INFINITY;
       if (need_mask) {
 #pragma unroll
@@ -246,14 +258,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
       }
       l_run = l_run * alpha + l_tile;
       m_run = m_new;
-      // P(j) goes to buffer j & 1 (this group's 64 columns are one 64-element box). Its previous reader, the
-      // product P V of tile j - 2, finished before S(j) did (the tensor core executes in issue order).
-      uint8_t* sPj = sP + (j & 1) * Cfg::kPBytes + wg * (BLOCK_M * 128);
-#pragma unroll
-      for (int chunk = 0; chunk < 8; ++chunk) {
-        uint4 val = make_uint4(pk[chunk * 4], pk[chunk * 4 + 1], pk[chunk * 4 + 2], pk[chunk * 4 + 3]);
-        *reinterpret_cast<uint4*>(sPj + row * 128 + ((chunk ^ (row & 7)) << 4)) = val;
-      }
+      // P(j) overwrites the first half of the S(j) columns this warp has just read (64 keys -> 32 columns)
+      tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(s * BLOCK_N + col_base), pk);
       // rescale O when some row of this warp moved its reference point (each group takes half of the head
       // dimension); O belongs to the previous P V product until that has completed
       if (j > 0 && __any_sync(0xffffffffu, moved)) {
@@ -268,9 +274,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const FwdParams p)
           for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
           tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(Cfg::kOCol + c * 32), ov);
         }
-        tc_wait_st();
       }
-      fence_proxy_async_smem();
+      tc_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
