@@ -24,6 +24,8 @@ borrows the embedding unit's gathered weight.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -65,7 +67,8 @@ class ShardedOptimizer:
     @torch.no_grad()
     def step(self, max_norm: float = 0.0) -> torch.Tensor:
         o = self.owner
-        sumsq = flat_sumsq(o.grad).clone()
+        # the fused reduce-scatter left per-CTA sums of squares of every unit's (fully accumulated) shard
+        sumsq = o._sumsq_partials.sum().reshape(1) if o.fused_reduce is not None else flat_sumsq(o.grad).clone()
         if o.local_grad is not None:
             if o.replica_group is not None:
                 dist.all_reduce(o.local_grad, op=dist.ReduceOp.SUM, group=o.replica_group)
@@ -121,7 +124,7 @@ class ShardedOptimizer:
 class ShardedDataParallel(nn.Module):
     def __init__(self, module, group, checkpoint_layers: bool = True, learning_rate: float = 1e-3,
                  betas=(0.9, 0.95), epsilon: float = 1e-8, weight_decay: float = 0.0,
-                 replica_group=None, replicas: int = 1, prefetch: bool = True) -> None:
+                 replica_group=None, replicas: int = 1, prefetch: bool = True, fused_reduce: bool | None = None) -> None:
         super().__init__()
         if module.norm_placement != "pre":
             raise ValueError("sharded training supports pre-norm models")
@@ -150,7 +153,18 @@ class ShardedDataParallel(nn.Module):
         self.v = torch.zeros(cursor, dtype=torch.float32, device=dev)
         largest = max(u.padded for u in self.units)
         self._full = [torch.empty(largest, dtype=self.dtype, device=dev) for _ in range(2 if self.prefetch else 1)]
-        self._full_grad = torch.zeros(largest, dtype=torch.float32, device=dev)
+        # Gradient reduce-scatter: one fused kernel over symmetric memory (pull + add + shard accumulation +
+        # partial sums of squares) on GPUs, NCCL reduce_scatter + add_ elsewhere or when switched off.
+        if fused_reduce is None:
+            fused_reduce = dev.type == "cuda" and 1 < self.world <= 8 and os.environ.get("AJB_FUSED_FSDP", "1") != "0"
+        self.fused_reduce = None
+        if fused_reduce:
+            from ajllm_b200.parallel.grad_reduce import FusedGradReduce
+            self.fused_reduce = FusedGradReduce(group, dev, largest)
+            self._full_grad = self.fused_reduce.buffer
+            self._sumsq_partials = torch.zeros(len(self.units), FusedGradReduce.CTAS, dtype=torch.float32, device=dev)
+        else:
+            self._full_grad = torch.zeros(largest, dtype=torch.float32, device=dev)
         self._resident: dict[int, int] = {}          # unit index -> slot of self._full holding it
         self._gather_events: dict[int, Any] = {}
         self._side = torch.cuda.Stream(device=dev) if self.prefetch else None
@@ -286,9 +300,13 @@ class ShardedDataParallel(nn.Module):
             if p.grad is not None:
                 p.main_grad.add_(p.grad.to(torch.float32))
                 p.grad = None
-        out = torch.empty(unit.shard, dtype=torch.float32, device=self.device)
-        dist.reduce_scatter_tensor(out, self._full_grad[:unit.padded], op=dist.ReduceOp.SUM, group=self.group)
-        self.grad[unit.base:unit.base + unit.shard].add_(out)
+        if self.fused_reduce is not None:
+            self.fused_reduce.reduce_into(self.grad[unit.base:unit.base + unit.shard], unit.shard, accumulate=True,
+                                          sumsq_partials=self._sumsq_partials[index])
+        else:
+            out = torch.empty(unit.shard, dtype=torch.float32, device=self.device)
+            dist.reduce_scatter_tensor(out, self._full_grad[:unit.padded], op=dist.ReduceOp.SUM, group=self.group)
+            self.grad[unit.base:unit.base + unit.shard].add_(out)
         for p in unit.params:
             p.main_grad = None
 

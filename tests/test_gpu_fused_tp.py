@@ -97,3 +97,60 @@ def test_fused_tensor_parallel_kernels_match_nccl_path(rows_local):
         assert out["status"] == 0, out
         bad = {k: v for k, v in out["errors"].items() if not v < 2e-2}
         assert not bad, bad
+
+
+def _all_reduce_worker(rank: int, world: int, port: int, results):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from ajllm_b200.ops import native
+        from ajllm_b200.parallel.fused import FusedTensorParallel
+
+        fused = FusedTensorParallel(dist.group.WORLD, device)
+        errors = {}
+        # decoding shapes: a handful of rows up to a few hundred, K sharded over the ranks; interleaved with a
+        # reduce-scatter call because both modes share receive buffer, counters and handshake words
+        for trial, (rows, n, k_local) in enumerate([(5, 512, 256), (128, 1024, 384), (300, 768, 512), (5, 512, 256)]):
+            torch.manual_seed(7 + trial)
+            x_all = (torch.randn(world, rows, k_local, device=device) * 0.5).to(torch.bfloat16)
+            w_all = (torch.randn(world, n, k_local, device=device) * 0.05).to(torch.bfloat16)
+            got = fused.gemm_all_reduce(x_all[rank].contiguous(), w_all[rank].contiguous())
+            want = sum(x_all[r].float() @ w_all[r].float().t() for r in range(world))
+            errors[f"ar/{trial}"] = float((got.float() - want).norm() / want.norm())
+            if trial == 1:
+                a = (torch.randn(256, k_local, device=device) * 0.5).to(torch.bfloat16)
+                fused.gemm_reduce_scatter(a, w_all[rank].contiguous(), False, n, k_local)
+        torch.cuda.synchronize()
+        results[rank] = {"errors": errors, "status": native.lib().ajb_check_status()}
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_gemm_all_reduce_for_decoding():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    manager = ctx.Manager()
+    results = manager.dict()
+    port = free_port()
+    procs = [ctx.Process(target=_all_reduce_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "a rank did not finish"
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for rank in range(2):
+        out = results[rank]
+        assert out["status"] == 0, out
+        bad = {k: v for k, v in out["errors"].items() if not v < 2e-2}
+        assert not bad, bad

@@ -1,0 +1,106 @@
+"""Fused gradient reduce-scatter (pull over symmetric memory + shard accumulation + sums of squares) on
+2 GPUs: against a gathered fp32 reference, and inside the sharded data-parallel wrapper against its NCCL
+path. Ranks are child processes, one per GPU."""
+
+import os
+
+import pytest
+import torch
+
+from tests.conftest import free_port
+
+pytestmark = pytest.mark.gpu
+
+MODEL = {"name": "d", "context_length": 256, "d_model": 256, "num_layers": 2, "num_heads": 2, "num_kv_heads": 1, "d_ff": 512,
+         "tie_embeddings": False, "init": {"type": "normal", "std": 0.05}}
+VOCAB = 512
+
+
+def _worker(rank: int, world: int, port: int, results):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from ajllm_b200.models import build_model
+        from ajllm_b200.ops import native
+        from ajllm_b200.parallel.fsdp import ShardedDataParallel
+        from ajllm_b200.parallel.grad_reduce import FusedGradReduce
+
+        out = {}
+        # ---- the kernel on its own: two calls, the second accumulates on top of the first
+        shard = 4096 * 37 + 8
+        reducer = FusedGradReduce(dist.group.WORLD, device, world * shard)
+        dst = torch.zeros(shard, device=device)
+        want = torch.zeros(shard, device=device)
+        partials = torch.zeros(FusedGradReduce.CTAS, device=device)
+        for call in range(2):
+            torch.manual_seed(50 + call)                           # every rank can rebuild every rank's buffer
+            everyone = torch.randn(world, world * shard, device=device)
+            reducer.buffer[: world * shard].copy_(everyone[rank])
+            reducer.reduce_into(dst, shard, accumulate=True, sumsq_partials=partials)
+            want += everyone[:, rank * shard:(rank + 1) * shard].sum(0)
+            torch.cuda.synchronize()
+            dist.barrier()
+        out["kernel_max_abs"] = float((dst - want).abs().max())
+        out["sumsq_rel"] = float((partials.sum() - want.square().sum()).abs() / want.square().sum())
+
+        # ---- inside the sharded wrapper: same model, same batches, fused against NCCL
+        shards = {}
+        for fused in (True, False):
+            torch.manual_seed(0)
+            with torch.device(device):
+                model = build_model(MODEL, VOCAB).to(dtype=torch.bfloat16)
+            fsdp = ShardedDataParallel(model, dist.group.WORLD, learning_rate=1e-3, fused_reduce=fused)
+            opt = fsdp.optimizer
+            norms = []
+            for step in range(2):
+                opt.zero_grad()
+                for micro in range(2):
+                    gen = torch.Generator().manual_seed(1000 + 10 * step + micro)
+                    tokens = torch.randint(0, VOCAB, (2 * world, 129), generator=gen)[rank * 2:(rank + 1) * 2].to(device)
+                    fsdp.loss(tokens[:, :-1], tokens[:, 1:], 0.5)
+                if step == 1:
+                    shards[fused] = fsdp.grad.clone()
+                norms.append(float(opt.step(1.0)))
+            out[f"norms_{fused}"] = norms
+            del fsdp, model
+        ref = shards[False]
+        out["fsdp_grad_rel"] = float((shards[True] - ref).norm() / ref.norm())
+        torch.cuda.synchronize()
+        out["status"] = native.lib().ajb_check_status()
+        results[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_gradient_reduce_scatter():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    manager = ctx.Manager()
+    results = manager.dict()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "a rank did not finish"
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for rank in range(2):
+        out = results[rank]
+        assert out["status"] == 0, out
+        assert out["kernel_max_abs"] < 1e-5, out
+        assert out["sumsq_rel"] < 1e-5, out
+        # the two paths add the same fp32 partials, in a different order at most
+        assert out["fsdp_grad_rel"] < 1e-3, out
+        for a, b in zip(out["norms_True"], out["norms_False"]):
+            assert abs(a - b) <= 1e-3 * max(abs(b), 1e-6), out
