@@ -3,6 +3,7 @@
 //   ag_gemm : C[M, N] = gather_rows(A_shards)[M, K] * op(B)      (column-parallel: all-gather -> GEMM)
 //   gemm_rs : C_local[M/tp, N] = reduce_scatter_rows(A[M, K] * op(B))   (row-parallel: GEMM -> reduce-scatter)
 //   gemm_ar : C[M, N] = sum over ranks of A[M, K] * op(B)                (row-parallel: GEMM -> all-reduce)
+//   gw_gemm : C[M, N] = A[M, K] * W^T, W inside gather(flat weight shards)  (sharded weights: all-gather -> GEMM)
 //
 // Both are one persistent kernel per rank built on the same tcgen05 main loop as gemm_bf16.cu
 // (TMA ring -> tcgen05.mma -> TMEM -> epilogue warps).
@@ -21,6 +22,13 @@
 // gemm_ar (decoding, where M is a few hundred rows at most): the same epilogue stores each partial tile
 // into every rank's receive buffer (slot = this rank), and the closing reduction sums all tp slots over
 // the whole [M, N] output, so the partial products cross NVLink once and no separate collective runs.
+//
+// gw_gemm (fully sharded parameters): the operand that is gathered is the weight. Every rank owns one
+// equal slice of a unit's flat parameter buffer; the copy CTAs pull the peers' slices into the local
+// full buffer exactly as in ag_gemm, and the TMA producer of a tile waits for the slices that its rows
+// of W (a byte range of the flat buffer, which may straddle two slices) live in. Tiles are visited
+// starting with the columns whose weights are already local, so the first products run while the rest
+// of the unit, including parameters this GEMM does not use, is still arriving.
 //
 // Every wait on another CTA or another GPU is bounded (see common.cuh); on expiry the kernel records a
 // status word, skips the dependent work and exits through the normal teardown.
@@ -49,7 +57,7 @@ constexpr int kCopyPiece = 32768;                       // bytes per bulk copy
 constexpr int kCopyBufs = (kStages * kStageBytes + kEpiBytes) / kCopyPiece;   // 6 pieces in flight per copy CTA
 constexpr int kQueue = 4;                               // depth of the per-CTA tile queue
 
-enum Mode : int { kAllGather = 0, kReduceScatter = 1, kAllReduce = 2 };
+enum Mode : int { kAllGather = 0, kReduceScatter = 1, kAllReduce = 2, kGatherWeight = 3 };
 
 struct Params {
   int mode;
@@ -57,6 +65,9 @@ struct Params {
   int tp, rank;
   int m_local;            // rows per rank
   int copy_ctas;          // all-gather: CTAs that move data instead of computing
+  long long shard_bytes;  // bytes each rank contributes to the gathered buffer
+  long long b_offset;     // gather-weight: byte offset of W inside the gathered buffer
+  long long b_row_bytes;  // gather-weight: bytes per row of W
   // all-gather
   const void* stage_ptrs[kMaxRanks];     // each rank's symmetric [m_local, k] staging buffer (peer addresses)
   void* gathered;                        // local [m, k]
@@ -159,7 +170,7 @@ __device__ __forceinline__ void bulk_wait_all_but_latest() { asm volatile("cp.as
 __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* bars, volatile uint32_t* abort_flag) {
   if (threadIdx.x != 0) return;
   const int cta = blockIdx.x, n_copy = p.copy_ctas;
-  const long long shard_bytes = (long long)p.m_local * p.k * 2;
+  const long long shard_bytes = p.shard_bytes;
   const long long pieces = (shard_bytes + kCopyPiece - 1) / kCopyPiece;
   if (cta == 0) {
     // tell every peer that this rank's staging buffer holds the data of this call
@@ -242,14 +253,21 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool is_copy_cta = p.mode == kAllGather && (int)blockIdx.x < p.copy_ctas;
+  const bool gathers = p.mode == kAllGather || p.mode == kGatherWeight;
+  const bool is_copy_cta = gathers && (int)blockIdx.x < p.copy_ctas;
   const int tiles_m_local = p.m_local / BM;
   const int tiles_n = (p.n + BN - 1) / BN;
-  const int shards = p.mode == kAllReduce ? 1 : p.tp;     // all-reduce: one "shard" of m_local = m rows
+  const int shards = (p.mode == kAllReduce || p.mode == kGatherWeight) ? 1 : p.tp;   // one "shard" of m_local = m rows
   const int num_tiles = tiles_m_local * shards * tiles_n;
   const int num_kb = (p.k + BK - 1) / BK;
   // all-gather: the local shard is ready first. reduce-scatter: the rows this rank owns come last.
-  const int first_shard = p.mode == kAllGather ? p.rank : (p.mode == kAllReduce ? 0 : (p.rank + 1) % p.tp);
+  const int first_shard = p.mode == kAllGather ? p.rank : (p.mode == kReduceScatter ? (p.rank + 1) % p.tp : 0);
+  // gather-weight: start with the column block whose weight rows begin in this rank's own slice
+  int tn_first = 0;
+  if (p.mode == kGatherWeight) {
+    const long long own = (long long)p.rank * p.shard_bytes - p.b_offset;
+    if (own > 0) tn_first = (int)min((long long)tiles_n - 1, (own + (long long)BN * p.b_row_bytes - 1) / ((long long)BN * p.b_row_bytes));
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -290,6 +308,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0, ready_shard = p.rank;
+      uint32_t ready_mask = 0;          // gather-weight: slices known to have arrived
       bool ok = *abort_flag == 0;
       for (uint32_t qi = 0; ok; ++qi) {
         const int slot = qi % kQueue;
@@ -300,6 +319,19 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (tile >= num_tiles) break;
         int shard, tm, tn;
         tile_coords(tile, tiles_m_local, tiles_n, shards, first_shard, p.mode == kReduceScatter, shard, tm, tn);
+        if (p.mode == kGatherWeight) {
+          tn = (tn + tn_first) % tiles_n;
+          // slices of the flat buffer that hold rows [tn * BN, tn * BN + BN) of W
+          const long long lo = p.b_offset + (long long)tn * BN * p.b_row_bytes;
+          const long long hi = p.b_offset + (long long)min(tn * BN + BN, p.n) * p.b_row_bytes - 1;
+          for (int sh = (int)(lo / p.shard_bytes); sh <= (int)(hi / p.shard_bytes) && ok; ++sh) {
+            if (sh == p.rank || (ready_mask >> sh) & 1u) continue;
+            if (!wait_ge(p.shard_flags + sh, (unsigned)p.copy_ctas, false, abort_flag, p.status, 11)) { ok = false; break; }
+            fence_proxy_async_all();
+            ready_mask |= 1u << sh;
+          }
+          if (!ok) break;
+        }
         if (p.mode == kAllGather && shard != ready_shard) {
           if (!wait_ge(p.shard_flags + shard, (unsigned)p.copy_ctas, false, abort_flag, p.status, 10)) { ok = false; break; }
           fence_proxy_async_all();      // copied rows were written through the async proxy of other CTAs
@@ -396,6 +428,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t use = qi >> 1;
       int shard, tm, tn;
       tile_coords(tile, tiles_m_local, tiles_n, shards, first_shard, p.mode == kReduceScatter, shard, tm, tn);
+      if (p.mode == kGatherWeight) tn = (tn + tn_first) % tiles_n;
       if (!mbar_wait(&acc_full[buf], use & 1, abort_flag, p.status, kCommGemm, 4)) { ok = false; break; }
       tc_fence_after_sync();
       bulk_wait_read_all();          // the previous tile's store has read this lane's staging row
@@ -435,7 +468,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       } else {
         __nv_bfloat16* dst;
-        if (p.mode == kAllGather) {
+        if (p.mode == kAllGather || p.mode == kGatherWeight) {
           dst = reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row * p.ldc + col0;
         } else {
           // partial sums of shard `shard` go to that rank's receive buffer, slot = this rank
@@ -448,7 +481,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // the previous tile had a whole tile time to land: wait for it (not for the one just issued) and announce it
       bulk_wait_all_but_latest();
       announce(pending_shard);
-      pending_shard = p.mode == kReduceScatter ? shard : (p.mode == kAllReduce ? p.tp : -1);
+      pending_shard = p.mode == kReduceScatter ? shard : (p.mode == kAllReduce ? p.tp : -1);   // gathers announce nothing
     }
     bulk_wait_all();
     announce(pending_shard);
@@ -461,7 +494,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tmem_dealloc(tmem_base, 2 * BN);
   }
 
-  if (p.mode != kAllGather) {
+  if (p.mode == kReduceScatter || p.mode == kAllReduce) {
     // ---- sum the tp partial copies of the rows this rank owns (all-reduce: of all rows) (fp32) into the local output
     int* arrived = reinterpret_cast<int*>(epi_base);
     if (threadIdx.x == 0) {
@@ -529,6 +562,8 @@ struct AjbCommArgs {
   unsigned int expected_count;
   unsigned int epoch;
   int a_rows;                    // all-reduce: rows of `a` that exist (<= m; the tiles above them read zeros); 0 means m
+  long long shard_elems;         // gather-weight: bf16 elements per rank slice of the flat buffer (multiple of 8)
+  long long b_offset_elems;      // gather-weight: first element of W inside the gathered buffer (multiple of 8)
 };
 
 extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
@@ -536,8 +571,14 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   using namespace ajb::comm;
   const AjbCommArgs& a = *args;
   AJB_REQUIRE(a.tp >= 2 && a.tp <= kMaxRanks, "comm_gemm: tp must be in [2, %d]", kMaxRanks);
-  if (a.mode == kAllReduce) {
-    AJB_REQUIRE(a.m % BM == 0, "comm_gemm: all-reduce rows (%d) must be a multiple of %d", a.m, BM);
+  if (a.mode == kAllReduce || a.mode == kGatherWeight) {
+    AJB_REQUIRE(a.m % BM == 0, "comm_gemm: rows (%d) must be a multiple of %d", a.m, BM);
+    if (a.mode == kGatherWeight) {
+      AJB_REQUIRE(!a.b_mn_major && a.ldb == a.k, "comm_gemm: gathered weights must be dense [n, k] rows");
+      AJB_REQUIRE(a.shard_elems > 0 && a.shard_elems % 8 == 0 && a.b_offset_elems % 8 == 0,
+                  "comm_gemm: slice length and weight offset must be multiples of 8 elements");
+      AJB_REQUIRE(a.b_offset_elems + (long long)a.n * a.k <= a.shard_elems * a.tp, "comm_gemm: W lies outside the gathered buffer");
+    }
   } else {
     AJB_REQUIRE(a.m % a.tp == 0 && (a.m / a.tp) % BM == 0, "comm_gemm: rows per rank (%d / %d) must be a multiple of %d",
                 a.m, a.tp, BM);
@@ -547,8 +588,12 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   Params p;
   memset(&p, 0, sizeof(p));
   p.mode = a.mode; p.m = a.m; p.n = a.n; p.k = a.k; p.tp = a.tp; p.rank = a.rank;
-  p.m_local = a.mode == kAllReduce ? a.m : a.m / a.tp;
-  p.copy_ctas = a.mode == kAllGather ? a.copy_ctas : 0;
+  p.m_local = (a.mode == kAllReduce || a.mode == kGatherWeight) ? a.m : a.m / a.tp;
+  const bool gathers = a.mode == kAllGather || a.mode == kGatherWeight;
+  p.copy_ctas = gathers ? a.copy_ctas : 0;
+  p.shard_bytes = a.mode == kGatherWeight ? a.shard_elems * 2 : (long long)p.m_local * a.k * 2;
+  p.b_offset = a.b_offset_elems * 2;
+  p.b_row_bytes = (long long)a.k * 2;
   for (int r = 0; r < a.tp; ++r) {
     p.stage_ptrs[r] = a.stage_ptrs[r];
     p.recv_ptrs[r] = a.recv_ptrs[r];
@@ -568,13 +613,14 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   AJB_CUDA_OK(cudaMemsetAsync(a.shard_flags, 0, 16 * sizeof(unsigned int), s));
 
   const void* a_ptr = a.mode == kAllGather ? a.gathered : a.a;
+  const void* b_ptr = a.mode == kGatherWeight ? static_cast<const void*>(static_cast<const uint8_t*>(a.gathered) + a.b_offset_elems * 2) : a.b;
   CUtensorMap map_a, map_b;
   const int a_rows = (a.mode == kAllReduce && a.a_rows > 0) ? a.a_rows : a.m;
   AJB_REQUIRE(a_rows <= a.m, "comm_gemm: a_rows (%d) exceeds m (%d)", a_rows, a.m);
   int rc = make_tensor_map_2d(&map_a, a_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, a.k, (uint64_t)a.k * 2, BM, 64);
   if (rc) return rc;
-  if (a.b_mn_major) rc = make_tensor_map_2d(&map_b, a.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.k, a.n, a.ldb * 2, BK, 64);
-  else              rc = make_tensor_map_2d(&map_b, a.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.k, a.ldb * 2, BN, 64);
+  if (a.b_mn_major) rc = make_tensor_map_2d(&map_b, b_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.k, a.n, a.ldb * 2, BK, 64);
+  else              rc = make_tensor_map_2d(&map_b, b_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.k, a.ldb * 2, BN, 64);
   if (rc) return rc;
   static bool configured[2] = {false, false};
   const int which = a.b_mn_major ? 1 : 0;
@@ -585,7 +631,7 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   }
   // every CTA of this kernel must be resident at once (copy CTAs feed compute CTAs): one CTA per SM
   const int grid = sm_count();
-  AJB_REQUIRE(p.copy_ctas < grid && (a.mode != kAllGather || p.copy_ctas >= 1), "comm_gemm: copy CTA count %d is out of range", p.copy_ctas);
+  AJB_REQUIRE(p.copy_ctas < grid && (!gathers || p.copy_ctas >= 1), "comm_gemm: copy CTA count %d is out of range", p.copy_ctas);
   if (which) comm_gemm_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
   else       comm_gemm_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
   AJB_CUDA_OK(cudaGetLastError());

@@ -22,7 +22,7 @@ from ajllm_b200.ops import native
 from ajllm_b200.ops.functional import EPI_ACCUM_F32, gemm
 
 _MAX_RANKS = 8
-MODE_ALL_GATHER, MODE_REDUCE_SCATTER, MODE_ALL_REDUCE = 0, 1, 2
+MODE_ALL_GATHER, MODE_REDUCE_SCATTER, MODE_ALL_REDUCE, MODE_GATHER_WEIGHT = 0, 1, 2, 3
 
 
 class _CommArgs(ctypes.Structure):
@@ -35,7 +35,7 @@ class _CommArgs(ctypes.Structure):
         ("counter_ptrs", ctypes.c_void_p * _MAX_RANKS), ("ready_ptrs", ctypes.c_void_p * _MAX_RANKS),
         ("done_ptrs", ctypes.c_void_p * _MAX_RANKS),
         ("shard_flags", ctypes.c_void_p), ("expected_count", ctypes.c_uint), ("epoch", ctypes.c_uint),
-        ("a_rows", ctypes.c_int),
+        ("a_rows", ctypes.c_int), ("shard_elems", ctypes.c_longlong), ("b_offset_elems", ctypes.c_longlong),
     ]
 
 
@@ -88,17 +88,19 @@ class FusedTensorParallel:
         return rows_total % self.size == 0 and (rows_total // self.size) % self.BLOCK_M == 0
 
     def _launch(self, mode: int, m: int, n: int, k: int, b: torch.Tensor, b_mn: bool, out: torch.Tensor,
-                a: torch.Tensor | None = None, gathered: torch.Tensor | None = None, a_rows: int = 0) -> None:
+                a: torch.Tensor | None = None, gathered: torch.Tensor | None = None, a_rows: int = 0,
+                shard_elems: int = 0, b_offset_elems: int = 0) -> None:
         self.epoch += 1
         args = _CommArgs()
         args.mode, args.m, args.n, args.k = mode, m, n, k
         args.tp, args.rank, args.b_mn_major, args.copy_ctas = self.size, self.rank, int(b_mn), self.copy_ctas
-        args.ldb, args.ldc = b.stride(0), out.stride(0)
+        args.ldb, args.ldc = (b.stride(0) if b.dim() == 2 else k), out.stride(0)
+        args.shard_elems, args.b_offset_elems = shard_elems, b_offset_elems
         args.a = a.data_ptr() if a is not None else None
         args.b, args.out = b.data_ptr(), out.data_ptr()
         args.gathered = gathered.data_ptr() if gathered is not None else None
         args.a_rows = a_rows
-        if mode != MODE_ALL_GATHER:
+        if mode in (MODE_REDUCE_SCATTER, MODE_ALL_REDUCE):
             rows = m if mode == MODE_ALL_REDUCE else m // self.size
             tiles = (rows // self.BLOCK_M) * ((n + self.BLOCK_N - 1) // self.BLOCK_N)
             self.expected_count += tiles * 4          # one count per epilogue warp per tile
@@ -151,6 +153,25 @@ class FusedTensorParallel:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
         self._launch(MODE_ALL_REDUCE, m, n, k, weight, False, out, a=x.contiguous(), a_rows=rows)
         return out[:rows]
+
+    def gather_weight_gemm(self, x: torch.Tensor, shard: torch.Tensor, n: int, k: int, offset_elems: int = 0):
+        """``x @ W^T`` where ``W [n, k]`` starts at element ``offset_elems`` of the flat parameter buffer that is
+        the concatenation of every rank's ``shard`` (fully sharded weights; inference or the forward of a unit).
+
+        Returns ``(flat, out)``: the gathered flat buffer (all parameters of the unit, usable by the GEMMs
+        that follow) and ``out [rows, n]``. The peers' slices travel while the first tiles are computed."""
+        rows = x.shape[0]
+        if rows % self.BLOCK_M != 0 or x.dtype != torch.bfloat16 or shard.dtype != torch.bfloat16:
+            raise ValueError("gather_weight_gemm needs bf16 operands and a multiple of 128 rows")
+        shard_elems = shard.numel()
+        self._ensure("stage", shard_elems * 2)
+        self._stage[: shard_elems * 2].view(torch.bfloat16).copy_(shard.reshape(-1))
+        flat = torch.empty(self.size * shard_elems, dtype=torch.bfloat16, device=self.device)
+        flat[self.rank * shard_elems:(self.rank + 1) * shard_elems].copy_(shard.reshape(-1))   # the kernel moves remote slices
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=self.device)
+        self._launch(MODE_GATHER_WEIGHT, rows, n, k, flat, False, out, a=x.contiguous(), gathered=flat,
+                     shard_elems=shard_elems, b_offset_elems=offset_elems)
+        return flat, out
 
     # ------------------------------------------------------------------ differentiable entry points
     def gather_linear(self, x_local: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -105,9 +105,9 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
         if "fsdp" not in defaults and "tp" not in defaults:
             defaults["fsdp"] = world
         sizes = check_parallel(defaults, world)
-        if sizes["pp"] != 1:
-            raise ValueError("pipeline parallelism is not part of this build; use tp / fsdp / ep")
-        mesh = ParallelMesh(tp=sizes["tp"], fsdp=sizes["fsdp"], ep=sizes["ep"])
+        if sizes["pp"] != 1 and (sizes["tp"] != 1 or sizes["fsdp"] != 1 or sizes["ep"] != 1):
+            raise ValueError("pipeline parallelism runs on its own here: set tp = fsdp = ep = 1 (pp = world size)")
+        mesh = ParallelMesh(tp=sizes["tp"], fsdp=sizes["fsdp"], ep=sizes["ep"], pp=sizes["pp"])
         if sizes["tp"] > 1:
             tp = TensorParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size)
         if sizes["ep"] > 1:
@@ -124,7 +124,12 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
     dp_size = mesh.dp_size if mesh is not None else 1
     dp_rank = mesh.dp_index if mesh is not None else 0
     loss_group = None
-    if mesh is not None and use_fsdp and dp_size > 1:
+    if mesh is not None and sizes["pp"] > 1:
+        from ajllm_b200.parallel import PipelineParallel, pp_optimizer_classes
+        micro = int((data.get("parallel", {}) or {}).get("pp_microbatches", sizes["pp"]))
+        model = PipelineParallel(model, mesh.pp.group, micro)
+        optimizer = FlatAdamW(model.module, classes=pp_optimizer_classes(mesh.pp.group), **_optimizer_kwargs(data))
+    elif mesh is not None and use_fsdp and dp_size > 1:
         from ajllm_b200.parallel.fsdp import ShardedDataParallel
         model = ShardedDataParallel(model, mesh.dp.group, checkpoint_layers=(checkpointing != "none"),
                                     **_optimizer_kwargs(data))

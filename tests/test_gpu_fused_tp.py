@@ -125,6 +125,17 @@ def _all_reduce_worker(rank: int, world: int, port: int, results):
             if trial == 1:
                 a = (torch.randn(256, k_local, device=device) * 0.5).to(torch.bfloat16)
                 fused.gemm_reduce_scatter(a, w_all[rank].contiguous(), False, n, k_local)
+        # fully sharded weights: W [n, k] sits at an offset inside a flat buffer whose equal slices (cut in the
+        # middle of a row) live on the ranks; the slices are gathered while x @ W^T is computed
+        for trial, (rows, n, k, offset, shard) in enumerate([(256, 640, 512, 0, 170000), (128, 304, 256, 4096, 64008)]):
+            torch.manual_seed(31 + trial)
+            flat_all = (torch.randn(world * shard, device=device) * 0.05).to(torch.bfloat16)
+            x = (torch.randn(rows, k, device=device) * 0.5).to(torch.bfloat16)
+            flat, got = fused.gather_weight_gemm(x, flat_all[rank * shard:(rank + 1) * shard].clone(), n, k, offset)
+            w = flat_all[offset:offset + n * k].view(n, k)
+            want = x.float() @ w.float().t()
+            errors[f"gw/{trial}"] = float((got.float() - want).norm() / want.norm())
+            errors[f"gw/flat/{trial}"] = float((flat.float() - flat_all.float()).abs().max())
         torch.cuda.synchronize()
         results[rank] = {"errors": errors, "status": native.lib().ajb_check_status()}
     finally:
