@@ -368,6 +368,9 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     constexpr uint32_t idesc = make_idesc(BM, BN, 1, false, B_MN);
+    // descriptor low words formed once; a stage is one multiply-add away, a k-step a compile-time offset
+    const uint32_t a_lo0 = desc_lo_k_major(smem_u32(smem));
+    const uint32_t b_lo0 = B_MN ? desc_lo_mn_major(smem_u32(smem) + kABytes, BK * 128) : desc_lo_k_major(smem_u32(smem) + kABytes);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -387,14 +390,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kCommGemm, 3)) { ok = false; break; }
         tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
-          const uint32_t sb = sa + kABytes;
+          const uint32_t a_lo = a_lo0 + (uint32_t)stage * (uint32_t)(kStageBytes >> 4);
+          const uint32_t b_lo = b_lo0 + (uint32_t)stage * (uint32_t)(kStageBytes >> 4);
+          umma_f16(tmem_d, desc_at(a_lo, 0), desc_at(b_lo, 0), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = desc_k_major(sa, k * UMMA_K * 2);
-            const uint64_t db = B_MN ? desc_mn_major(sb, BK * 128, k * UMMA_K) : desc_k_major(sb, k * UMMA_K * 2);
-            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 1; k < BK / UMMA_K; ++k)
+            umma_f16_c<true>(tmem_d, desc_at(a_lo, (uint32_t)k * UMMA_K * 2),
+                             desc_at(b_lo, B_MN ? mn_major_step(k) : (uint32_t)k * UMMA_K * 2), idesc);
           tc_commit(&empty[stage]);
         }
         __syncwarp();

@@ -188,6 +188,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc(BM, BN, /*bf16*/ 1, A_MN, B_MN);
+    // The issuing thread has 128 cycles per product (N = 256): descriptor low words are formed once, a
+    // stage is one multiply-add away and a k-step a compile-time offset (see common.cuh).
+    const uint32_t a_lo0 = A_MN ? desc_lo_mn_major(smem_u32(stage_base), BK * 128) : desc_lo_k_major(smem_u32(stage_base));
+    const uint32_t b_lo0 = B_MN ? desc_lo_mn_major(smem_u32(stage_base) + Cfg::kABytes, BK * 128)
+                                : desc_lo_k_major(smem_u32(stage_base) + Cfg::kABytes);
     int stage = 0;
     uint32_t phase = 0;
     int iter = 0;
@@ -209,14 +214,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kGemm, 3)) { ok = false; break; }
         tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t sa = smem_u32(stage_base + stage * Cfg::kStageBytes);
-          const uint32_t sb = sa + Cfg::kABytes;
+          const uint32_t a_lo = a_lo0 + (uint32_t)stage * (uint32_t)(Cfg::kStageBytes >> 4);
+          const uint32_t b_lo = b_lo0 + (uint32_t)stage * (uint32_t)(Cfg::kStageBytes >> 4);
+          umma_f16(tmem_d, desc_at(a_lo, 0), desc_at(b_lo, 0), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = A_MN ? desc_mn_major(sa, BK * 128, k * UMMA_K) : desc_k_major(sa, k * UMMA_K * 2);
-            const uint64_t db = B_MN ? desc_mn_major(sb, BK * 128, k * UMMA_K) : desc_k_major(sb, k * UMMA_K * 2);
-            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 1; k < BK / UMMA_K; ++k)
+            umma_f16_c<true>(tmem_d, desc_at(a_lo, A_MN ? mn_major_step(k) : (uint32_t)k * UMMA_K * 2),
+                             desc_at(b_lo, B_MN ? mn_major_step(k) : (uint32_t)k * UMMA_K * 2), idesc);
           tc_commit(&empty[stage]);  // frees the smem slot once these MMAs have read it
         }
         __syncwarp();

@@ -12,8 +12,11 @@
 namespace ajb {
 namespace probe {
 
-template <int N, int A_SRC, int B_MN>   // A_SRC: 0 shared K-major, 1 shared MN-major, 2 tensor memory
-__global__ void __launch_bounds__(192, 1) mma_probe_kernel(long long* out, int iters, uint32_t commit_mask) {
+// A_SRC: 0 shared K-major, 1 shared MN-major, 2 tensor memory. COMMIT_EVERY: a tcgen05.commit after every so many
+// products (0: none). Everything that varies is a template parameter: a run-time test between two products
+// already doubles the measured cost.
+template <int N, int A_SRC, int B_MN, int COMMIT_EVERY>
+__global__ void __launch_bounds__(192, 1) mma_probe_kernel(long long* out, int iters) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t bar, scratch_bar;
   __shared__ uint32_t tmem_slot;
@@ -53,7 +56,7 @@ __global__ void __launch_bounds__(192, 1) mma_probe_kernel(long long* out, int i
           if (k) umma_f16_c<true>(d, desc_at(a_lo, a_off), desc_at(b_lo, b_off), idesc);
           else umma_f16_c<false>(d, desc_at(a_lo, a_off), desc_at(b_lo, b_off), idesc);
         }
-        if ((commit_mask >> k) & 1u) tc_commit(&scratch_bar);   // one shift and test: the issue loop must stay lean
+        if (COMMIT_EVERY > 0 && (k + 1) % COMMIT_EVERY == 0) tc_commit(&scratch_bar);
       }
     }
     tc_commit(&bar);
@@ -69,23 +72,26 @@ __global__ void __launch_bounds__(192, 1) mma_probe_kernel(long long* out, int i
   }
 }
 
-template <int N, int A_SRC, int B_MN>
-static int run(long long* out, int iters, int commit_every, cudaStream_t s) {
+template <int N, int A_SRC, int B_MN, int COMMIT_EVERY>
+static int run(long long* out, int iters, cudaStream_t s) {
   constexpr int kSmem = 200 * 1024;
-  AJB_CUDA_OK(cudaFuncSetAttribute(mma_probe_kernel<N, A_SRC, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-  uint32_t mask = 0;
-  for (int k = 0; k < 8; ++k)
-    if (commit_every > 0 && (k + 1) % commit_every == 0) mask |= 1u << k;
-  mma_probe_kernel<N, A_SRC, B_MN><<<sm_count(), 192, kSmem, s>>>(out, iters, mask);
+  AJB_CUDA_OK(cudaFuncSetAttribute(mma_probe_kernel<N, A_SRC, B_MN, COMMIT_EVERY>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+  mma_probe_kernel<N, A_SRC, B_MN, COMMIT_EVERY><<<sm_count(), 192, kSmem, s>>>(out, iters);
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 template <int N>
-static int run_n(int a_src, int b_mn, long long* out, int iters, int commit_every, cudaStream_t s) {
-  if (a_src == 0) return b_mn ? run<N, 0, 1>(out, iters, commit_every, s) : run<N, 0, 0>(out, iters, commit_every, s);
-  if (a_src == 1) return b_mn ? run<N, 1, 1>(out, iters, commit_every, s) : run<N, 1, 0>(out, iters, commit_every, s);
-  return b_mn ? run<N, 2, 1>(out, iters, commit_every, s) : run<N, 2, 0>(out, iters, commit_every, s);
+static int run_n(int a_src, int b_mn, int commit_every, long long* out, int iters, cudaStream_t s) {
+  if (commit_every == 4 && a_src == 0 && !b_mn) return run<N, 0, 0, 4>(out, iters, s);
+  if (commit_every == 1 && a_src == 0 && !b_mn) return run<N, 0, 0, 1>(out, iters, s);
+  if (commit_every != 0) {
+    set_error("mma_probe: commits are measured with both operands K-major in shared memory, every 1 or 4 products");
+    return 2;
+  }
+  if (a_src == 0) return b_mn ? run<N, 0, 1, 0>(out, iters, s) : run<N, 0, 0, 0>(out, iters, s);
+  if (a_src == 1) return b_mn ? run<N, 1, 1, 0>(out, iters, s) : run<N, 1, 0, 0>(out, iters, s);
+  return b_mn ? run<N, 2, 1, 0>(out, iters, s) : run<N, 2, 0, 0>(out, iters, s);
 }
 
 }  // namespace probe
@@ -98,7 +104,7 @@ extern "C" int ajb_mma_probe(int n, int a_source, int b_mn_major, int commit_eve
   AJB_REQUIRE(a_source >= 0 && a_source <= 2 && iters > 0 && iters <= 4096, "mma_probe: bad arguments");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   long long* out = reinterpret_cast<long long*>(cycles_out);
-  if (n == 64) return probe::run_n<64>(a_source, b_mn_major, out, iters, commit_every, s);
-  if (n == 128) return probe::run_n<128>(a_source, b_mn_major, out, iters, commit_every, s);
-  return probe::run_n<256>(a_source, b_mn_major, out, iters, commit_every, s);
+  if (n == 64) return probe::run_n<64>(a_source, b_mn_major, commit_every, out, iters, s);
+  if (n == 128) return probe::run_n<128>(a_source, b_mn_major, commit_every, out, iters, s);
+  return probe::run_n<256>(a_source, b_mn_major, commit_every, out, iters, s);
 }
