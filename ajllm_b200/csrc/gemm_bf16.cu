@@ -55,6 +55,10 @@ struct Params {
   // c + s * split_stride (fp32 store epilogue) and a small kernel sums the slices afterwards.
   int split_k;
   long long split_stride;
+  // transposed store: element (row, col) of the product goes to c[col * ldc + row]. Decoding computes
+  // (W x^T)^T this way: the weight rows fill the 128-row side of the tile whatever the batch size, and
+  // the few activation rows are the narrow side.
+  int transpose_c;
   DeviceStatus* status;
 };
 
@@ -254,6 +258,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int col = col0 + c;
         if (!row_ok || col >= p.n) continue;
         const int valid = min(32, p.n - col);
+        if (p.transpose_c) {
+          // consecutive lanes hold consecutive rows: each store instruction writes 32 neighbours of one output row
+          const long long base = b * (p.split_k > 1 ? p.split_stride : p.c_batch_stride) + (long long)col * p.ldc + row;
+          if (p.epilogue == kStoreBf16) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + base;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) dst[(long long)j * p.ldc] = __float2bfloat16(__uint_as_float(v[j]));
+          } else {
+            float* dst = reinterpret_cast<float*>(p.c) + base;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) dst[(long long)j * p.ldc] = __uint_as_float(v[j]);
+          }
+          continue;
+        }
         if (p.epilogue == kStoreBf16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + b * (p.split_k > 1 ? p.split_stride : p.c_batch_stride) + (long long)row * p.ldc + col;
           if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
@@ -313,6 +333,7 @@ struct BatchSpec {
   int segment_rows = 0;
   int split_k = 1;
   long long split_stride = 0;
+  int transpose_c = 0;
 };
 
 template <int BN, bool A_MN, bool B_MN, bool BATCHED>
@@ -353,6 +374,7 @@ static int launch(const void* a, const void* b, void* c, int m, int n, int k, lo
   p.segment_rows = spec.segment_rows > 0 ? spec.segment_rows : m;
   p.split_k = spec.split_k;
   p.split_stride = spec.split_stride;
+  p.transpose_c = spec.transpose_c;
   p.status = device_status_buffer();
   const long long tiles = (long long)p.tiles_m * p.tiles_n * spec.batch * spec.split_k;
   const int grid = tiles < sm_count() ? (int)tiles : sm_count();
@@ -455,6 +477,29 @@ extern "C" int ajb_gemm_bf16_splitk(const void* a, const void* b, void* c, void*
   const long long vecs = (long long)m * n / 8;
   const int blocks = (int)((vecs + 255) / 256 < (long long)sm_count() * 8 ? (vecs + 255) / 256 : (long long)sm_count() * 8);
   gemm::splitk_reduce_kernel<<<blocks, 256, 0, s>>>((const float*)workspace, (__nv_bfloat16*)c, vecs, (long long)m * n, split_k);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Decoding GEMM: out[rows, n] bf16 = x[rows, k] w[n, k]^T for rows <= 128, computed as (w x^T)^T: the tile's
+// 128-row side is filled by weight rows, so there are n / 128 tiles times `split_k` K slices streaming the
+// weights, and the partial products are rows x 128 instead of 128 x 256. workspace: split_k * rows * n floats.
+extern "C" int ajb_gemm_bf16_decode(const void* x, const void* w, void* out, void* workspace, int rows, int n, int k,
+                                    long long ldx, long long ldw, int split_k, void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(rows > 0 && rows <= 128 && n > 0 && k > 0 && split_k >= 1, "decode gemm: bad problem");
+  AJB_REQUIRE(n % 8 == 0, "decode gemm: n must be a multiple of 8");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  gemm::BatchSpec spec;
+  spec.transpose_c = 1;
+  if (split_k == 1) return gemm::dispatch<false>(w, x, out, n, rows, k, ldw, ldx, n, 0, 0, 0, spec, s);
+  spec.split_k = split_k;
+  spec.split_stride = (long long)rows * n;
+  int rc = gemm::dispatch<false>(w, x, workspace, n, rows, k, ldw, ldx, n, 0, 0, /*fp32 store*/ 2, spec, s);
+  if (rc) return rc;
+  const long long vecs = (long long)rows * n / 8;
+  const int blocks = (int)((vecs + 255) / 256 < (long long)sm_count() * 8 ? (vecs + 255) / 256 : (long long)sm_count() * 8);
+  gemm::splitk_reduce_kernel<<<blocks, 256, 0, s>>>((const float*)workspace, (__nv_bfloat16*)out, vecs, (long long)rows * n, split_k);
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }

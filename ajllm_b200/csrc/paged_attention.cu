@@ -9,6 +9,13 @@
 // softmax warps whose 32-row quarter holds real rows do any work. Row (head h, new token i) may see
 // keys 0 .. context_len - q_len + i.
 //
+// Plain decoding has 4 to 8 real rows, all in the first quarter, and one warp would do the softmax of
+// 128 columns per tile while three idle. With at most 32 rows (REPL) the query rows are therefore staged
+// four times, once per 32-lane quarter: the score tile then holds four identical copies, and warp q
+// works on key columns [32 q, 32 q + 32) of its own copy. The four partial row maxima (and at the end the
+// partial row sums) are exchanged through shared memory; P is assembled in rows 0..31 of the operand
+// tile, so only the first quarter of O is meaningful and the first warp alone rescales and stores it.
+//
 // Layouts: q [tokens, Hq, hd] bf16 (rows of a sequence are contiguous, `q_start[seq]` is its first
 // row); caches [num_blocks, block_size = 16, Hkv, hd] bf16; block_tables [num_seqs, max_blocks] int32;
 // out like q.
@@ -28,7 +35,8 @@ template <int HD>
 struct Cfg {
   static constexpr int kTile = TILE * HD * 2;
   static constexpr int kP = TILE * TILE * 2;
-  static constexpr int kSmem = kTile /*Q*/ + 4 * kTile /*2 x (K,V)*/ + kP + 256;
+  static constexpr int kExchange = 2 * 4 * 32 * 4;   // [parity][quarter][row] partial maxima / sums (REPL)
+  static constexpr int kSmem = kTile /*Q*/ + 4 * kTile /*2 x (K,V)*/ + kP + kExchange + 256;
   static constexpr int kOCol = 256;
 };
 
@@ -49,7 +57,7 @@ __device__ __forceinline__ void store_chunk(uint8_t* tile, int row, int ch, uint
   *reinterpret_cast<uint4*>(dst) = val;
 }
 
-template <int HD>
+template <int HD, bool REPL>
 __global__ void __launch_bounds__(kThreads, 1)
 paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const Params p) {
@@ -59,7 +67,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + C::kTile;
   uint8_t* sP = sKV + 4 * C::kTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kP);
+  float* sExchange = reinterpret_cast<float*>(sP + C::kP);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kP + C::kExchange);
   if (smem_misaligned(smem, p.status, kPagedKernelId, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* kv_full = bars;        // 2
   uint64_t* kv_empty = bars + 2;   // 2
@@ -67,7 +76,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   uint64_t* s_free = bars + 6;     // 2
   uint64_t* p_ready = bars + 8;    // 1
   uint64_t* pv_done = bars + 9;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* xbar = bars + 10;      // 1 (REPL: the four softmax warps exchange partial maxima / sums)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,6 +98,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     mbar_init(p_ready, 4);
     mbar_init(pv_done, 1);
+    mbar_init(xbar, 4);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensor_map(&map_k);
@@ -100,8 +111,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // stage Q: rows beyond `rows` are zero (their scores are never used)
   if (warp >= 2) {
     const int t = threadIdx.x - 64;                 // 0..127 == tile row
-    const bool real = t < rows;
-    const int h = real ? t / p.q_len : 0, i = real ? t % p.q_len : 0;
+    const int qr = REPL ? (t & 31) : t;             // REPL: every quarter holds a copy of the query rows
+    const bool real = qr < rows;
+    const int h = real ? qr / p.q_len : 0, i = real ? qr % p.q_len : 0;
     const __nv_bfloat16* src = p.q + ((size_t)(p.q_start[seq] + i) * p.heads + kv_head * group + h) * HD;
 #pragma unroll
     for (int ch = 0; ch < HD / 8; ++ch) {
@@ -140,7 +152,11 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   } else if (warp == 1) {
     constexpr uint32_t idesc_s = make_idesc(TILE, TILE, 1, false, false);
     constexpr uint32_t idesc_o = make_idesc(TILE, HD, 1, false, true);
-    const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+    // descriptor low words; a k-step is a compile-time offset added to one of these (see common.cuh)
+    const uint32_t q_km = desc_lo_k_major(smem_u32(sQ)), p_km = desc_lo_k_major(smem_u32(sP));
+    const uint32_t k_km0 = desc_lo_k_major(smem_u32(sKV));
+    const uint32_t v_mn0 = desc_lo_mn_major(smem_u32(sKV) + C::kTile, TILE * 128);
+    constexpr uint32_t kStageStep = (2 * C::kTile) >> 4;
     bool ok = true;
     auto issue_s = [&](int j) -> bool {
       const int s = j & 1;
@@ -149,12 +165,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       if (!mbar_wait(&s_free[s], (use & 1) ^ 1, abort_flag, p.status, kPagedKernelId, 4)) return false;
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t aK = smem_u32(sKV + s * 2 * C::kTile);
+        const uint32_t k_km = k_km0 + (uint32_t)s * kStageStep;
+        const uint32_t d = tmem_base + (uint32_t)(s * TILE);
+        umma_f16_c<false>(d, desc_at(q_km, 0), desc_at(k_km, 0), idesc_s);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t box = (uint32_t)(k / 4) * (TILE * 128), off = (uint32_t)(k % 4) * 32;
-          umma_f16(tmem_base + (uint32_t)(s * TILE), desc_k_major(aQ + box, off), desc_k_major(aK + box, off), idesc_s, k != 0);
-        }
+        for (int k = 1; k < HD / 16; ++k)
+          umma_f16_c<true>(d, desc_at(q_km, k_major_step(k, TILE * 128)), desc_at(k_km, k_major_step(k, TILE * 128)), idesc_s);
         tc_commit(&s_full[s]);
       }
       __syncwarp();
@@ -169,17 +185,123 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       if (!mbar_wait(p_ready, (uint32_t)j & 1, abort_flag, p.status, kPagedKernelId, 5)) { ok = false; break; }
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t aV = smem_u32(sKV + (j & 1) * 2 * C::kTile + C::kTile);
+        const uint32_t v_mn = v_mn0 + (uint32_t)(j & 1) * kStageStep;
+        umma_f16(tmem_base + C::kOCol, desc_at(p_km, 0), desc_at(v_mn, 0), idesc_o, j != 0);
 #pragma unroll
-        for (int k = 0; k < TILE / 16; ++k) {
-          const uint32_t pbox = (uint32_t)(k / 4) * (TILE * 128), poff = (uint32_t)(k % 4) * 32;
-          umma_f16(tmem_base + C::kOCol, desc_k_major(aP + pbox, poff), desc_mn_major(aV, TILE * 128, k * 16), idesc_o,
-                   (j | k) != 0);
-        }
+        for (int k = 1; k < TILE / 16; ++k)
+          umma_f16_c<true>(tmem_base + C::kOCol, desc_at(p_km, k_major_step(k, TILE * 128)), desc_at(v_mn, mn_major_step(k)), idesc_o);
         tc_commit(pv_done);
         tc_commit(&kv_empty[j & 1]);
       }
       __syncwarp();
+    }
+  } else if (REPL) {
+    // ---- at most 32 query rows, copied into every quarter: warp q handles key columns [32 q, 32 q + 32)
+    const int quarter = warp & 3;
+    const bool real = lane < rows;
+    const int h = real ? lane / p.q_len : 0, qi = real ? lane % p.q_len : 0;
+    const int k_max = real ? ctx - p.q_len + qi : -1;   // last visible key
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float sl = p.scale * kLog2e;
+    float m_run = -INFINITY, l_run = 0.0f;              // l_run: this warp's 32 columns of every tile only
+    bool ok = true;
+    // publishes `mine`, waits (bounded) for the other three warps, returns all four values of this row
+    auto exchange = [&](uint32_t phase, float mine, float (&all)[4]) -> bool {
+      float* slot = sExchange + (phase & 1) * 128;
+      slot[quarter * 32 + lane] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xbar);
+      if (!mbar_wait(xbar, phase & 1, abort_flag, p.status, kPagedKernelId, 9)) return false;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) all[q] = slot[q * 32 + lane];
+      return true;
+    };
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kPagedKernelId, 6)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int k0 = j * TILE + quarter * 32;
+      uint32_t sv[32];
+      tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * TILE + quarter * 32), sv);
+      tc_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[s]);
+      float m_loc = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float x = __uint_as_float(sv[i]);
+        if (k0 + i > k_max) x = -INFINITY;
+        sv[i] = __float_as_uint(x);
+        m_loc = fmaxf(m_loc, x);
+      }
+      float part[4];
+      if (!exchange((uint32_t)j, m_loc, part)) { ok = false; break; }
+      const float m_tile = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+      // lazy reference maximum (see flash_fwd.cu); every warp sees the same m_tile and decides alike
+      const bool moved = (m_tile - m_run) * sl > 8.0f;
+      const float m_new = moved ? m_tile : m_run;
+      const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = moved ? exp2f((m_run - m_safe) * sl) : 1.0f;
+      const float neg = -m_safe * sl;
+      float l_tile = 0.0f;
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sl, neg));
+        const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl, neg));
+        l_tile += p0 + p1;
+        pk[i / 2] = pack_bf16x2(p0, p1);
+      }
+      l_run = l_run * alpha + l_tile;
+      m_run = m_new;
+      if (j > 0 && !mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kPagedKernelId, 7)) { ok = false; break; }
+      tc_fence_after_sync();
+      // P row `lane`, key columns of this warp: rows 32..127 of the operand tile are never read back
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)
+        store_chunk(sP, lane, quarter * 4 + ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
+      if (quarter == 0 && j > 0 && __any_sync(0xffffffffu, moved)) {
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
+        }
+        tc_wait_st();
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ok && n_tiles > 0) ok = exchange((uint32_t)n_tiles, l_run, sums);
+    if (ok && quarter == 0 && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
+      tc_fence_after_sync();
+      const float l_all = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      const float inv_l = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+      __nv_bfloat16* dst = p.out + ((size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t ov[32];
+        tmem_ld_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
+        tc_wait_ld();
+        if (real) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(ov[8 * i]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
+            q.y = pack_bf16x2(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
+            q.z = pack_bf16x2(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
+            q.w = pack_bf16x2(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
+            reinterpret_cast<uint4*>(dst + c * 32)[i] = q;
+          }
+        }
+      }
     }
   } else {
     const int quarter = warp & 3;
@@ -315,14 +437,18 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, const
   if (rc) return rc;
   static bool configured = false;
   if (!configured) {
-    AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     configured = true;
   }
   Params p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_tables = (const int*)block_tables;
   p.context_lens = (const int*)context_lens; p.q_start = (const int*)q_start; p.max_blocks = max_blocks;
   p.heads = heads; p.kv_heads = kv_heads; p.q_len = q_len; p.scale = scale; p.status = device_status_buffer();
-  paged_attention_kernel<HD><<<dim3(num_seqs, kv_heads), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
+  if ((heads / kv_heads) * q_len <= 32)
+    paged_attention_kernel<HD, true><<<dim3(num_seqs, kv_heads), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
+  else
+    paged_attention_kernel<HD, false><<<dim3(num_seqs, kv_heads), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }

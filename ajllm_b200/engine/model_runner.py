@@ -6,10 +6,17 @@ are written to the sequence's cache slots and each new token attends to everythi
 sequence up to and including itself. Under tensor parallelism activations are replicated, every rank
 holds its own heads of the cache, and the two row-parallel projections end in an all-reduce.
 Weights may be bf16 tensors or block-scaled fp8 (:mod:`ajllm_b200.engine.quant`).
+
+Pure decoding steps (one new token per sequence) on one GPU are replayed from CUDA graphs: a step is a few
+hundred short kernels, and launching them one by one costs more host time than they run. One graph per
+batch-size bucket is captured on first use over static input buffers (token ids, positions, cache slots,
+block tables, context lengths); a step copies its inputs into those buffers and replays. Rows that pad a
+batch up to its bucket read and write a scratch cache block that no sequence owns.
 """
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -34,8 +41,25 @@ def _matmul(x: torch.Tensor, weight) -> torch.Tensor:
     return ops.linear(x, weight)
 
 
+class _DecodeGraph:
+    """Static buffers and the captured graph of one batch-size bucket."""
+
+    def __init__(self, bucket: int, max_blocks: int, device: torch.device) -> None:
+        self.bucket = bucket
+        self.ids = torch.zeros(bucket, dtype=torch.long, device=device)
+        self.pos = torch.zeros(bucket, dtype=torch.long, device=device)
+        self.pos32 = torch.zeros(bucket, dtype=torch.int32, device=device)
+        self.slots = torch.zeros(bucket, dtype=torch.long, device=device)
+        self.tables = torch.zeros(bucket, max_blocks, dtype=torch.int32, device=device)
+        self.ctx = torch.ones(bucket, dtype=torch.int32, device=device)
+        self.starts = torch.arange(bucket, dtype=torch.int32, device=device)
+        self.logits: torch.Tensor | None = None
+        self.graph: torch.cuda.CUDAGraph | None = None
+
+
 class ModelRunner:
     FUSED_ALL_REDUCE_MAX_ROWS = 2048     # beyond this the partial tiles (tp copies per rank) outgrow the win
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 
     def __init__(self, model, cache: PagedKVCache, quantization: str | None = None) -> None:
         self.model = model
@@ -62,6 +86,105 @@ class ModelRunner:
             elif quantization not in (None, "none", "bf16"):
                 raise ValueError(f"unknown quantization '{quantization}'")
             self.weights.append(entry)
+        # decoding graphs: one GPU, dense feed-forward blocks (expert routing has data-dependent shapes)
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self._scratch_block: int | None = None
+        self.use_graphs = (self.device.type == "cuda" and self.dtype == torch.bfloat16
+                           and (self.tp is None or self.tp.size == 1)
+                           and not any("moe" in w for w in self.weights)
+                           and os.environ.get("AJB_DECODE_GRAPHS", "1") != "0")
+
+    # ------------------------------------------------------------------ graph-replayed decoding
+    def _decode_static(self, g: _DecodeGraph) -> torch.Tensor:
+        """One decoding step over the static buffers of ``g`` (every row: one new token, everything else cached)."""
+        from ajllm_b200.ops import serving
+        model, cache = self.model, self.cache
+        n = g.bucket
+        plan = object.__new__(serving.PagedPlan)
+        plan.total_rows = n
+        plan.launches = [(1, n, g.tables, g.starts, g.ctx)]
+        stream = model.token_embeddings(g.ids)
+        if model.position_embeddings is not None:
+            stream = stream + model.position_embeddings(g.pos)
+        pending = None
+        for index, (layer, w) in enumerate(zip(model.layers, self.weights)):
+            attn = layer.attention
+            stream, normed = layer.norm1.add_and_norm(stream, pending)
+            qkv = _matmul(normed, w["qkv"])
+            if attn.use_rope:
+                serving.rope_packed_(qkv, attn.rope_cos, attn.rope_sin, g.pos32, attn.num_heads, attn.num_kv_heads, attn.head_dim)
+            q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
+            cache.write(index, g.slots, k, v)
+            attended = serving.paged_attention_planned(q.contiguous(), cache.keys[index], cache.values[index], plan)
+            attended = _matmul(attended.reshape(n, -1), w["out"])
+            stream, normed = layer.norm2.add_and_norm(stream, attended)
+            if "w13" in w:
+                pending = _matmul(ops.swiglu_interleaved(_matmul(normed, w["w13"])), w["w2"])
+            else:
+                pending = _matmul(ops.silu(_matmul(normed, w["w1"])), w["w2"])
+        hidden = model.final_norm.add_and_norm(stream, pending)[1]
+        return ops.linear(hidden, model.head_weight).float()
+
+    def _graph_for(self, bucket: int) -> _DecodeGraph:
+        g = self._graphs.get(bucket)
+        if g is not None:
+            return g
+        cache = self.cache
+        if self._scratch_block is None:
+            self._scratch_block = cache.allocator.allocate()       # padding rows read and write this block only
+        max_blocks = (self.model.context_length + cache.block_size - 1) // cache.block_size
+        g = _DecodeGraph(bucket, max_blocks, self.device)
+        g.tables.fill_(self._scratch_block)
+        g.slots.fill_(self._scratch_block * cache.block_size)
+        # one eager run on a side stream first (lazy kernel attributes, allocator warm-up), then the capture
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._decode_static(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        g.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g.graph):
+            g.logits = self._decode_static(g)
+        self._graphs[bucket] = g
+        return g
+
+    def _forward_decode_graph(self, items: list[RunItem]) -> torch.Tensor | None:
+        """Replay path for a pure decoding step; ``None`` when the step does not qualify."""
+        n = len(items)
+        if n == 0 or n > self.GRAPH_BUCKETS[-1]:
+            return None
+        cache, model = self.cache, self.model
+        for item in items:
+            if len(item.token_ids) != 1 or item.num_logits != 1 or cache.length(item.seq_id) == 0:
+                return None
+            if cache.length(item.seq_id) + 1 > model.context_length:
+                raise ValueError(f"sequence {item.seq_id} would exceed the context length {model.context_length}")
+        bucket = next(b for b in self.GRAPH_BUCKETS if b >= n)
+        g = self._graph_for(bucket)
+        tokens, positions, slots, ctx = [], [], [], []
+        for item in items:
+            start = cache.length(item.seq_id)
+            slots.extend(cache.append_slots(item.seq_id, 1))
+            tokens.append(item.token_ids[0])
+            positions.append(start)
+            ctx.append(start + 1)
+        pad = bucket - n
+        scratch_slot = self._scratch_block * cache.block_size
+        host = torch.tensor([tokens + [0] * pad, positions + [0] * pad, slots + [scratch_slot] * pad, ctx + [1] * pad],
+                            dtype=torch.long).pin_memory()
+        staged = host.to(self.device, non_blocking=True)
+        g.ids.copy_(staged[0])
+        g.pos.copy_(staged[1])
+        g.pos32.copy_(staged[1])
+        g.slots.copy_(staged[2])
+        g.ctx.copy_(staged[3])
+        tables = cache.block_table_tensor([item.seq_id for item in items], self.device)
+        g.tables[:n, :tables.shape[1]].copy_(tables)
+        if pad:
+            g.tables[n:, 0].fill_(self._scratch_block)
+        g.graph.replay()
+        return g.logits[:n]
 
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp is not None and self.tp.size > 1:
@@ -82,6 +205,10 @@ class ModelRunner:
     @torch.no_grad()
     def forward(self, items: list[RunItem]) -> torch.Tensor:
         """Returns logits ``[sum_i num_logits_i, vocab]`` in item order."""
+        if self.use_graphs:
+            logits = self._forward_decode_graph(items)
+            if logits is not None:
+                return logits
         model, cache = self.model, self.cache
         tokens, positions, slots, q_lens, ctx_lens, seq_ids, logit_rows = [], [], [], [], [], [], []
         cursor = 0

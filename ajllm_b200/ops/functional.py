@@ -157,6 +157,8 @@ def linear_skinny(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     every SM streaming weights; fp32 partial products are summed by a second small kernel."""
     m, k = x2.shape
     n = weight.shape[0]
+    if m <= 128:
+        return _linear_decode(x2, weight)
     tiles = ((m + 127) // 128) * ((n + 255) // 256)
     k_blocks = (k + 63) // 64
     want = max(1, min(k_blocks // 4, (148 + tiles - 1) // tiles))
@@ -172,6 +174,30 @@ def linear_skinny(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
             workspace = torch.empty(need, dtype=torch.float32, device=x2.device)
             _SPLITK_WORKSPACE[key] = workspace
     native.call("ajb_gemm_bf16_splitk", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), native.ptr(workspace), m, n, k,
+                x2.stride(0), weight.stride(0), split, native.stream_ptr())
+    return out
+
+
+def _linear_decode(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x2 @ weight.T`` for at most 128 rows as ``(weight @ x2.T).T``: weight rows fill the 128-row side of the
+    tensor-core tile, ``n / 128`` tiles times a few K slices stream the weights, partial products are tiny."""
+    m, k = x2.shape
+    n = weight.shape[0]
+    tiles = (n + 127) // 128
+    k_blocks = (k + 63) // 64
+    want = max(1, min(k_blocks // 4, (2 * 148 + tiles - 1) // tiles))      # about two CTAs' worth of work per SM
+    per = (k_blocks + want - 1) // want
+    split = (k_blocks + per - 1) // per
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=x2.device)
+    workspace = None
+    if split > 1:
+        key = (x2.device.index, )
+        need = split * m * n
+        workspace = _SPLITK_WORKSPACE.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.float32, device=x2.device)
+            _SPLITK_WORKSPACE[key] = workspace
+    native.call("ajb_gemm_bf16_decode", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), native.ptr(workspace), m, n, k,
                 x2.stride(0), weight.stride(0), split, native.stream_ptr())
     return out
 

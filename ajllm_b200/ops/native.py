@@ -31,6 +31,7 @@ _SIGNATURES: dict[str, list] = {
     "ajb_gemm_bf16_batched": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_long, c_long,
                               c_long, c_int, c_int, c_int, c_void, c_int, c_void],
     "ajb_gemm_bf16_splitk": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_int, c_void],
+    "ajb_gemm_bf16_decode": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_int, c_void],
     "ajb_rmsnorm_fwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float, c_void],
     "ajb_rmsnorm_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_void],
     "ajb_colsum_f32": [c_void, c_void, c_int, c_int, c_int, c_void],
@@ -117,7 +118,7 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 
 # kernels launched per entry point (everything else launches one)
-_LAUNCHES_PER_CALL = {"ajb_flash_bwd": 3, "ajb_sumsq_f32": 2}
+_LAUNCHES_PER_CALL = {"ajb_flash_bwd": 3, "ajb_sumsq_f32": 2, "ajb_gemm_bf16_decode": 2}
 launch_count = 0
 
 
