@@ -26,7 +26,7 @@ constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;
 
-enum Epilogue : int { kStoreBf16 = 0, kAccumF32 = 1, kStoreF32 = 2 };
+enum Epilogue : int { kStoreBf16 = 0, kAccumF32 = 1, kStoreF32 = 2, kAtomicAddF32 = 3 };
 
 template <int BN>
 struct Config {
@@ -294,7 +294,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         } else {
           float* dst = reinterpret_cast<float*>(p.c) + b * (p.split_k > 1 ? p.split_stride : p.c_batch_stride) + (long long)row * p.ldc + col;
           const bool accumulate = p.epilogue == kAccumF32;
-          if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          if (p.epilogue == kAtomicAddF32) {
+            // several K slices add into the same tile: 16-byte reductions, order not fixed
+            if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                red_add_f32x4(dst + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                              __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < valid) atomicAdd(dst + j, __uint_as_float(v[j]));
+            }
+          } else if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float4 q = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
@@ -434,8 +446,26 @@ extern "C" int ajb_gemm_bf16(const void* a, const void* b, void* c, int m, int n
                              long long ldc, int a_mn_major, int b_mn_major, int epilogue, void* stream) {
   using namespace ajb;
   AJB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm: empty problem %dx%dx%d", m, n, k);
-  AJB_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm: unknown epilogue %d", epilogue);
-  return gemm::dispatch<false>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, gemm::BatchSpec(),
+  AJB_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm: unknown epilogue %d", epilogue);
+  gemm::BatchSpec spec;
+  if (epilogue == gemm::kAtomicAddF32) {
+    // Accumulating products with a long K (weight gradients: K = tokens) often have a tile count that fills the
+    // SMs badly, e.g. 352 tiles on 148 SMs run as three rounds, the last one 40 % full. Cutting K into slices that
+    // add into the same tile with reductions evens that out; with one slice this is the plain accumulate epilogue.
+    const int tiles = ((m + gemm::BM - 1) / gemm::BM) * ((n + 255) / 256);
+    const int sms = sm_count();
+    const int k_blocks = (k + gemm::BK - 1) / gemm::BK;
+    int best = 1;
+    double best_eff = (double)tiles / (((tiles + sms - 1) / sms) * (double)sms);
+    for (int split = 2; split <= 4 && k_blocks / split >= 32; ++split) {
+      const int units = tiles * split;
+      const double eff = (double)units / (((units + sms - 1) / sms) * (double)sms);
+      if (eff > best_eff + 0.04) { best = split; best_eff = eff; }
+    }
+    if (best == 1) epilogue = gemm::kAccumF32;
+    else { spec.split_k = best; spec.split_stride = 0; }
+  }
+  return gemm::dispatch<false>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, spec,
                                reinterpret_cast<cudaStream_t>(stream));
 }
 

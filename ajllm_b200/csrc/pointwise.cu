@@ -27,6 +27,11 @@ __device__ __forceinline__ Bf16x8 pack8(const float (&in)[8]) {
   return out;
 }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -219,20 +224,24 @@ __global__ void rope_qk_kernel(__nv_bfloat16* __restrict__ qkv, const float* __r
 }
 
 // ------------------------------------------------------------------------------------------ SwiGLU
+// One thread per 16-byte vector of the interleaved (gate, up) columns: neighbouring threads touch neighbouring
+// 16 bytes of the wide tensor and neighbouring 8 bytes of the narrow one, so every sector that moves is used whole.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ act,
-                                  long long total_vec /* rows * F / 8 */) {
+                                  long long total_vec /* rows * F / 4: vectors of four (gate, up) pairs */) {
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vec;
        idx += (long long)gridDim.x * blockDim.x) {
-    float a[8], b[8], o[8];
-    unpack8(reinterpret_cast<const Bf16x8*>(gate_up)[2 * idx], a);
-    unpack8(reinterpret_cast<const Bf16x8*>(gate_up)[2 * idx + 1], b);
+    float a[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(gate_up)[idx], a);
+    float o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float g0 = a[2 * i], u0 = a[2 * i + 1], g1 = b[2 * i], u1 = b[2 * i + 1];
-      o[i] = g0 / (1.0f + __expf(-g0)) * u0;
-      o[4 + i] = g1 / (1.0f + __expf(-g1)) * u1;
+      const float g = a[2 * i], u = a[2 * i + 1];
+      o[i] = g / (1.0f + __expf(-g)) * u;
     }
-    reinterpret_cast<Bf16x8*>(act)[idx] = pack8(o);
+    uint2 packed;
+    packed.x = pack2(o[0], o[1]);
+    packed.y = pack2(o[2], o[3]);
+    reinterpret_cast<uint2*>(act)[idx] = packed;
   }
 }
 
@@ -240,25 +249,19 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate_up, con
                                   __nv_bfloat16* __restrict__ dgate_up, long long total_vec) {
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vec;
        idx += (long long)gridDim.x * blockDim.x) {
-    float a[8], b[8], d[8], oa[8], ob[8];
-    unpack8(reinterpret_cast<const Bf16x8*>(gate_up)[2 * idx], a);
-    unpack8(reinterpret_cast<const Bf16x8*>(gate_up)[2 * idx + 1], b);
-    unpack8(reinterpret_cast<const Bf16x8*>(dact)[idx], d);
+    float a[8], oa[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(gate_up)[idx], a);
+    const uint2 dv = reinterpret_cast<const uint2*>(dact)[idx];
+    const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dv.x));
+    const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dv.y));
+    const float d[4] = {d01.x, d01.y, d23.x, d23.y};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      {
-        const float g = a[2 * i], u = a[2 * i + 1], sig = 1.0f / (1.0f + __expf(-g));
-        oa[2 * i] = d[i] * u * sig * (1.0f + g * (1.0f - sig));
-        oa[2 * i + 1] = d[i] * g * sig;
-      }
-      {
-        const float g = b[2 * i], u = b[2 * i + 1], sig = 1.0f / (1.0f + __expf(-g));
-        ob[2 * i] = d[4 + i] * u * sig * (1.0f + g * (1.0f - sig));
-        ob[2 * i + 1] = d[4 + i] * g * sig;
-      }
+      const float g = a[2 * i], u = a[2 * i + 1], sig = 1.0f / (1.0f + __expf(-g));
+      oa[2 * i] = d[i] * u * sig * (1.0f + g * (1.0f - sig));
+      oa[2 * i + 1] = d[i] * g * sig;
     }
-    reinterpret_cast<Bf16x8*>(dgate_up)[2 * idx] = pack8(oa);
-    reinterpret_cast<Bf16x8*>(dgate_up)[2 * idx + 1] = pack8(ob);
+    reinterpret_cast<Bf16x8*>(dgate_up)[idx] = pack8(oa);
   }
 }
 
@@ -513,7 +516,7 @@ extern "C" int ajb_rope_qk(void* qkv, const void* cos_t, const void* sin_t, cons
 
 extern "C" int ajb_swiglu_fwd(const void* gate_up, void* act, long long rows, int ff, void* stream) {
   AJB_REQUIRE(ff % 8 == 0, "swiglu: width %d must be a multiple of 8", ff);
-  const long long total = rows * (ff / 8);
+  const long long total = rows * (ff / 4);
   if (total <= 0) return 0;
   swiglu_fwd_kernel<<<grid_for(total, 256), 256, 0, STREAM(stream)>>>((const bf16*)gate_up, (bf16*)act, total);
   AJB_CUDA_OK(cudaGetLastError());
@@ -523,7 +526,7 @@ extern "C" int ajb_swiglu_fwd(const void* gate_up, void* act, long long rows, in
 extern "C" int ajb_swiglu_bwd(const void* gate_up, const void* dact, void* dgate_up, long long rows, int ff,
                               void* stream) {
   AJB_REQUIRE(ff % 8 == 0, "swiglu: width %d must be a multiple of 8", ff);
-  const long long total = rows * (ff / 8);
+  const long long total = rows * (ff / 4);
   if (total <= 0) return 0;
   swiglu_bwd_kernel<<<grid_for(total, 256), 256, 0, STREAM(stream)>>>((const bf16*)gate_up, (const bf16*)dact,
                                                                        (bf16*)dgate_up, total);

@@ -19,10 +19,18 @@ from ajllm_b200.ops import native, reference
 EPI_STORE_BF16 = 0
 EPI_ACCUM_F32 = 1
 EPI_STORE_F32 = 2
+EPI_ADD_F32 = 3         # accumulate; long-K products may be cut into K slices that add with reductions (order not fixed)
+
+
+def wgrad_epilogue() -> int:
+    """Epilogue of a weight-gradient GEMM that accumulates into ``main_grad``."""
+    return EPI_ACCUM_F32 if DETERMINISTIC_WGRAD else EPI_ADD_F32
 
 # Attention backward: False selects the fused single-pass kernel (dQ summed with fp32 reductions, last
 # bits may differ between runs); True (or AJB_DETERMINISTIC_ATTENTION=1) the bit-reproducible two-kernel path.
-DETERMINISTIC_ATTENTION_BACKWARD = os.environ.get("AJB_DETERMINISTIC_ATTENTION", "0") == "1"
+DETERMINISTIC_ATTENTION_BACKWARD = os.environ.get("AJB_DETERMINISTIC_ATTENTION", os.environ.get("AJB_DETERMINISTIC", "0")) == "1"
+# Weight gradients accumulated into ``main_grad``: with AJB_DETERMINISTIC=1 every output tile is owned by one CTA.
+DETERMINISTIC_WGRAD = os.environ.get("AJB_DETERMINISTIC", "0") == "1"
 
 
 def _is_cuda(t: torch.Tensor) -> bool:
@@ -140,7 +148,7 @@ class _LinearFn(torch.autograd.Function):
             main = getattr(weight, "main_grad", None)
             if main is not None:
                 # fp32 accumulation straight into the optimizer's gradient buffer
-                gemm(g2, x2, main, n, k, m, a_mn_major=True, b_mn_major=True, epilogue=EPI_ACCUM_F32)
+                gemm(g2, x2, main, n, k, m, a_mn_major=True, b_mn_major=True, epilogue=wgrad_epilogue())
                 weight.main_grad_written = True
             else:
                 grad_w = torch.empty(n, k, dtype=torch.bfloat16, device=g2.device)

@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from ajllm_b200.ops import native
-from ajllm_b200.ops.functional import EPI_ACCUM_F32, gemm
+from ajllm_b200.ops.functional import gemm, wgrad_epilogue
 
 _MAX_RANKS = 8
 MODE_ALL_GATHER, MODE_REDUCE_SCATTER, MODE_ALL_REDUCE, MODE_GATHER_WEIGHT = 0, 1, 2, 3
@@ -195,7 +195,7 @@ def _wgrad(grad_out: torch.Tensor, activations: torch.Tensor, weight: torch.Tens
     main = getattr(weight, "main_grad", None)
     if main is not None:
         gemm(grad_out, activations, main, n, k, grad_out.shape[0], a_mn_major=True, b_mn_major=True,
-             epilogue=EPI_ACCUM_F32)
+             epilogue=wgrad_epilogue())
         weight.main_grad_written = True
         return None
     out = torch.empty(n, k, dtype=torch.bfloat16, device=grad_out.device)

@@ -61,6 +61,19 @@ def test_gemm_wgrad_layout_accumulates_fp32(m, n, k):
     assert _rel_err(out, a.float().t() @ b.float()) < 5e-3
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 5632, 8192), (4096, 2048, 4096), (264, 520, 1000)])
+def test_gemm_accumulate_with_k_slices(m, n, k):
+    """Epilogue 3: C += A^T B where a long K may be cut into slices that add with reductions (352 or 256 tiles on
+    148 SMs trigger the cut for the first two shapes; the third stays a single slice)."""
+    torch.manual_seed(3)
+    a = torch.randn(k, m, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(k, n, device=_dev(), dtype=torch.bfloat16)
+    acc = torch.randn(m, n, device=_dev(), dtype=torch.float32)
+    want = acc + a.float().t() @ b.float()
+    ops.gemm(a, b, acc, m, n, k, a_mn_major=True, b_mn_major=True, epilogue=3)
+    assert _rel_err(acc, want) < 2e-3
+
+
 def test_gemm_strided_operands():
     """Column slices of wider buffers are passed by leading dimension, not copied."""
     torch.manual_seed(3)
