@@ -103,3 +103,28 @@ def test_cli_accepts_every_verb_and_launcher_builds_torchrun():
     command = build_command(parse(["--config", "c.yaml", "--nproc-per-node", "4"]))
     assert "torch.distributed.run" in command and command[-5:] == ["ajllm_b200", "lm", "train", "--config", "c.yaml"]
     assert command[command.index("--master-addr") + 1] == "127.0.0.1"
+
+
+def test_acceleration_benchmark_writes_json_csv_and_figure(tmp_path):
+    """The acceleration benchmark (reference: ajllm/workflows/benchmark_distributed.py) on CPU: every configuration
+    and phase appears in the JSON / CSV, the sharded configurations run on two gloo ranks."""
+    import csv
+    import json
+
+    from ajllm_b200.workflows import benchmark_distributed as bench
+    from tests.conftest import free_port
+
+    out = bench.main(["--device", "cpu", "--world-size", "2", "--vocab-size", "64", "--d-model", "32", "--num-layers", "2",
+                      "--num-heads", "4", "--batch-size", "4", "--context-length", "16", "--steps", "2", "--warmup", "1",
+                      "--master-port", str(free_port()), "--output-dir", str(tmp_path)])
+    payload = json.loads((tmp_path / "benchmark_acceleration.json").read_text())
+    assert {r["config"] for r in payload} == set(bench.CONFIGS)
+    assert sum(1 for r in payload if r["config"] == "fsdp_ac") == 2           # one record per rank
+    for record in payload:
+        for phase in bench.PHASES:
+            assert record[phase]["mean_ms"] >= 0.0
+        assert record["tokens_per_second"] > 0
+    rows = list(csv.DictReader((tmp_path / "benchmark_acceleration.csv").open()))
+    assert len(rows) == len(payload) * len(bench.PHASES)
+    assert (tmp_path / "benchmark_acceleration.png").exists() or (tmp_path / "benchmark_time.svg").exists()
+    assert out["json"].endswith("benchmark_acceleration.json")
