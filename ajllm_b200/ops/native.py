@@ -109,6 +109,25 @@ def bind(name: str, argtypes: list, restype=c_int):
     return fn
 
 
+class PeerTimeout(RuntimeError):
+    """A kernel gave up a bounded wait (on a peer GPU's flag or on one of its own barriers) and returned early."""
+
+    def __init__(self, code: int) -> None:
+        self.code, self.kernel_id, self.stage = code, (code & 0xFF) - 1, code >> 8
+        names = {0: "gemm", 1: "flash forward", 2: "flash backward (dK/dV)", 3: "flash backward (dQ)", 4: "tensor-parallel gemm",
+                 5: "paged attention", 6: "fp8 gemm", 7: "expert exchange", 8: "flash backward (fused)", 9: "gradient reduce-scatter"}
+        super().__init__(f"kernel '{names.get(self.kernel_id, self.kernel_id)}' stopped waiting at stage {self.stage} "
+                         f"(status word {code:#x}); its outputs are incomplete")
+
+
+def check_status(raise_on_timeout: bool = True) -> int:
+    """Synchronise the device and read (and clear) the kernels' status words: 0 when every bounded wait completed."""
+    code = int(lib().ajb_check_status())
+    if code > 0 and raise_on_timeout:
+        raise PeerTimeout(code)
+    return code
+
+
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 

@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from ajllm_b200.ops import native
 from ajllm_b200.ops.functional import gemm, wgrad_epilogue
+from ajllm_b200.utils.timing import nvtx_range
 
 _MAX_RANKS = 8
 MODE_ALL_GATHER, MODE_REDUCE_SCATTER, MODE_ALL_REDUCE, MODE_GATHER_WEIGHT = 0, 1, 2, 3
@@ -41,6 +42,7 @@ class _CommArgs(ctypes.Structure):
 
 class FusedTensorParallel:
     BLOCK_M, BLOCK_N = 128, 256
+    GUARD_BYTES, GUARD_PATTERN = 4096, 0xA5
 
     def __init__(self, group, device: torch.device, copy_ctas: int | None = None) -> None:
         import torch.distributed._symmetric_memory as symm_mem
@@ -72,17 +74,28 @@ class FusedTensorParallel:
     # ------------------------------------------------------------------ symmetric buffers (grown on demand)
     def _ensure(self, which: str, nbytes: int):
         current = getattr(self, f"_{which}")
-        if current is not None and current.numel() >= nbytes:
+        if current is not None and current.numel() - self.GUARD_BYTES >= nbytes:
             return
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
         size = max(nbytes, 1 << 20)
-        buf = self._symm.empty(size, dtype=torch.uint8, device=self.device)
+        # a guard page behind the payload: peers write into this buffer with raw pointers, and a pattern that
+        # survives (`guards_intact`) shows that none of them ran past the end
+        buf = self._symm.empty(size + self.GUARD_BYTES, dtype=torch.uint8, device=self.device)
+        buf[size:].fill_(self.GUARD_PATTERN)
         ptrs = list(self._symm.rendezvous(buf, self.group).buffer_ptrs)
         setattr(self, f"_{which}", buf)
         setattr(self, f"_{which}_ptrs", ptrs)
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
+
+    def guards_intact(self) -> bool:
+        """True when the guard bytes behind every symmetric buffer still hold their pattern."""
+        for which in ("stage", "recv"):
+            buf = getattr(self, f"_{which}")
+            if buf is not None and not bool((buf[-self.GUARD_BYTES:] == self.GUARD_PATTERN).all()):
+                return False
+        return True
 
     def supports(self, rows_total: int) -> bool:
         return rows_total % self.size == 0 and (rows_total // self.size) % self.BLOCK_M == 0
@@ -114,7 +127,8 @@ class FusedTensorParallel:
         args.expected_count = self.expected_count & 0xFFFFFFFF
         args.epoch = self.epoch & 0xFFFFFFFF
         native.launch_count += 1
-        status = self._fn(ctypes.byref(args), native.stream_ptr())
+        with nvtx_range(("ag_gemm", "gemm_rs", "gemm_ar", "gw_gemm")[mode]):
+            status = self._fn(ctypes.byref(args), native.stream_ptr())
         if status != 0:
             raise RuntimeError(f"ajb_comm_gemm failed: {native.lib().ajb_last_error().decode()}")
 

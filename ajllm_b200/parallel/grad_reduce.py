@@ -17,6 +17,7 @@ import torch
 import torch.distributed as dist
 
 from ajllm_b200.ops import native
+from ajllm_b200.utils.timing import nvtx_range
 
 _MAX_RANKS = 8
 
@@ -83,6 +84,7 @@ class FusedGradReduce:
         args.epoch = self.epoch & 0xFFFFFFFF
         args.local_counter = self._counter.data_ptr()
         native.launch_count += 1
-        status = self._fn(ctypes.byref(args), native.stream_ptr())
+        with nvtx_range("grad_reduce_scatter"):
+            status = self._fn(ctypes.byref(args), native.stream_ptr())
         if status != 0:
             raise RuntimeError(f"ajb_grad_reduce_scatter failed: {native.lib().ajb_last_error().decode()}")

@@ -17,6 +17,7 @@ import torch
 import torch.distributed as dist
 
 from ajllm_b200.ops import native
+from ajllm_b200.utils.timing import nvtx_range
 
 
 class _Args(ctypes.Structure):
@@ -97,7 +98,9 @@ class FusedExpertExchange:
         buf, ptrs = self.buffer(name, total, dim)
         args = self._args(slots, dim, local_experts, stride, ptrs, counts)
         native.launch_count += 1
-        if self._push(ctypes.byref(args), rows.data_ptr(), native.ptr(scale), native.stream_ptr()) != 0:
+        with nvtx_range("moe_dispatch"):
+            status = self._push(ctypes.byref(args), rows.data_ptr(), native.ptr(scale), native.stream_ptr())
+        if status != 0:
             raise RuntimeError(f"ajb_moe_push_rows failed: {native.lib().ajb_last_error().decode()}")
         received = buf.clone().view(local_experts, self.size * stride, dim)
         buf.zero_()
@@ -118,8 +121,10 @@ class FusedExpertExchange:
         out = torch.empty(slots.shape[0], dim, dtype=torch.bfloat16, device=self.device) if want_rows else None
         dots = torch.zeros(slots.shape, dtype=torch.float32, device=self.device) if upstream is not None else None
         native.launch_count += 1
-        if self._pull(ctypes.byref(args), native.ptr(out), native.ptr(weights), native.ptr(upstream), native.ptr(dots),
-                      native.stream_ptr()) != 0:
+        with nvtx_range("moe_combine"):
+            status = self._pull(ctypes.byref(args), native.ptr(out), native.ptr(weights), native.ptr(upstream), native.ptr(dots),
+                                native.stream_ptr())
+        if status != 0:
             raise RuntimeError(f"ajb_moe_pull_rows failed: {native.lib().ajb_last_error().decode()}")
         return out, dots
 

@@ -7,6 +7,8 @@ events on the launching stream and, across ranks, the maximum is reported.
 
 from __future__ import annotations
 
+import contextlib
+import os
 import shutil
 import statistics
 import subprocess
@@ -21,6 +23,23 @@ _QUERY = (
     "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
     "clocks_event_reasons.sw_power_cap"
 )
+
+
+_NVTX = os.environ.get("AJB_NVTX", "0") == "1"
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """Named range around a fused path (all-gather GEMM, expert dispatch, gradient reduce-scatter, ...) for a
+    timeline profiler; a no-op unless ``AJB_NVTX=1`` and a GPU is present."""
+    if _NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield
 
 
 class DeviceTimer:

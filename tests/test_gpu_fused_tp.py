@@ -66,6 +66,18 @@ def _worker(rank: int, world: int, port: int, rows_local: int, results):
                 errors[f"{tag}/rs/z/{trial}"] = rel(z, want_z[rank * rows_local:(rank + 1) * rows_local])
                 errors[f"{tag}/rs/da/{trial}"] = rel(a.grad, g_row.float() @ w_row[rank].float())
                 errors[f"{tag}/rs/dw/{trial}"] = rel(wr.grad, g_row.float().t() @ (x_full[:, :n_local].float() * (rank + 1)))
+        # the same call twice must give the same bits (a race in the flag / epoch protocol would show here), and
+        # nobody may have written behind the end of a symmetric buffer
+        torch.manual_seed(9)
+        xs = (torch.randn(rows_local, d_model, device=device) * 0.5).to(torch.bfloat16)
+        ws = (torch.randn(n_local, d_model, device=device) * 0.05).to(torch.bfloat16)
+        first = [fused.all_gather_gemm(xs, ws, False, n_local, d_model)[1].clone() for _ in range(2)]
+        errors["repeat/ag"] = 0.0 if torch.equal(first[0], first[1]) else 1.0
+        xa = (torch.randn(rows_local * world, n_local, device=device) * 0.5).to(torch.bfloat16)
+        wr = (torch.randn(d_model, n_local, device=device) * 0.05).to(torch.bfloat16)
+        second = [fused.gemm_reduce_scatter(xa, wr, False, d_model, n_local).clone() for _ in range(2)]
+        errors["repeat/rs"] = 0.0 if torch.equal(second[0], second[1]) else 1.0
+        errors["guards"] = 0.0 if fused.guards_intact() else 1.0
         torch.cuda.synchronize()
         status = native.lib().ajb_check_status()
         results[rank] = {"errors": errors, "status": status}

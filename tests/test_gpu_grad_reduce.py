@@ -77,6 +77,51 @@ def _worker(rank: int, world: int, port: int, results):
         dist.destroy_process_group()
 
 
+def test_peer_that_never_signals_ends_in_a_status_word_not_a_hang():
+    """One GPU plays rank 0 of two; the second rank does not exist, so its "buffer is ready" word is never
+    written. The kernel's wait runs out (2 s budget), it records a status word, skips the reduction and returns;
+    the host turns the word into PeerTimeout, and the same kernel works again once the words are in place."""
+    import ctypes
+
+    from ajllm_b200.ops import native
+    from ajllm_b200.parallel.grad_reduce import _Args
+
+    device = torch.device("cuda")
+    fn = native.lib().ajb_grad_reduce_scatter
+    fn.argtypes = [ctypes.POINTER(_Args), ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    shard = 4096
+    buffers = [torch.randn(2 * shard, device=device) for _ in range(2)]
+    flags = [torch.zeros(32, dtype=torch.int32, device=device) for _ in range(2)]
+    counter = torch.zeros(4, dtype=torch.int32, device=device)
+    dst = torch.zeros(shard, device=device)
+    assert native.check_status() == 0
+
+    def launch(epoch: int) -> None:
+        args = _Args()
+        args.world, args.rank, args.shard_elems = 2, 0, shard
+        for r in range(2):
+            args.full_ptrs[r] = buffers[r].data_ptr()
+            args.ready_ptrs[r] = flags[r].data_ptr()
+            args.done_ptrs[r] = flags[r].data_ptr() + 8 * 4
+        args.dst, args.accumulate, args.scale, args.sumsq_partials, args.ctas = dst.data_ptr(), 0, 1.0, None, 8
+        args.epoch, args.local_counter = epoch, counter.data_ptr()
+        assert fn(ctypes.byref(args), native.stream_ptr()) == 0
+
+    launch(1)                                   # rank 1's words stay 0: every wait on them must give up
+    with pytest.raises(native.PeerTimeout) as caught:
+        native.check_status()
+    assert caught.value.kernel_id == 9
+    assert float(dst.abs().max()) == 0.0        # the reduction was skipped, nothing half-written
+    assert native.check_status() == 0           # reading cleared the word; the context is healthy
+    flags[0][1] = 2                             # what rank 1 would have written: ready[1], done[1]
+    flags[0][8 + 1] = 2
+    launch(2)
+    assert native.check_status() == 0
+    want = buffers[0][:shard] + buffers[1][:shard]
+    assert float((dst - want).abs().max()) < 1e-6
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_gradient_reduce_scatter():
     import torch.multiprocessing as mp
