@@ -206,6 +206,68 @@ class PipelineParallel(nn.Module):
         raise NotImplementedError("a pipeline stage has no whole-model forward; use loss() or gather the stages")
 
 
+class PipelineOptimizer:
+    """One stage's :class:`~ajllm_b200.training.optim.FlatAdamW` behind the optimizer surface the trainer uses, with
+    whole-model state dicts: ``state_dict()`` gathers every stage's moments (and fp32 master weights) under
+    whole-model parameter names in model order, ``load_state_dict()`` keeps this stage's part. A checkpoint written
+    by a pipeline run therefore has the same layout as one written by a single process."""
+
+    def __init__(self, pipe: PipelineParallel, **adamw_kwargs) -> None:
+        from ajllm_b200.training.optim import FlatAdamW
+
+        self.pipe = pipe
+        self.inner = FlatAdamW(pipe.module, classes=pp_optimizer_classes(pipe.group), **adamw_kwargs)
+
+    @property
+    def param_groups(self):
+        return self.inner.param_groups
+
+    @property
+    def step_count(self) -> int:
+        return self.inner.step_count
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.inner.zero_grad(set_to_none)
+
+    def step(self, max_norm: float = 0.0) -> torch.Tensor:
+        return self.inner.step(max_norm)
+
+    def state_dict(self) -> dict:
+        local = self.inner.state_dict()
+        names = [self.pipe.global_name(n) for n in local["param_names"]]
+        mine = {"names": names,
+                "entries": [local["state"][i] for i in range(len(names))] if local["state"] else [],
+                "masters": {self.pipe.global_name(k): v.cpu() for k, v in local.get("master_weights", {}).items()}}
+        for entry in mine["entries"]:
+            entry["first_moment"], entry["second_moment"] = entry["first_moment"].cpu(), entry["second_moment"].cpu()
+        parts: list[dict] = [None] * self.pipe.stages          # type: ignore[list-item]
+        dist.all_gather_object(parts, mine, group=self.pipe.group)
+        merged_names = [n for part in parts for n in part["names"]]
+        merged_entries = [e for part in parts for e in part["entries"]]
+        group = dict(local["param_groups"][0])
+        group["params"] = list(range(len(merged_names)))
+        out = {"state": dict(enumerate(merged_entries)), "param_groups": [group], "param_names": merged_names}
+        masters = {k: v for part in parts for k, v in part["masters"].items()}
+        if masters:
+            out["master_weights"] = masters
+        return out
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        names = state_dict.get("param_names")
+        if names is None:
+            raise ValueError("an optimizer state without parameter names cannot be split over pipeline stages")
+        own = {self.pipe.global_name(k): k for k in self.pipe.module.state_dict().keys()}
+        picked = [(i, own[n]) for i, n in enumerate(names) if n in own]
+        state = state_dict.get("state") or {}
+        local = {"param_groups": [dict(state_dict["param_groups"][0], params=list(range(len(picked))))],
+                 "param_names": [local_name for _, local_name in picked],
+                 "state": {j: state[i] if i in state else state[str(i)] for j, (i, _) in enumerate(picked)} if state else {}}
+        masters = state_dict.get("master_weights")
+        if masters is not None:
+            local["master_weights"] = {own[n]: v for n, v in masters.items() if n in own}
+        self.inner.load_state_dict(local)
+
+
 def pp_optimizer_classes(group) -> list[dict]:
     """Parameter classes for :class:`ajllm_b200.training.optim.FlatAdamW` on one pipeline stage: nothing to
     reduce (every parameter lives on exactly one stage) but the gradient norm is summed over the stages."""

@@ -125,10 +125,10 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
     dp_rank = mesh.dp_index if mesh is not None else 0
     loss_group = None
     if mesh is not None and sizes["pp"] > 1:
-        from ajllm_b200.parallel import PipelineParallel, pp_optimizer_classes
+        from ajllm_b200.parallel import PipelineOptimizer, PipelineParallel
         micro = int((data.get("parallel", {}) or {}).get("pp_microbatches", sizes["pp"]))
         model = PipelineParallel(model, mesh.pp.group, micro)
-        optimizer = FlatAdamW(model.module, classes=pp_optimizer_classes(mesh.pp.group), **_optimizer_kwargs(data))
+        optimizer = PipelineOptimizer(model, **_optimizer_kwargs(data))
     elif mesh is not None and use_fsdp and dp_size > 1:
         from ajllm_b200.parallel.fsdp import ShardedDataParallel
         model = ShardedDataParallel(model, mesh.dp.group, checkpoint_layers=(checkpointing != "none"),

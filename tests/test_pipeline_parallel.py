@@ -62,3 +62,41 @@ def test_pipeline_training_matches_single_process(world, microbatches):
     tokens = [torch.randint(0, VOCAB, (4, 13)) for _ in range(steps)]
     state0, losses, state1 = _single(tokens, steps)
     run_ranks(_rank, world, state0, tokens, losses, state1, microbatches)
+
+
+def _resume_rank(rank, world, state0, tokens, want_state):
+    """Two steps, a checkpoint of whole-model weights and optimizer state in between, into fresh objects."""
+    from ajllm_b200.models import build_model
+    from ajllm_b200.parallel import ParallelMesh, PipelineOptimizer, PipelineParallel
+
+    mesh = ParallelMesh(tp=1, fsdp=1, pp=world)
+
+    def fresh(weights):
+        torch.manual_seed(0)
+        model = build_model(CONFIG, VOCAB)
+        pipe = PipelineParallel(model, mesh.pp.group, 2)
+        pipe.load_state_dict(weights)
+        return pipe, PipelineOptimizer(pipe, learning_rate=1e-2, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1)
+
+    pipe, opt = fresh(state0)
+    opt.zero_grad()
+    pipe.loss(tokens[0][:, :-1], tokens[0][:, 1:])
+    opt.step(0.5)
+    saved_model, saved_opt = pipe.state_dict(), opt.state_dict()
+    assert list(saved_opt["param_names"]) == list(saved_model.keys())        # single-process layout
+    pipe2, opt2 = fresh(saved_model)
+    opt2.load_state_dict(saved_opt)
+    assert opt2.step_count == 1
+    opt2.zero_grad()
+    pipe2.loss(tokens[1][:, :-1], tokens[1][:, 1:])
+    opt2.step(0.5)
+    merged = pipe2.state_dict()
+    for key, value in want_state.items():
+        assert torch.allclose(merged[key], value, atol=2e-5), (key, float((merged[key] - value).abs().max()))
+
+
+def test_pipeline_checkpoint_round_trip_matches_uninterrupted_training():
+    torch.manual_seed(1)
+    tokens = [torch.randint(0, VOCAB, (4, 13)) for _ in range(2)]
+    state0, _, state1 = _single(tokens, 2)
+    run_ranks(_resume_rank, 2, state0, tokens, state1)
