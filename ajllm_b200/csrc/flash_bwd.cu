@@ -1,6 +1,9 @@
-// FlashAttention backward for sm_100a. Default: one fused tcgen05 kernel (see flash_bwd_fused_kernel)
-// whose dQ tiles are reduced into an fp32 buffer. Alternative, bit-reproducible path: two tcgen05
-// kernels plus a small reduction:
+// FlashAttention backward for sm_100a. Three paths share this entry point:
+//   * head_dim 128 with a dQ accumulation buffer: flash_bwd_hd128.cu (five products per 128 x 64 step, dQ through
+//     TMA reduce-adds);
+//   * other head sizes with a buffer: flash_bwd_fused_kernel below (five products per 128 x 128 step, dQ through
+//     16-byte reductions);
+//   * no buffer: the bit-reproducible path, two tcgen05 kernels plus a small reduction:
 //
 //   delta[b,h,t] = sum_d O[b,t,h,d] * dO[b,t,h,d]
 //   dK/dV kernel : one CTA per (KV tile, KV head, batch); loops over the query heads of the group and

@@ -140,9 +140,11 @@ class TransformerLM(nn.Module):
         """
         hidden = self.hidden_states(token_ids)
         local_targets = self._local_tokens(targets.reshape(-1))
-        share = 1.0
+        # replicated data parallelism sets `data_parallel_share = 1 / dp` so that gradients and losses of the
+        # replicas add up to those of the global batch with plain sums
+        share = float(getattr(self, "data_parallel_share", 1.0))
         if self.tp is not None and self.tp.size > 1:
-            share = 1.0 / self.tp.size
+            share = share / self.tp.size
         loss = ops.linear_cross_entropy(hidden, self.head_weight, local_targets, loss_scale) * share
         aux = self.aux_loss()
         if aux is not None:

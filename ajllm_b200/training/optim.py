@@ -62,6 +62,14 @@ class AdamW(torch.optim.Optimizer):
         return loss
 
 
+def _spec_groups(spec: dict, key: str) -> list:
+    """Process groups of a parameter class: ``key`` (one group) and / or ``key + "s"`` (a list), ``None`` entries dropped."""
+    groups = list(spec.get(key + "s") or [])
+    if spec.get(key) is not None:
+        groups.insert(0, spec[key])
+    return [g for g in groups if g is not None]
+
+
 def _group_sum_(value: torch.Tensor, group) -> torch.Tensor:
     if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(value, op=dist.ReduceOp.SUM, group=group)
@@ -161,7 +169,7 @@ class FlatAdamW:
             if id(p) not in seen:
                 seen.add(id(p))
                 unique.append((name, p))
-        # classes: [{"name", "match": fn(name, param)->bool, "reduce_group", "norm_group"}], first match wins;
+        # classes: [{"name", "match": fn(name, param)->bool, "reduce_group(s)", "norm_group(s)"}], first match wins;
         # the default single class needs no communication
         self.classes = classes or [{"name": "all", "match": lambda n, p: True, "reduce_group": None,
                                     "norm_group": None}]
@@ -218,19 +226,20 @@ class FlatAdamW:
     @torch.no_grad()
     def reduce_grads(self) -> None:
         for spec, (begin, end) in zip(self.classes, self.class_ranges):
-            group = spec.get("reduce_group")
-            if group is not None and end > begin and dist.get_world_size(group) > 1:
-                dist.all_reduce(self.grad[begin:end], op=dist.ReduceOp.SUM, group=group)
+            for group in _spec_groups(spec, "reduce_group"):
+                if end > begin and dist.get_world_size(group) > 1:
+                    dist.all_reduce(self.grad[begin:end], op=dist.ReduceOp.SUM, group=group)
 
     @torch.no_grad()
     def global_sumsq(self) -> torch.Tensor:
-        need_groups = any(spec.get("norm_group") is not None for spec in self.classes)
+        need_groups = any(_spec_groups(spec, "norm_group") for spec in self.classes)
         if not need_groups:
             return flat_sumsq(self.grad, self._sumsq)
         total = self._sumsq.zero_()
         for index, (spec, (begin, end)) in enumerate(zip(self.classes, self.class_ranges)):
             part = flat_sumsq(self.grad[begin:end]) if end > begin else torch.zeros_like(total)
-            _group_sum_(part, spec.get("norm_group"))
+            for group in _spec_groups(spec, "norm_group"):
+                _group_sum_(part, group)
             total += part
         return total
 
