@@ -111,7 +111,11 @@ class Trainer:
             value = value.clone()
             dist.all_reduce(value, op=dist.ReduceOp.SUM, group=tp.group)   # shares add up to the mean
         if self.loss_reduce_group is not None:
-            value = _mean_over_group(value, self.loss_reduce_group)
+            if float(getattr(self.base_model, "data_parallel_share", 1.0)) != 1.0:
+                value = value.clone()           # replicas report local_mean / dp: the shares add up to the mean
+                dist.all_reduce(value, op=dist.ReduceOp.SUM, group=self.loss_reduce_group)
+            else:
+                value = _mean_over_group(value, self.loss_reduce_group)
         return float(value.item())
 
     @torch.no_grad()
