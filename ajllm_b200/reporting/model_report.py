@@ -66,15 +66,18 @@ def _memory_table(r: ResourceEstimate) -> str:
 
 
 def write_model_report(path: str | Path, model: torch.nn.Module, model_config: dict[str, Any], vocab_size: int,
-                       batch_size: int | str = "B", training_config: dict[str, Any] | None = None) -> Path:
+                       batch_size: int | str = "B", training_config: dict[str, Any] | None = None,
+                       state_dict: dict[str, torch.Tensor] | None = None) -> Path:
+    """``state_dict``: the whole model's tensors when ``model`` holds only this rank's part of them (under tensor or
+    expert parallelism gathering them is a collective, so the caller does it on every rank and passes the result)."""
     target = Path(path)
     target.parent.mkdir(parents=True, exist_ok=True)
     T, D = int(model_config["context_length"]), int(model_config["d_model"])
     H, L = int(model_config["num_heads"]), int(model_config["num_layers"])
     Hkv = int(model_config.get("num_kv_heads", H))
     F, hd = int(getattr(model, "d_ff")), D // H
-    named = list(model.state_dict().items())
-    total = sum(p.numel() for p in model.parameters())
+    named = list((state_dict if state_dict is not None else model.state_dict()).items())
+    total = sum(t.numel() for _, t in named) if state_dict is not None else sum(p.numel() for p in model.parameters())
     numeric_batch = int(batch_size) if isinstance(batch_size, int) else int(model_config.get("report_batch_size", 1))
     shown_batch = batch_size if isinstance(batch_size, int) else f"{batch_size} (estimate uses {numeric_batch})"
     flash = next(model.parameters()).is_cuda

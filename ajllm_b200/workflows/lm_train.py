@@ -119,6 +119,14 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
     model = model.to(device=device, dtype=dtype)
     parameter_count = sum(p.numel() for p in model.parameters())
     base_model = model
+    # the report describes the whole model: written before any wrapper shards or splits the parameters, from gathered
+    # tensors (a collective, hence on every rank) when tensor or expert parallelism holds only a part of them here
+    whole_state = base_model.state_dict() if (tp is not None or ep is not None) else None
+    if _is_main():
+        training_for_report = data.get("training", {}) or {}
+        write_model_report(run_directory / "model_report.md", base_model, model_cfg, vocab_size,
+                           int(training_for_report.get("batch_size", 64)), training_for_report, state_dict=whole_state)
+    del whole_state
 
     optimizer = None
     dp_size = mesh.dp_size if mesh is not None else 1
@@ -160,7 +168,6 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
         print(f"  model parameters on this rank: {parameter_count:,}")
         print(f"  FSDP: {'enabled' if use_fsdp else 'disabled'}  mixed precision: {mixed or 'disabled'}")
         print(f"  activation checkpointing: {checkpointing}")
-        write_model_report(run_directory / "model_report.md", base_model, model_cfg, vocab_size, batch_size, training_cfg)
     manifest = {"experiment": experiment, "dataset": dataset_cfg["name"], "tokenizer": tokenizer_cfg["name"],
                 "model": model_cfg["name"], "parameter_count": parameter_count, "device": str(device),
                 "world_size": world, "parallel": sizes}

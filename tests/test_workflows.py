@@ -128,3 +128,43 @@ def test_acceleration_benchmark_writes_json_csv_and_figure(tmp_path):
     assert len(rows) == len(payload) * len(bench.PHASES)
     assert (tmp_path / "benchmark_acceleration.png").exists() or (tmp_path / "benchmark_time.svg").exists()
     assert out["json"].endswith("benchmark_acceleration.json")
+
+
+def _train_rank(rank, world, root, config):
+    from pathlib import Path
+
+    from ajllm_b200.workflows import lm_train as workflow
+
+    out = workflow.run(loaded(Path(root), config))
+    assert out["status"] == "completed" and out["steps"] == 2
+    if rank == 0:
+        run_dir = Path(out["run_directory"])
+        ckpt = torch.load(run_dir / "checkpoints" / "final.pt", weights_only=False)
+        # whole-model, un-prefixed keys whatever the parallel mode
+        assert "token_embeddings.weight" in ckpt["model_state_dict"]
+        assert any(k.startswith("layers.1.") for k in ckpt["model_state_dict"])
+        events = [json.loads(line) for line in (run_dir / "metrics.jsonl").read_text().splitlines()]
+        losses = [e["loss"] for e in events if e["event"] == "train"]
+        assert len(losses) == 2 and all(2.0 < value < 8.0 for value in losses), losses
+
+
+@pytest.mark.parametrize("mode", ["fsdp", "replicas", "pipeline", "tensor"])
+def test_train_workflow_on_two_ranks(project, mode):
+    """`lm train` end to end on two gloo ranks in each multi-rank mode: sharded, replicated, pipelined, tensor-parallel."""
+    from tests.conftest import run_ranks
+
+    config = train_config(project, max_steps=2)
+    config["model"] = {**config["model"], "tie_embeddings": False}
+    config["experiment"] = f"two_ranks_{mode}"
+    if mode == "fsdp":
+        config["acceleration"] = {"use_fsdp": True}
+    elif mode == "replicas":
+        config["acceleration"] = {"use_fsdp": False}
+        config["parallel"] = {"fsdp": 2}
+    elif mode == "pipeline":
+        config["acceleration"] = {"use_fsdp": False}
+        config["parallel"] = {"pp": 2, "fsdp": 1, "pp_microbatches": 2}
+    else:
+        config["acceleration"] = {"use_fsdp": False}
+        config["parallel"] = {"tp": 2, "fsdp": 1}
+    run_ranks(_train_rank, 2, str(project), config)
