@@ -148,9 +148,9 @@ def _train_rank(rank, world, root, config):
         assert len(losses) == 2 and all(2.0 < value < 8.0 for value in losses), losses
 
 
-@pytest.mark.parametrize("mode", ["fsdp", "replicas", "pipeline", "tensor"])
+@pytest.mark.parametrize("mode", ["fsdp", "replicas", "pipeline", "tensor", "experts"])
 def test_train_workflow_on_two_ranks(project, mode):
-    """`lm train` end to end on two gloo ranks in each multi-rank mode: sharded, replicated, pipelined, tensor-parallel."""
+    """`lm train` end to end on two gloo ranks in each multi-rank mode: sharded, replicated, pipelined, tensor-parallel, expert-parallel."""
     from tests.conftest import run_ranks
 
     config = train_config(project, max_steps=2)
@@ -164,7 +164,12 @@ def test_train_workflow_on_two_ranks(project, mode):
     elif mode == "pipeline":
         config["acceleration"] = {"use_fsdp": False}
         config["parallel"] = {"pp": 2, "fsdp": 1, "pp_microbatches": 2}
-    else:
+    elif mode == "tensor":
         config["acceleration"] = {"use_fsdp": False}
         config["parallel"] = {"tp": 2, "fsdp": 1}
+    else:
+        config["model"] = {**config["model"], "d_ff": 32,
+                           "moe": {"num_experts": 4, "top_k": 2, "shared_experts": 1, "d_ff": 32, "capacity_factor": 4.0}}
+        config["acceleration"] = {"use_fsdp": True}
+        config["parallel"] = {"fsdp": 2, "ep": 2}
     run_ranks(_train_rank, 2, str(project), config)
