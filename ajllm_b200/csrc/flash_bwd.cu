@@ -51,24 +51,29 @@ __device__ __forceinline__ void store_operand_chunk(uint8_t* tile, int row, int 
 // ------------------------------------------------------------------------------------------ delta
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
                                    float* __restrict__ delta, int batch, int seq, int heads, int head_dim) {
-  // one warp per (b, t, h)
-  const long long warp_id = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  // head_dim / 8 threads per (b, t, h), one 16-byte vector of O and of dO each; head_dim is 64 or 128, so a
+  // group is 8 or 16 lanes of one warp
+  const int group = head_dim >> 3;
+  const long long thread = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long item = thread / group;
+  const int part = (int)(thread % group);
   const long long total = (long long)batch * seq * heads;
-  if (warp_id >= total) return;
-  const int h = (int)(warp_id % heads);
-  const long long bt = warp_id / heads;
-  const __nv_bfloat16* o = out + (size_t)warp_id * head_dim;
-  const __nv_bfloat16* d = dout + (size_t)warp_id * head_dim;
   float s = 0.0f;
-  for (int i = lane * 2; i < head_dim; i += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
-    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
-    s += a.x * g.x + a.y * g.y;
-  }
+  if (item < total) {
+    const uint4 a = reinterpret_cast<const uint4*>(out + (size_t)item * head_dim)[part];
+    const uint4 g = reinterpret_cast<const uint4*>(dout + (size_t)item * head_dim)[part];
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(gh[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  for (int off = group >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (item < total && part == 0) {
+    const int h = (int)(item % heads);
+    const long long bt = item / heads;
     const int b = (int)(bt / seq), t = (int)(bt % seq);
     delta[((size_t)b * heads + h) * seq + t] = s;
   }
@@ -923,9 +928,9 @@ template <int HD>
 static int launch_bwd(const void* qkv, const void* out, const void* dout, const void* lse, void* delta, void* dqkv,
                       void* dq_acc, int batch, int seq, int heads, int kv_heads, long long row_stride, int causal,
                       float scale, cudaStream_t stream) {
-  const long long warps = (long long)batch * seq * heads;
+  const long long items = (long long)batch * seq * heads;
   const int threads = 256;
-  const long long blocks = (warps * 32 + threads - 1) / threads;
+  const long long blocks = (items * (HD / 8) + threads - 1) / threads;
   flash_delta_kernel<<<(unsigned)blocks, threads, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout,
                                                                 (float*)delta, batch, seq, heads, HD);
   AJB_CUDA_OK(cudaGetLastError());
