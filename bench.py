@@ -230,7 +230,7 @@ def run_ours(args) -> None:
 def run_reference(args) -> None:
     ref_root = ROOT / "baseline" / "_ref"
     if not (ref_root / "ajllm" / "__init__.py").is_file():
-        emit({"impl": "reference", "unavailable": "baseline/_ref holds no reference install (see DESIGN.md)"})
+        emit({"impl": "reference", "unavailable": "baseline/_ref holds no reference install"})
         return
     sys.path.insert(0, str(ref_root))
     try:
