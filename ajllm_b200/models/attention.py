@@ -32,6 +32,7 @@ class SelfAttention(nn.Module):
         self.total_heads, self.total_kv_heads = num_heads, num_kv_heads
         self.head_dim = d_model // num_heads
         self.tp = tp
+        self.qkv_override = None
         tp_size = tp.size if tp is not None else 1
         if num_heads % tp_size or num_kv_heads % tp_size:
             raise ValueError("tensor parallel size must divide both head counts")
@@ -124,6 +125,8 @@ class SelfAttention(nn.Module):
     # ----- compute
     def project_qkv(self, x: torch.Tensor) -> torch.Tensor:
         """``x`` holds this rank's tokens; the result covers all tokens and this rank's heads."""
+        if self.qkv_override is not None:         # a wrapper that produces the projection its own way (sharded weights)
+            return self.qkv_override(x)
         if self.tp is not None and self.tp.size > 1:
             return self.tp.gather_linear(x, self.qkv_proj)
         return ops.linear(x, self.qkv_proj)

@@ -51,6 +51,42 @@ class _Unit:
     base: int = 0                                  # offset of this unit's shard in the rank-wide flat buffers
 
 
+class _GatherWeightLinearFn(torch.autograd.Function):
+    """``x @ W^T`` where producing the output also makes ``W`` resident: ``produce(x)`` runs the kernel that gathers
+    the unit's flat parameter buffer while it multiplies (``csrc/comm_gemm.cu`` mode 3) and points the unit's
+    parameters at the gathered buffer. The backward pass is the ordinary one, on the then-resident weight."""
+
+    @staticmethod
+    def forward(ctx, x, weight, produce):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        out = produce(x2)
+        ctx.save_for_backward(x2, weight)
+        ctx.lead = x.shape[:-1]
+        return out.view(*ctx.lead, out.shape[-1])
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from ajllm_b200.ops.functional import gemm, wgrad_epilogue
+        x2, weight = ctx.saved_tensors
+        n, k = weight.shape
+        g2 = grad_out.reshape(-1, n).to(torch.bfloat16).contiguous()
+        m = g2.shape[0]
+        grad_x = None
+        if ctx.needs_input_grad[0]:
+            grad_x = torch.empty(m, k, dtype=torch.bfloat16, device=g2.device)
+            gemm(g2, weight, grad_x, m, k, n, b_mn_major=True)
+            grad_x = grad_x.view(*ctx.lead, k)
+        grad_w = None
+        main = getattr(weight, "main_grad", None)
+        if main is not None:
+            gemm(g2, x2, main, n, k, m, a_mn_major=True, b_mn_major=True, epilogue=wgrad_epilogue())
+            weight.main_grad_written = True
+        else:
+            grad_w = torch.empty(n, k, dtype=torch.bfloat16, device=g2.device)
+            gemm(g2, x2, grad_w, n, k, m, a_mn_major=True, b_mn_major=True)
+        return grad_x, grad_w, None
+
+
 class ShardedOptimizer:
     """AdamW over this rank's shards; same surface as :class:`~ajllm_b200.training.optim.FlatAdamW`."""
 
@@ -83,6 +119,7 @@ class ShardedOptimizer:
             flat_adamw(o.local_master, o.local_grad, o.local_m, o.local_v,
                        None if o.local_master is o.local_working else o.local_working, self.step_count,
                        g["lr"], b1, b2, g["eps"], g["weight_decay"], sumsq, max_norm)
+        o.refresh_norm_cache()
         return sumsq.sqrt()
 
     def state_dict(self) -> dict[str, Any]:
@@ -124,7 +161,8 @@ class ShardedOptimizer:
 class ShardedDataParallel(nn.Module):
     def __init__(self, module, group, checkpoint_layers: bool = True, learning_rate: float = 1e-3,
                  betas=(0.9, 0.95), epsilon: float = 1e-8, weight_decay: float = 0.0,
-                 replica_group=None, replicas: int = 1, prefetch: bool = True, fused_reduce: bool | None = None) -> None:
+                 replica_group=None, replicas: int = 1, prefetch: bool = True, fused_reduce: bool | None = None,
+                 fused_gather: bool | None = None) -> None:
         super().__init__()
         if module.norm_placement != "pre":
             raise ValueError("sharded training supports pre-norm models")
@@ -165,6 +203,15 @@ class ShardedDataParallel(nn.Module):
             self._sumsq_partials = torch.zeros(len(self.units), FusedGradReduce.CTAS, dtype=torch.float32, device=dev)
         else:
             self._full_grad = torch.zeros(largest, dtype=torch.float32, device=dev)
+        # Parameter all-gather of a block fused into its first GEMM (the QKV projection): opt-in, bf16 on GPUs.
+        # Needs the block's first norm gain before the block's parameters arrive: every rank keeps a copy of those.
+        if fused_gather is None:
+            fused_gather = os.environ.get("AJB_FUSED_FSDP_GATHER", "0") == "1"
+        self.fused_gather = None
+        self._norm_cache: dict[int, torch.Tensor] = {}
+        if fused_gather and dev.type == "cuda" and self.dtype == torch.bfloat16 and 1 < self.world <= 8:
+            from ajllm_b200.parallel.fused import FusedTensorParallel
+            self.fused_gather = FusedTensorParallel(group, dev)
         self._resident: dict[int, int] = {}          # unit index -> slot of self._full holding it
         self._gather_events: dict[int, Any] = {}
         self._side = torch.cuda.Stream(device=dev) if self.prefetch else None
@@ -173,6 +220,8 @@ class ShardedDataParallel(nn.Module):
         self.master = self.working if self.dtype == torch.float32 else self.working.float()
         self._setup_local_params()
         self.optimizer = ShardedOptimizer(self, learning_rate, betas, epsilon, weight_decay)
+        if self.fused_gather is not None:
+            self.refresh_norm_cache()
 
     # ------------------------------------------------------------------ construction
     def _is_local(self, name: str) -> bool:
@@ -310,6 +359,83 @@ class ShardedDataParallel(nn.Module):
         for p in unit.params:
             p.main_grad = None
 
+    # ------------------------------------------------------------------ gather fused into the first GEMM of a block
+    def refresh_norm_cache(self) -> None:
+        """Copies of every block's first norm gain on every rank (one small broadcast; after each optimizer step)."""
+        if self.fused_gather is None:
+            return
+        layers = list(self.module.layers)
+        d = self.module.d_model
+        packed = torch.empty(len(layers), d, dtype=self.dtype, device=self.device)
+        for i, layer in enumerate(layers, start=1):
+            unit = self.units[i]
+            off = self._offset_of(unit, layer.norm1.weight)
+            if off + d > unit.shard:
+                raise ValueError("a block's first norm gain must lie inside the first rank's slice of its unit")
+            if self.rank == 0:
+                packed[i - 1].copy_(self.working[unit.base + off:unit.base + off + d])
+        src = dist.get_global_rank(self.group, 0) if hasattr(dist, "get_global_rank") else 0
+        dist.broadcast(packed, src=src, group=self.group)
+        self._norm_cache = {i: packed[i - 1] for i in range(1, len(layers) + 1)}
+
+    @staticmethod
+    def _offset_of(unit: _Unit, param) -> int:
+        """Offset of ``param`` in its unit's flat buffer (identity search: ``==`` on tensors is element-wise)."""
+        return next(off for p, off in zip(unit.params, unit.offsets) if p is param)
+
+    def _make_resident(self, index: int, slot: int) -> None:
+        unit = self.units[index]
+        full = self._full[slot]
+        for p, off in zip(unit.params, unit.offsets):
+            p.data = full[off:off + p._full_shape.numel()].view(p._full_shape)
+        self._resident[index] = slot
+
+    def _run_block(self, index: int, layer, stream, pending, shape, prefetch_next: int | None):
+        """Forward of block ``index`` (unit number). Default: make the unit resident (NCCL all-gather, usually
+        prefetched one unit ahead), then run the block. With the fused gather and a unit that is not resident
+        yet, the QKV projection itself gathers the unit (its first norm runs on the cached gain)."""
+        attn = layer.attention
+        fusable = (self.fused_gather is not None and index not in self._resident and index in self._norm_cache
+                   and stream.dim() == 2 and stream.shape[0] % 128 == 0 and getattr(attn, "tp", None) is None)
+        if not fusable:
+            self._acquire(index, self._prefetch_target(prefetch_next))
+            return layer.forward_prenorm(stream, pending, shape)
+        unit = self.units[index]
+        busy = set(self._resident.values())
+        slot = next((s for s in range(len(self._full)) if s not in busy), None)
+        if slot is None:
+            raise RuntimeError("no free gather buffer: a unit was not released")
+        weight = attn.qkv_proj
+        n, k = weight._full_shape
+        offset = self._offset_of(unit, weight)
+
+        def produce(x2: torch.Tensor) -> torch.Tensor:
+            _, out = self.fused_gather.gather_weight_gemm(
+                x2, self.working[unit.base:unit.base + unit.shard], n, k, offset_elems=offset,
+                out_flat=self._full[slot][:unit.padded])
+            self._make_resident(index, slot)
+            return out
+
+        layer.norm1.weight.data = self._norm_cache[index]        # same values as the gathered copy that replaces it
+        attn.qkv_override = lambda x: _GatherWeightLinearFn.apply(x, weight, produce)
+        try:
+            result = layer.forward_prenorm(stream, pending, shape)
+        finally:
+            attn.qkv_override = None
+        target = self._prefetch_target(prefetch_next)
+        if target is not None and self.prefetch:
+            self._issue_gather(target)
+        return result
+
+    def _is_block(self, index: int) -> bool:
+        return 1 <= index <= len(self.module.layers)
+
+    def _prefetch_target(self, index: int | None) -> int | None:
+        """Units that gather inside their own first GEMM are not prefetched."""
+        if index is None or (self.fused_gather is not None and self._is_block(index)):
+            return None
+        return index
+
     # ------------------------------------------------------------------ compute
     def _embed(self, ids_flat: torch.Tensor, seq: int) -> torch.Tensor:
         m = self.module
@@ -339,13 +465,12 @@ class ShardedDataParallel(nn.Module):
     def _forward_only(self, token_ids, targets) -> torch.Tensor:
         m, n = self.module, len(self.units)
         B, T = token_ids.shape
-        self._acquire(0, 1)
+        self._acquire(0, self._prefetch_target(1))
         stream = self._embed(token_ids.reshape(-1), T)
         self._release(0)
         pending = None
         for i, layer in enumerate(m.layers, start=1):
-            self._acquire(i, i + 1 if i + 1 < n else None)
-            stream, pending = layer.forward_prenorm(stream, pending, (B, T))
+            stream, pending = self._run_block(i, layer, stream, pending, (B, T), i + 1 if i + 1 < n else None)
             self._release(i)
         self._acquire(n - 1)
         if m.tie_embeddings:
@@ -377,19 +502,18 @@ class ShardedDataParallel(nn.Module):
         ids_flat = token_ids.reshape(-1)
         # ---- forward without autograd, remembering each unit's input
         with torch.no_grad():
-            self._acquire(0, 1)
+            self._acquire(0, self._prefetch_target(1))
             stream = self._embed(ids_flat, T)
             self._release(0)
             pending = None
             saved = []
             for i, layer in enumerate(m.layers, start=1):
                 saved.append((stream, pending))
-                self._acquire(i, i + 1 if i + 1 < n else None)
-                stream, pending = layer.forward_prenorm(stream, pending, (B, T))
+                stream, pending = self._run_block(i, layer, stream, pending, (B, T), i + 1 if i + 1 < n else None)
                 self._release(i)
         # ---- head: forward + backward with autograd
         head = n - 1
-        self._acquire(head, head - 1 if head - 1 >= 1 else None)
+        self._acquire(head, self._prefetch_target(head - 1 if head - 1 >= 1 else None))
         self._attach_grad_views(self.units[head])
         tied_grad = None
         if tied:
@@ -419,13 +543,12 @@ class ShardedDataParallel(nn.Module):
         # ---- blocks in reverse: recompute with autograd, back-propagate, reduce-scatter
         for i in range(len(m.layers), 0, -1):
             layer = m.layers[i - 1]
-            self._acquire(i, i - 1 if i - 1 >= 1 else 0)
             self._attach_grad_views(self.units[i])
             s_in, p_in = saved[i - 1]
             s_in = s_in.detach().requires_grad_(True)
             p_req = p_in.detach().requires_grad_(True) if p_in is not None else None
             with torch.enable_grad():
-                s_out, p_out = layer.forward_prenorm(s_in, p_req, (B, T))
+                s_out, p_out = self._run_block(i, layer, s_in, p_req, (B, T), i - 1 if i - 1 >= 1 else 0)
                 outs, grads = [s_out, p_out], [grad_stream, grad_pending]
                 aux = getattr(layer.feed_forward, "last_aux_loss", None)
                 if aux is not None and aux.requires_grad:
@@ -514,3 +637,4 @@ class ShardedDataParallel(nn.Module):
             self.master.copy_(self.working.float())
             if self.local_master is not None:
                 self.local_master.copy_(self.local_working.float())
+        self.refresh_norm_cache()

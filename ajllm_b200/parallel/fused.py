@@ -168,19 +168,23 @@ class FusedTensorParallel:
         self._launch(MODE_ALL_REDUCE, m, n, k, weight, False, out, a=x.contiguous(), a_rows=rows)
         return out[:rows]
 
-    def gather_weight_gemm(self, x: torch.Tensor, shard: torch.Tensor, n: int, k: int, offset_elems: int = 0):
+    def gather_weight_gemm(self, x: torch.Tensor, shard: torch.Tensor, n: int, k: int, offset_elems: int = 0,
+                           out_flat: torch.Tensor | None = None):
         """``x @ W^T`` where ``W [n, k]`` starts at element ``offset_elems`` of the flat parameter buffer that is
         the concatenation of every rank's ``shard`` (fully sharded weights; inference or the forward of a unit).
 
         Returns ``(flat, out)``: the gathered flat buffer (all parameters of the unit, usable by the GEMMs
-        that follow) and ``out [rows, n]``. The peers' slices travel while the first tiles are computed."""
+        that follow; ``out_flat`` when given) and ``out [rows, n]``. The peers' slices travel while the first
+        tiles are computed."""
         rows = x.shape[0]
         if rows % self.BLOCK_M != 0 or x.dtype != torch.bfloat16 or shard.dtype != torch.bfloat16:
             raise ValueError("gather_weight_gemm needs bf16 operands and a multiple of 128 rows")
         shard_elems = shard.numel()
         self._ensure("stage", shard_elems * 2)
         self._stage[: shard_elems * 2].view(torch.bfloat16).copy_(shard.reshape(-1))
-        flat = torch.empty(self.size * shard_elems, dtype=torch.bfloat16, device=self.device)
+        flat = out_flat if out_flat is not None else torch.empty(self.size * shard_elems, dtype=torch.bfloat16, device=self.device)
+        if flat.numel() != self.size * shard_elems or flat.dtype != torch.bfloat16 or not flat.is_contiguous():
+            raise ValueError("out_flat must be a contiguous bf16 buffer of world * shard elements")
         flat[self.rank * shard_elems:(self.rank + 1) * shard_elems].copy_(shard.reshape(-1))   # the kernel moves remote slices
         out = torch.empty(rows, n, dtype=torch.bfloat16, device=self.device)
         self._launch(MODE_GATHER_WEIGHT, rows, n, k, flat, False, out, a=x.contiguous(), gathered=flat,

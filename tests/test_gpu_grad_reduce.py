@@ -50,11 +50,16 @@ def _worker(rank: int, world: int, port: int, results):
 
         # ---- inside the sharded wrapper: same model, same batches, fused against NCCL
         shards = {}
-        for fused in (True, False):
+        # True / False: gradient reduce-scatter fused / NCCL; "gather": additionally the parameter all-gather of
+        # every block runs inside the block's QKV projection (csrc/comm_gemm.cu, gather-weight mode)
+        for fused in (True, False, "gather"):
             torch.manual_seed(0)
             with torch.device(device):
                 model = build_model(MODEL, VOCAB).to(dtype=torch.bfloat16)
-            fsdp = ShardedDataParallel(model, dist.group.WORLD, learning_rate=1e-3, fused_reduce=fused)
+            fsdp = ShardedDataParallel(model, dist.group.WORLD, learning_rate=1e-3, fused_reduce=bool(fused),
+                                       fused_gather=(fused == "gather"))
+            if fused == "gather":
+                assert fsdp.fused_gather is not None
             opt = fsdp.optimizer
             norms = []
             for step in range(2):
@@ -70,6 +75,7 @@ def _worker(rank: int, world: int, port: int, results):
             del fsdp, model
         ref = shards[False]
         out["fsdp_grad_rel"] = float((shards[True] - ref).norm() / ref.norm())
+        out["fsdp_gather_grad_rel"] = float((shards["gather"] - ref).norm() / ref.norm())
         torch.cuda.synchronize()
         out["status"] = native.lib().ajb_check_status()
         results[rank] = out
@@ -145,7 +151,10 @@ def test_fused_gradient_reduce_scatter():
         assert out["status"] == 0, out
         assert out["kernel_max_abs"] < 1e-5, out
         assert out["sumsq_rel"] < 1e-5, out
-        # the two paths add the same fp32 partials, in a different order at most
-        assert out["fsdp_grad_rel"] < 1e-3, out
-        for a, b in zip(out["norms_True"], out["norms_False"]):
-            assert abs(a - b) <= 1e-3 * max(abs(b), 1e-6), out
+        # the paths add the same fp32 partials in a different order; the step-2 gradients compared here also carry
+        # the order-dependent last bits of step 1 (K-sliced weight gradients and dQ are summed with reductions)
+        assert out["fsdp_grad_rel"] < 5e-3, out
+        assert out["fsdp_gather_grad_rel"] < 5e-3, out
+        for key in ("norms_True", "norms_gather"):
+            for a, b in zip(out[key], out["norms_False"]):
+                assert abs(a - b) <= 1e-3 * max(abs(b), 1e-6), out
