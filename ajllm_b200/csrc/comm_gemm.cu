@@ -233,6 +233,80 @@ struct TileQueue {
   int tile[kQueue];
 };
 
+// Closing reduction: out[i] = sum over the tp slots of this rank's receive buffer, fp32 accumulation, 8 bf16 per
+// vector. One CTA per SM with 192 threads has to keep the whole memory system busy here, so every thread has
+// TP * U independent 16-byte loads in flight before it adds anything (TP = 0: rank count known only at run time,
+// U loads in flight per slot).
+template <int TP, int U>
+__device__ __forceinline__ void sum_slots(const Params& p) {
+  const long long vec_total = (long long)p.m_local * p.n / 8;
+  const uint4* base = reinterpret_cast<const uint4*>(p.recv_ptrs[p.rank]);
+  uint4* out = reinterpret_cast<uint4*>(p.out_local);
+  const long long stride = (long long)gridDim.x * kThreads;
+  const int tp = TP > 0 ? TP : p.tp;
+  for (long long i0 = (long long)blockIdx.x * kThreads + threadIdx.x; i0 < vec_total; i0 += stride * U) {
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+    if (TP > 0) {
+      uint4 q[TP > 0 ? TP : 1][U];
+#pragma unroll
+      for (int r = 0; r < (TP > 0 ? TP : 1); ++r)
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          q[r][u] = i < vec_total ? base[(long long)r * vec_total + i] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+      for (int r = 0; r < (TP > 0 ? TP : 1); ++r)
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[r][u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc[u][2 * j] += f.x;
+            acc[u][2 * j + 1] += f.y;
+          }
+        }
+    } else {
+      for (int r = 0; r < tp; ++r) {
+        uint4 q[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          q[u] = i < vec_total ? base[(long long)r * vec_total + i] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc[u][2 * j] += f.x;
+            acc[u][2 * j + 1] += f.y;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < vec_total) {
+        uint4 o;
+        o.x = pack_bf16x2(acc[u][0], acc[u][1]);
+        o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+        o.z = pack_bf16x2(acc[u][4], acc[u][5]);
+        o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+        out[i] = o;
+      }
+    }
+  }
+}
+
+
 template <bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
@@ -409,15 +483,23 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quarter = warp & 3;
     uint8_t* my_row = epi_base + (quarter * 32 + lane) * kEpiRowPitch;    // this lane's staged output row
     bool ok = true;
-    int pending_shard = -1;          // tile whose bulk stores are in flight and not yet announced (-1: none, tp: to all ranks)
-    auto announce = [&](int shard_done) {
-      __syncwarp();                  // every lane's rows of that tile are complete in (peer) memory
-      if (shard_done < 0 || lane != 0) return;
-      if (shard_done < p.tp) {
-        red_release_sys_add(p.counter_ptrs[shard_done] + p.rank, 1u);
-      } else {
-        for (int r = 0; r < p.tp; ++r) red_release_sys_add(p.counter_ptrs[r] + p.rank, 1u);
+    // The reader of a receive buffer only starts once every tile of every rank has been counted, so the
+    // tiles are credited in bulk: this warp counts what it stored for the current destination and tells the
+    // owner (one release per destination, after the stores have landed) when the destination changes and
+    // at the end. A release per tile would stall the epilogue for longer than the tile's MMAs take.
+    int pending_shard = -1;          // destination of the uncredited tiles (-1: none, tp: every rank)
+    unsigned int pending_tiles = 0;
+    auto credit = [&]() {
+      bulk_wait_all();
+      __syncwarp();                  // every lane's rows of those tiles are complete in (peer) memory
+      if (pending_tiles != 0 && lane == 0) {
+        if (pending_shard < p.tp) {
+          red_release_sys_add(p.counter_ptrs[pending_shard] + p.rank, pending_tiles);
+        } else {
+          for (int r = 0; r < p.tp; ++r) red_release_sys_add(p.counter_ptrs[r] + p.rank, pending_tiles);
+        }
       }
+      pending_tiles = 0;
     };
     for (uint32_t qi = 0; ok; ++qi) {
       const int slot = qi % kQueue;
@@ -480,13 +562,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (bytes > 0) bulk_s2g(dst, my_row, (uint32_t)bytes);
       }
       bulk_commit();
-      // the previous tile had a whole tile time to land: wait for it (not for the one just issued) and announce it
-      bulk_wait_all_but_latest();
-      announce(pending_shard);
-      pending_shard = p.mode == kReduceScatter ? shard : (p.mode == kAllReduce ? p.tp : -1);   // gathers announce nothing
+      const int target = p.mode == kReduceScatter ? shard : (p.mode == kAllReduce ? p.tp : -1);   // gathers announce nothing
+      if (target != pending_shard) credit();
+      pending_shard = target;
+      if (target >= 0) ++pending_tiles;
     }
-    bulk_wait_all();
-    announce(pending_shard);
+    credit();
   }
 
   tc_fence_before_sync();
@@ -507,27 +588,11 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     __syncthreads();
     if (*arrived) {
-      const long long vec_total = (long long)p.m_local * p.n / 8;
-      const uint4* base = reinterpret_cast<const uint4*>(p.recv_ptrs[p.rank]);
-      uint4* out = reinterpret_cast<uint4*>(p.out_local);
-      for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < vec_total; i += (long long)gridDim.x * kThreads) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r = 0; r < p.tp; ++r) {
-          const uint4 q = base[(long long)r * vec_total + i];
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h[j]);
-            acc[2 * j] += f.x;
-            acc[2 * j + 1] += f.y;
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]);
-        o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]);
-        o.w = pack_bf16x2(acc[6], acc[7]);
-        out[i] = o;
+      switch (p.tp) {
+        case 2: sum_slots<2, 8>(p); break;
+        case 4: sum_slots<4, 4>(p); break;
+        case 8: sum_slots<8, 2>(p); break;
+        default: sum_slots<0, 4>(p); break;
       }
     }
     __syncthreads();

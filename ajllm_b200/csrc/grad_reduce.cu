@@ -68,6 +68,44 @@ __device__ __forceinline__ bool wait_epoch(const unsigned int* p, unsigned int w
   }
 }
 
+// U vectors per thread and trip (WMAX bounds the rank count): with `world` peers that is world * U independent 16-byte loads in flight per
+// thread before the first add, which is what hides the NVLink round trip with only a few dozen CTAs.
+template <int WMAX, int U>
+__device__ __forceinline__ float reduce_slices(const Params& p) {
+  float ss = 0.0f;
+  const long long stride = (long long)gridDim.x * kThreads;
+  for (long long i0 = (long long)blockIdx.x * kThreads + threadIdx.x; i0 < p.shard_vec4; i0 += stride * U) {
+    float4 part[WMAX][U];
+#pragma unroll
+    for (int r = 0; r < WMAX; ++r)
+      if (r < p.world) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          part[r][u] = i < p.shard_vec4 ? ld_peer(p.full_ptrs[r] + (long long)p.rank * p.shard_vec4 + i)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= p.shard_vec4) break;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < WMAX; ++r)
+        if (r < p.world) { acc.x += part[r][u].x; acc.y += part[r][u].y; acc.z += part[r][u].z; acc.w += part[r][u].w; }
+      float4 out = make_float4(acc.x * p.scale, acc.y * p.scale, acc.z * p.scale, acc.w * p.scale);
+      if (p.accumulate) {
+        const float4 old = p.dst[i];
+        out.x += old.x; out.y += old.y; out.z += old.z; out.w += old.w;
+      }
+      p.dst[i] = out;
+      ss += out.x * out.x + out.y * out.y + out.z * out.z + out.w * out.w;
+    }
+  }
+  return ss;
+}
+
 __global__ void __launch_bounds__(kThreads) grad_reduce_scatter_kernel(const Params p) {
   __shared__ int s_ok;
   __shared__ float s_red[kThreads / 32];
@@ -83,24 +121,9 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_scatter_kernel(const Par
   __syncthreads();
   float ss = 0.0f;
   if (s_ok) {
-    const long long stride = (long long)gridDim.x * kThreads;
-    for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < p.shard_vec4; i += stride) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      float4 part[kMaxRanks];
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < p.world) part[r] = ld_peer(p.full_ptrs[r] + (long long)p.rank * p.shard_vec4 + i);
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < p.world) { acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w; }
-      float4 out = make_float4(acc.x * p.scale, acc.y * p.scale, acc.z * p.scale, acc.w * p.scale);
-      if (p.accumulate) {
-        const float4 old = p.dst[i];
-        out.x += old.x; out.y += old.y; out.z += old.z; out.w += old.w;
-      }
-      p.dst[i] = out;
-      ss += out.x * out.x + out.y * out.y + out.z * out.z + out.w * out.w;
-    }
+    if (p.world <= 2) ss = reduce_slices<2, 8>(p);
+    else if (p.world <= 4) ss = reduce_slices<4, 4>(p);
+    else ss = reduce_slices<kMaxRanks, 2>(p);
   }
   if (p.sumsq_partials != nullptr) {
 #pragma unroll
