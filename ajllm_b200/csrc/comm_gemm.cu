@@ -484,23 +484,10 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint8_t* my_row = epi_base + (quarter * 32 + lane) * kEpiRowPitch;    // this lane's staged output row
     bool ok = true;
     // The reader of a receive buffer only starts once every tile of every rank has been counted, so the
-    // tiles are credited in bulk: this warp counts what it stored for the current destination and tells the
-    // owner (one release per destination, after the stores have landed) when the destination changes and
-    // at the end. A release per tile would stall the epilogue for longer than the tile's MMAs take.
-    int pending_shard = -1;          // destination of the uncredited tiles (-1: none, tp: every rank)
-    unsigned int pending_tiles = 0;
-    auto credit = [&]() {
-      bulk_wait_all();
-      __syncwarp();                  // every lane's rows of those tiles are complete in (peer) memory
-      if (pending_tiles != 0 && lane == 0) {
-        if (pending_shard < p.tp) {
-          red_release_sys_add(p.counter_ptrs[pending_shard] + p.rank, pending_tiles);
-        } else {
-          for (int r = 0; r < p.tp; ++r) red_release_sys_add(p.counter_ptrs[r] + p.rank, pending_tiles);
-        }
-      }
-      pending_tiles = 0;
-    };
+    // tiles are credited in bulk at the end of the kernel: lane r of this warp counts the tiles stored to
+    // rank r and, once all stores have landed, tells rank r with one release. A release per tile would stall
+    // the epilogue for longer than the tile's MMAs take.
+    unsigned int stored_tiles = 0;   // lane r: tiles this warp stored into rank r's receive buffer
     for (uint32_t qi = 0; ok; ++qi) {
       const int slot = qi % kQueue;
       if (!mbar_wait(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 7)) break;
@@ -562,12 +549,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (bytes > 0) bulk_s2g(dst, my_row, (uint32_t)bytes);
       }
       bulk_commit();
-      const int target = p.mode == kReduceScatter ? shard : (p.mode == kAllReduce ? p.tp : -1);   // gathers announce nothing
-      if (target != pending_shard) credit();
-      pending_shard = target;
-      if (target >= 0) ++pending_tiles;
+      if (p.mode == kReduceScatter) stored_tiles += lane == shard ? 1u : 0u;
+      else if (p.mode == kAllReduce) stored_tiles += lane < p.tp ? 1u : 0u;
     }
-    credit();
+    bulk_wait_all();
+    __syncwarp();                    // every lane's rows are complete in (peer) memory
+    if (stored_tiles != 0) red_release_sys_add(p.counter_ptrs[lane] + p.rank, stored_tiles);
   }
 
   tc_fence_before_sync();
