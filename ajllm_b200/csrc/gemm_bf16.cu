@@ -15,6 +15,9 @@
 // epilogue of tile i overlaps the main loop of tile i+1. Tiles are visited in groups of 16 row-blocks
 // so that a wave of CTAs shares its A and B panels through L2.
 #include "common.cuh"
+#include "gemm_pair.h"
+
+#include <cstdlib>
 
 namespace ajb {
 
@@ -447,26 +450,51 @@ extern "C" int ajb_gemm_bf16(const void* a, const void* b, void* c, int m, int n
   using namespace ajb;
   AJB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm: empty problem %dx%dx%d", m, n, k);
   AJB_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm: unknown epilogue %d", epilogue);
-  gemm::BatchSpec spec;
-  if (epilogue == gemm::kAtomicAddF32) {
-    // Accumulating products with a long K (weight gradients: K = tokens) often have a tile count that fills the
-    // SMs badly, e.g. 352 tiles on 148 SMs run as three rounds, the last one 40 % full. Cutting K into slices that
-    // add into the same tile with reductions evens that out; with one slice this is the plain accumulate epilogue.
-    const int tiles = ((m + gemm::BM - 1) / gemm::BM) * ((n + 255) / 256);
-    const int sms = sm_count();
-    const int k_blocks = (k + gemm::BK - 1) / gemm::BK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int sms = sm_count();
+  const int k_blocks = (k + gemm::BK - 1) / gemm::BK;
+  // Accumulating products with a long K (weight gradients: K = tokens) often have a tile count that fills the
+  // SMs badly, e.g. 352 tiles on 148 SMs run as three rounds, the last one 40 % full. Cutting K into slices that
+  // add into the same tile with reductions evens that out; with one slice this is the plain accumulate epilogue.
+  auto pick_split = [&](int tiles, int units_per_round) {
     int best = 1;
-    double best_eff = (double)tiles / (((tiles + sms - 1) / sms) * (double)sms);
+    double best_eff = (double)tiles / (((tiles + units_per_round - 1) / units_per_round) * (double)units_per_round);
+    if (epilogue != gemm::kAtomicAddF32) return best;
     for (int split = 2; split <= 4 && k_blocks / split >= 32; ++split) {
       const int units = tiles * split;
-      const double eff = (double)units / (((units + sms - 1) / sms) * (double)sms);
+      const double eff = (double)units / (((units + units_per_round - 1) / units_per_round) * (double)units_per_round);
       if (eff > best_eff + 0.04) { best = split; best_eff = eff; }
     }
-    if (best == 1) epilogue = gemm::kAccumF32;
-    else { spec.split_k = best; spec.split_stride = 0; }
+    return best;
+  };
+  const int tiles_single = ((m + gemm::BM - 1) / gemm::BM) * ((n + 255) / 256);
+  const int split_single = pick_split(tiles_single, sms);
+
+  // Two kernels: CTA pairs on 256 x 256 tiles (a third fewer operand bytes per CTA, about 1.1 x faster per tile)
+  // and single CTAs on 128 x 256 or 128 x 128 tiles. Time is rounds x k-blocks per round; the pair kernel gets
+  // the problem unless its coarser tiles cost more rounds than its per-tile advantage buys back.
+  static const bool pairs_enabled = [] {
+    const char* v = std::getenv("AJB_GEMM_PAIR");
+    return v == nullptr || v[0] != '0';
+  }();
+  const bool narrow = (n % 256 != 0) && ((n + 127) / 128 * 128 < (n + 255) / 256 * 256);
+  if (pairs_enabled && !narrow && m > gemm::BM) {
+    const int pairs = gemm_pair::capacity();
+    const int tiles_pair = ((m + 2 * gemm::BM - 1) / (2 * gemm::BM)) * ((n + 255) / 256);
+    const int split_pair = pick_split(tiles_pair, pairs);
+    const double rounds_single = (double)((tiles_single * split_single + sms - 1) / sms) / split_single;
+    const double rounds_pair = (double)((tiles_pair * split_pair + pairs - 1) / pairs) / split_pair;
+    if (rounds_pair * 0.93 <= rounds_single) {
+      const int epi = (epilogue == gemm::kAtomicAddF32 && split_pair == 1) ? (int)gemm::kAccumF32 : epilogue;
+      return gemm_pair::run(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epi, split_pair, s);
+    }
   }
-  return gemm::dispatch<false>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, spec,
-                               reinterpret_cast<cudaStream_t>(stream));
+  gemm::BatchSpec spec;
+  if (epilogue == gemm::kAtomicAddF32) {
+    if (split_single == 1) epilogue = gemm::kAccumF32;
+    else { spec.split_k = split_single; spec.split_stride = 0; }
+  }
+  return gemm::dispatch<false>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, spec, s);
 }
 
 // `batch` equal-shaped problems (one per expert), operands / outputs `*_stride` elements apart. When valid_rows is

@@ -51,6 +51,8 @@ def run_gemm(dev, small: bool) -> None:
         gemm_case(dev, "square", 16384, 4096, 4096)
         return
     rows = 32768
+    print(f"resident CTA pairs: {native.lib().ajb_gemm_pair_capacity()} (AJB_GEMM_PAIR=0 keeps every product on the "
+          f"single-CTA kernel)", flush=True)
     gemm_case(dev, "fwd qkv", rows, 4096, 2048)
     gemm_case(dev, "fwd w13", rows, 11264, 2048)
     gemm_case(dev, "fwd w2", rows, 2048, 5632)
@@ -59,9 +61,9 @@ def run_gemm(dev, small: bool) -> None:
     gemm_case(dev, "dgrad w13", rows, 2048, 11264, b_mn=True)
     gemm_case(dev, "dgrad w2", rows, 5632, 2048, b_mn=True)
     gemm_case(dev, "dgrad qkv", rows, 2048, 4096, b_mn=True)
-    gemm_case(dev, "wgrad w13 (f32 acc)", 11264, 2048, rows, a_mn=True, b_mn=True, epilogue=1)
-    gemm_case(dev, "wgrad w2 (f32 acc)", 2048, 5632, rows, a_mn=True, b_mn=True, epilogue=1)
-    gemm_case(dev, "wgrad qkv (f32 acc)", 4096, 2048, rows, a_mn=True, b_mn=True, epilogue=1)
+    gemm_case(dev, "wgrad w13 (f32 add)", 11264, 2048, rows, a_mn=True, b_mn=True, epilogue=3)
+    gemm_case(dev, "wgrad w2 (f32 add)", 2048, 5632, rows, a_mn=True, b_mn=True, epilogue=3)
+    gemm_case(dev, "wgrad qkv (f32 add)", 4096, 2048, rows, a_mn=True, b_mn=True, epilogue=3)
     gemm_case(dev, "square 8192", 8192, 8192, 8192)
 
 

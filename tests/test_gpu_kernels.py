@@ -74,6 +74,31 @@ def test_gemm_accumulate_with_k_slices(m, n, k):
     assert _rel_err(acc, want) < 2e-3
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("epilogue,split_k", [(0, 1), (1, 1), (2, 1), (3, 1), (3, 3)])
+def test_gemm_on_cta_pairs(a_mn, b_mn, epilogue, split_k):
+    """The cta_group::2 kernel on its own: ragged edges (rows 1152 = 4.5 pair tiles, columns 832, K 6208 = 97
+    k-blocks) in every operand layout and epilogue, K slices included, against an fp32 matmul."""
+    torch.manual_seed(5)
+    m, n, k = 1152, 832, 6208
+    a_rows = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    b_rows = torch.randn(n, k, device=_dev(), dtype=torch.bfloat16)
+    a = a_rows.t().contiguous() if a_mn else a_rows
+    b = b_rows.t().contiguous() if b_mn else b_rows
+    want = a_rows.float() @ b_rows.float().t()
+    if epilogue == 0:
+        out = torch.zeros(m, n, device=_dev(), dtype=torch.bfloat16)
+    else:
+        out = torch.randn(m, n, device=_dev(), dtype=torch.float32)
+        if epilogue in (1, 3):
+            want = want + out
+    native.call("ajb_gemm_bf16_pair", a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0),
+                out.stride(0), int(a_mn), int(b_mn), epilogue, split_k, native.stream_ptr())
+    torch.cuda.synchronize()
+    assert native.lib().ajb_check_status() == 0
+    assert _rel_err(out, want) < (5e-3 if epilogue == 0 else 2e-3)
+
+
 def test_gemm_strided_operands():
     """Column slices of wider buffers are passed by leading dimension, not copied."""
     torch.manual_seed(3)
