@@ -35,6 +35,9 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "gemm_pair.h"
+
+#include <cstdlib>
 
 namespace ajb {
 namespace comm {
@@ -44,17 +47,28 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr int kStages = 3;
 constexpr int kABytes = BM * BK * 2;
-constexpr int kBBytes = BN * BK * 2;
-constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kEpiRowPitch = BN * 2 + 16;               // staged output rows, padded against bank conflicts
 constexpr int kEpiBytes = BM * kEpiRowPitch;            // one bf16 output tile, staged for bulk row stores
-constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 512;
+// Two variants of the kernel. Single CTAs: 128 x 256 tiles, A and the whole B tile per stage. CTA pairs (clusters
+// of two, tcgen05 cta_group::2): 256 x 256 tiles, each CTA stages its 128 rows of A and half of the B tile, so a
+// stage is a third smaller and the ring one slot deeper; rows per rank must then be a multiple of 256.
+template <bool PAIR>
+struct Cfg {
+  static constexpr int kStages = PAIR ? 4 : 3;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;
+  static constexpr int kBBytes = kBRows * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  static constexpr int kSmemBytes = kRingBytes + kEpiBytes + 512;
+  static constexpr int kTileRows = PAIR ? 2 * BM : BM;
+};
 constexpr int kMaxRanks = 8;
 constexpr int kGroupM = 16;
 constexpr int kCopyPiece = 32768;                       // bytes per bulk copy
-constexpr int kCopyBufs = (kStages * kStageBytes + kEpiBytes) / kCopyPiece;   // 6 pieces in flight per copy CTA
+constexpr int kCopyBufs = 6;                            // pieces in flight per copy CTA (ring = pipeline + epilogue space)
+static_assert((Cfg<false>::kRingBytes + kEpiBytes) / kCopyPiece >= kCopyBufs, "copy ring does not fit");
+static_assert((Cfg<true>::kRingBytes + kEpiBytes) / kCopyPiece >= kCopyBufs, "copy ring does not fit");
 constexpr int kQueue = 4;                               // depth of the per-CTA tile queue
 
 enum Mode : int { kAllGather = 0, kReduceScatter = 1, kAllReduce = 2, kGatherWeight = 3 };
@@ -307,9 +321,11 @@ __device__ __forceinline__ void sum_slots(const Params& p) {
 }
 
 
-template <bool B_MN>
-__global__ void __launch_bounds__(kThreads, 1)
-comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+template <bool B_MN, bool PAIR>
+__device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p) {
+  using C = Cfg<PAIR>;
+  constexpr int kStages = C::kStages;
+  constexpr int kStageBytes = C::kStageBytes;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   uint8_t* epi_base = smem + kStages * kStageBytes;
@@ -327,9 +343,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // pair variant: the even CTA of a cluster leads (draws tiles, arms the full barriers, issues the products)
+  const uint32_t pair_rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = pair_rank == 0;
   const bool gathers = p.mode == kAllGather || p.mode == kGatherWeight;
-  const bool is_copy_cta = gathers && (int)blockIdx.x < p.copy_ctas;
-  const int tiles_m_local = p.m_local / BM;
+  const bool is_copy_cta = gathers && (int)blockIdx.x < p.copy_ctas;     // copy_ctas is even for pairs: whole clusters copy
+  const int tiles_m_local = p.m_local / C::kTileRows;
   const int tiles_n = (p.n + BN - 1) / BN;
   const int shards = (p.mode == kAllReduce || p.mode == kGatherWeight) ? 1 : p.tp;   // one "shard" of m_local = m rows
   const int num_tiles = tiles_m_local * shards * tiles_n;
@@ -350,12 +369,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);
+      mbar_init(&acc_empty[b], PAIR ? 8 : 4);     // pairs: the leader's barrier collects both CTAs' epilogue warps
     }
     for (int i = 0; i < kCopyBufs; ++i) mbar_init(&copy_bars[i], 1);
     for (int i = 0; i < kQueue; ++i) {
       mbar_init(&q_full[i], 1);
-      mbar_init(&q_empty[i], 5);      // MMA warp + four epilogue warps
+      // consumers of a queue slot: MMA warp + four epilogue warps; pairs: plus the peer's producer and epilogue warps
+      mbar_init(&q_empty[i], PAIR ? 10 : 5);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -363,11 +383,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     prefetch_tensor_map(&map_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(tmem_slot, 2 * BN); tmem_relinquish_pair(); }
+    else      { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();    // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -376,6 +397,19 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     copy_cta_all_gather(p, smem, copy_bars, abort_flag);
     __syncthreads();
   }
+  // shared::cluster addresses of the barriers and the queue that live in the other CTA of the pair
+  const uint32_t full_leader = PAIR ? map_to_cta(smem_u32(&full[0]), 0) : 0u;
+  const uint32_t acc_empty_leader = PAIR ? map_to_cta(smem_u32(&acc_empty[0]), 0) : 0u;
+  const uint32_t q_empty_leader = PAIR ? map_to_cta(smem_u32(&q_empty[0]), 0) : 0u;
+  const uint32_t q_full_peer = PAIR ? map_to_cta(smem_u32(&q_full[0]), 1) : 0u;
+  const uint32_t queue_peer = PAIR ? map_to_cta(smem_u32(&queue->tile[0]), 1) : 0u;
+  const uint32_t empty_peer = PAIR ? map_to_cta(smem_u32(&empty[0]), 1) : 0u;
+  const uint32_t acc_full_peer = PAIR ? map_to_cta(smem_u32(&acc_full[0]), 1) : 0u;
+  // a consumer of queue slot `slot` is done with it
+  auto release_slot = [&](int slot) {
+    if (PAIR) mbar_arrive_cluster(q_empty_leader + (uint32_t)slot * 8u);
+    else mbar_arrive(&q_empty[slot]);
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -386,11 +420,26 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = *abort_flag == 0;
       for (uint32_t qi = 0; ok; ++qi) {
         const int slot = qi % kQueue;
-        if (!mbar_wait(&q_empty[slot], ((qi / kQueue) & 1) ^ 1, abort_flag, p.status, kCommGemm, 5)) { ok = false; break; }
-        const int tile = (int)atomicAdd(p.tile_counter, 1u);
-        queue->tile[slot] = tile < num_tiles ? tile : -1;
-        mbar_arrive(&q_full[slot]);
-        if (tile >= num_tiles) break;
+        int tile;
+        if (leader) {
+          // pairs: half of the slot's consumers arrive from the other CTA, hence the cluster-scope acquire
+          if (!(PAIR ? mbar_wait_cluster(&q_empty[slot], ((qi / kQueue) & 1) ^ 1, abort_flag, p.status, kCommGemm, 5)
+                     : mbar_wait(&q_empty[slot], ((qi / kQueue) & 1) ^ 1, abort_flag, p.status, kCommGemm, 5))) { ok = false; break; }
+          tile = (int)atomicAdd(p.tile_counter, 1u);
+          if (tile >= num_tiles) tile = -1;
+          queue->tile[slot] = tile;
+          if (PAIR) {
+            // the peer works on the same tile: the number goes into its queue too, then its slot is marked full
+            st_shared_cluster_u32(queue_peer + (uint32_t)slot * 4u, (uint32_t)tile);
+            mbar_arrive_cluster(q_full_peer + (uint32_t)slot * 8u);
+          }
+          mbar_arrive(&q_full[slot]);
+        } else {
+          if (!mbar_wait_cluster(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 8)) { ok = false; break; }
+          tile = queue->tile[slot];
+          release_slot(slot);
+        }
+        if (tile < 0) break;
         int shard, tm, tn;
         tile_coords(tile, tiles_m_local, tiles_n, shards, first_shard, p.mode == kReduceScatter, shard, tm, tn);
         if (p.mode == kGatherWeight) {
@@ -411,25 +460,38 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           fence_proxy_async_all();      // copied rows were written through the async proxy of other CTAs
           ready_shard = shard;
         }
-        const int m0 = tm * BM, n0 = tn * BN;
+        const int m0 = tm * C::kTileRows + (int)pair_rank * BM, n0 = tn * BN + (int)pair_rank * C::kBRows;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kCommGemm, 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
-          mbar_arrive_expect_tx(&full[stage], kStageBytes);
           const int k0 = kb * BK;
-          tma_load_2d(sa, &map_a, &full[stage], k0, m0);
-          if (B_MN) {
+          if (PAIR) {
+            // both CTAs' loads complete on the leader's barrier, which the leader arms with the bytes of both
+            if (leader) mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes);
+            const uint32_t bar = full_leader + (uint32_t)stage * 8u;
+            tma_load_2d_pair(sa, &map_a, bar, k0, m0);
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0);
+              for (int j = 0; j < C::kBRows / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), &map_b, bar, n0 + 64 * j, k0);
+            } else {
+              tma_load_2d_pair(sb, &map_b, bar, k0, n0);
+            }
           } else {
-            tma_load_2d(sb, &map_b, &full[stage], k0, n0);
+            mbar_arrive_expect_tx(&full[stage], kStageBytes);
+            tma_load_2d(sa, &map_a, &full[stage], k0, m0);
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &map_b, &full[stage], n0 + 64 * j, k0);
+            } else {
+              tma_load_2d(sb, &map_b, &full[stage], k0, n0);
+            }
           }
           ++issued;
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) {
+      if (!ok && leader) {
         const int pending = min(issued, kStages);
         int s = stage;
         uint32_t ph = phase;
@@ -440,8 +502,8 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       }
     }
-  } else if (warp == 1) {
-    constexpr uint32_t idesc = make_idesc(BM, BN, 1, false, B_MN);
+  } else if (warp == 1 && leader) {
+    constexpr uint32_t idesc = make_idesc(C::kTileRows, BN, 1, false, B_MN);
     // descriptor low words formed once; a stage is one multiply-add away, a k-step a compile-time offset
     const uint32_t a_lo0 = desc_lo_k_major(smem_u32(smem));
     const uint32_t b_lo0 = B_MN ? desc_lo_mn_major(smem_u32(smem) + kABytes, BK * 128) : desc_lo_k_major(smem_u32(smem) + kABytes);
@@ -450,14 +512,15 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool ok = true;
     for (uint32_t qi = 0; ok; ++qi) {
       const int slot = qi % kQueue;
-      if (!mbar_wait(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 6)) break;
+      if (!mbar_wait(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 6)) break;   // filled by this CTA
       const int tile = queue->tile[slot];
       __syncwarp();
-      if (lane == 0) mbar_arrive(&q_empty[slot]);
+      if (lane == 0) release_slot(slot);
       if (tile < 0) break;
       const int buf = qi & 1;
       const uint32_t use = qi >> 1;
-      if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, kCommGemm, 2)) { ok = false; break; }
+      if (!(PAIR ? mbar_wait_cluster(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, kCommGemm, 2)
+                 : mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, kCommGemm, 2))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
       for (int kb = 0; kb < num_kb; ++kb) {
@@ -466,20 +529,38 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (lane == 0) {
           const uint32_t a_lo = a_lo0 + (uint32_t)stage * (uint32_t)(kStageBytes >> 4);
           const uint32_t b_lo = b_lo0 + (uint32_t)stage * (uint32_t)(kStageBytes >> 4);
-          umma_f16(tmem_d, desc_at(a_lo, 0), desc_at(b_lo, 0), idesc, kb != 0 ? 1u : 0u);
+          if (PAIR) {
+            umma_pair_f16(tmem_d, desc_at(a_lo, 0), desc_at(b_lo, 0), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 1; k < BK / UMMA_K; ++k)
-            umma_f16_c<true>(tmem_d, desc_at(a_lo, (uint32_t)k * UMMA_K * 2),
-                             desc_at(b_lo, B_MN ? mn_major_step(k) : (uint32_t)k * UMMA_K * 2), idesc);
-          tc_commit(&empty[stage]);
+            for (int k = 1; k < BK / UMMA_K; ++k)
+              umma_pair_f16_c<true>(tmem_d, desc_at(a_lo, (uint32_t)k * UMMA_K * 2),
+                                    desc_at(b_lo, B_MN ? mn_major_step(k) : (uint32_t)k * UMMA_K * 2), idesc);
+            // the slot is free in both CTAs once these products have read it
+            tc_commit_pair(smem_u32(&empty[stage]));
+            tc_commit_pair(empty_peer + (uint32_t)stage * 8u);
+          } else {
+            umma_f16(tmem_d, desc_at(a_lo, 0), desc_at(b_lo, 0), idesc, kb != 0 ? 1u : 0u);
+#pragma unroll
+            for (int k = 1; k < BK / UMMA_K; ++k)
+              umma_f16_c<true>(tmem_d, desc_at(a_lo, (uint32_t)k * UMMA_K * 2),
+                               desc_at(b_lo, B_MN ? mn_major_step(k) : (uint32_t)k * UMMA_K * 2), idesc);
+            tc_commit(&empty[stage]);
+          }
         }
         __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
-      if (ok && lane == 0) tc_commit(&acc_full[buf]);
+      if (ok && lane == 0) {
+        if (PAIR) {
+          tc_commit_pair(smem_u32(&acc_full[buf]));
+          tc_commit_pair(acc_full_peer + (uint32_t)buf * 8u);
+        } else {
+          tc_commit(&acc_full[buf]);
+        }
+      }
       __syncwarp();
     }
-  } else {
+  } else if (warp >= 2) {
     const int quarter = warp & 3;
     uint8_t* my_row = epi_base + (quarter * 32 + lane) * kEpiRowPitch;    // this lane's staged output row
     bool ok = true;
@@ -490,10 +571,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     unsigned int stored_tiles = 0;   // lane r: tiles this warp stored into rank r's receive buffer
     for (uint32_t qi = 0; ok; ++qi) {
       const int slot = qi % kQueue;
-      if (!mbar_wait(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 7)) break;
+      // pairs: the peer's slot is written and marked full by the leader, hence the cluster-scope acquire
+      if (!(PAIR ? mbar_wait_cluster(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 7)
+                 : mbar_wait(&q_full[slot], (qi / kQueue) & 1, abort_flag, p.status, kCommGemm, 7))) break;
       const int tile = queue->tile[slot];
       __syncwarp();
-      if (lane == 0) mbar_arrive(&q_empty[slot]);
+      if (lane == 0) release_slot(slot);
       if (tile < 0) break;
       const int buf = qi & 1;
       const uint32_t use = qi >> 1;
@@ -523,9 +606,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_before_sync();
       fence_proxy_async_smem();      // the bulk store below reads this row through the async proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(acc_empty_leader + (uint32_t)buf * 8u);
+        else mbar_arrive(&acc_empty[buf]);
+      }
       // one bulk store per row: up to 512 contiguous bytes leave the SM without passing through registers
-      const int row = tm * BM + quarter * 32 + lane;
+      const int row = tm * C::kTileRows + (int)pair_rank * BM + quarter * 32 + lane;
       const int col0 = tn * BN;
       const int bytes = min(BN, p.n - col0) * 2;
       if (p.mode == kAllReduce) {
@@ -559,9 +645,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   tc_fence_before_sync();
   __syncthreads();
+  // pairs: neither CTA frees tensor memory or moves on while the other may still read its shared memory or write
+  // its accumulators (every role of both CTAs has finished, or given up after a bounded wait, before this point)
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
 
   if (p.mode == kReduceScatter || p.mode == kAllReduce) {
@@ -594,6 +684,18 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     }
   }
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  comm_gemm_body<B_MN, false>(map_a, map_b, p);
+}
+
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+comm_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  comm_gemm_body<B_MN, true>(map_a, map_b, p);
 }
 
 }  // namespace comm
@@ -644,7 +746,14 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   p.mode = a.mode; p.m = a.m; p.n = a.n; p.k = a.k; p.tp = a.tp; p.rank = a.rank;
   p.m_local = (a.mode == kAllReduce || a.mode == kGatherWeight) ? a.m : a.m / a.tp;
   const bool gathers = a.mode == kAllGather || a.mode == kGatherWeight;
+  // CTA pairs for the two training modes when every rank's rows split into 256-row tiles (AJB_COMM_PAIR=0: never)
+  static const bool pairs_enabled = [] {
+    const char* v = std::getenv("AJB_COMM_PAIR");
+    return v == nullptr || v[0] != '0';
+  }();
+  const bool pair = pairs_enabled && (a.mode == kAllGather || a.mode == kReduceScatter) && p.m_local % (2 * BM) == 0;
   p.copy_ctas = gathers ? a.copy_ctas : 0;
+  if (pair) p.copy_ctas = (p.copy_ctas + 1) / 2 * 2;      // whole clusters copy
   p.shard_bytes = a.mode == kGatherWeight ? a.shard_elems * 2 : (long long)p.m_local * a.k * 2;
   p.b_offset = a.b_offset_elems * 2;
   p.b_row_bytes = (long long)a.k * 2;
@@ -674,20 +783,31 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   int rc = make_tensor_map_2d(&map_a, a_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, a.k, (uint64_t)a.k * 2, BM, 64);
   if (rc) return rc;
   if (a.b_mn_major) rc = make_tensor_map_2d(&map_b, b_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.k, a.n, a.ldb * 2, BK, 64);
-  else              rc = make_tensor_map_2d(&map_b, b_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.k, a.ldb * 2, BN, 64);
+  else              rc = make_tensor_map_2d(&map_b, b_ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.k, a.ldb * 2,
+                                            pair ? Cfg<true>::kBRows : BN, 64);
   if (rc) return rc;
-  static bool configured[2] = {false, false};
-  const int which = a.b_mn_major ? 1 : 0;
+  static bool configured[4] = {false, false, false, false};
+  const int which = (a.b_mn_major ? 1 : 0) | (pair ? 2 : 0);
   if (!configured[which]) {
-    if (which) AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    else       AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    const int single_bytes = Cfg<false>::kSmemBytes, pair_bytes = Cfg<true>::kSmemBytes;
+    switch (which) {
+      case 0: AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, single_bytes)); break;
+      case 1: AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, single_bytes)); break;
+      case 2: AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_bytes)); break;
+      default: AJB_CUDA_OK(cudaFuncSetAttribute(comm_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_bytes)); break;
+    }
     configured[which] = true;
   }
-  // every CTA of this kernel must be resident at once (copy CTAs feed compute CTAs): one CTA per SM
-  const int grid = sm_count();
+  // every CTA of this kernel must be resident at once (copy CTAs feed compute CTAs): one CTA per SM, and for the
+  // pair variant as many clusters as the device can hold at once
+  const int grid = pair ? 2 * gemm_pair::capacity() : sm_count();
   AJB_REQUIRE(p.copy_ctas < grid && (!gathers || p.copy_ctas >= 1), "comm_gemm: copy CTA count %d is out of range", p.copy_ctas);
-  if (which) comm_gemm_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
-  else       comm_gemm_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
+  switch (which) {
+    case 0: comm_gemm_kernel<false><<<grid, kThreads, Cfg<false>::kSmemBytes, s>>>(map_a, map_b, p); break;
+    case 1: comm_gemm_kernel<true><<<grid, kThreads, Cfg<false>::kSmemBytes, s>>>(map_a, map_b, p); break;
+    case 2: comm_gemm_pair_kernel<false><<<grid, kThreads, Cfg<true>::kSmemBytes, s>>>(map_a, map_b, p); break;
+    default: comm_gemm_pair_kernel<true><<<grid, kThreads, Cfg<true>::kSmemBytes, s>>>(map_a, map_b, p); break;
+  }
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }
