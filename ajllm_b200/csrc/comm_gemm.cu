@@ -70,6 +70,8 @@ constexpr int kCopyBufs = 6;                            // pieces in flight per 
 static_assert((Cfg<false>::kRingBytes + kEpiBytes) / kCopyPiece >= kCopyBufs, "copy ring does not fit");
 static_assert((Cfg<true>::kRingBytes + kEpiBytes) / kCopyPiece >= kCopyBufs, "copy ring does not fit");
 constexpr int kQueue = 4;                               // depth of the per-CTA tile queue
+constexpr int kMaxGroups = 32;                          // arrival groups per shard (all-gather)
+constexpr int kScratchWords = 16 + kMaxRanks * kMaxGroups;   // local scratch: flags, counters, group flags
 
 enum Mode : int { kAllGather = 0, kReduceScatter = 1, kAllReduce = 2, kGatherWeight = 3 };
 
@@ -86,6 +88,12 @@ struct Params {
   const void* stage_ptrs[kMaxRanks];     // each rank's symmetric [m_local, k] staging buffer (peer addresses)
   void* gathered;                        // local [m, k]
   unsigned int* shard_flags;             // local, zeroed by the host before launch, one per shard
+  // all-gather: a shard arrives in up to kMaxGroups groups of `group_pieces` consecutive 32 KB pieces; every copy CTA
+  // adds one to group_flags[shard * kMaxGroups + g] when its pieces of group g are in local memory, so the tiles of
+  // a remote shard start as soon as their own rows are there instead of after the whole shard
+  unsigned int* group_flags;
+  int group_pieces;                      // pieces per group (a multiple of copy_ctas)
+  int groups;                            // groups per shard
   // reduce-scatter
   void* recv_ptrs[kMaxRanks];            // each rank's symmetric [tp, m_local, n] receive buffer (all-reduce: m_local = m)
   unsigned int* counter_ptrs[kMaxRanks]; // each rank's symmetric arrival counters, one per source rank
@@ -178,7 +186,7 @@ __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, u
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all_but_latest() { asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all_but_two() { asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); }
 
 // One copy CTA's share of the all-gather: thread 0 streams 32 KB pieces through a shared-memory ring.
 __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* bars, volatile uint32_t* abort_flag) {
@@ -198,8 +206,18 @@ __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* ba
     if (!ok) break;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(p.stage_ptrs[shard]);
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.gathered) + (long long)shard * shard_bytes;
-    // pieces cta, cta + n_copy, ... of this shard
+    // pieces cta, cta + n_copy, ... of this shard; this CTA's j-th piece lies in group j / per_group
     long long next_load = cta, next_store = cta;
+    const int per_group = p.group_pieces / n_copy;      // pieces of one CTA per group
+    int stored = 0, announced = 0;                      // this CTA's stores issued / groups announced (this shard)
+    auto announce_through = [&](int complete_stores) {  // the first `complete_stores` stores are in global memory
+      const int upto = complete_stores / per_group;     // groups wholly covered by them
+      if (upto <= announced) return;
+      fence_proxy_async_all();
+      __threadfence();
+      for (; announced < upto && announced < p.groups; ++announced)
+        red_release_gpu_add(p.group_flags + shard * kMaxGroups + announced, 1u);
+    };
     auto piece_bytes = [&](long long piece) -> uint32_t {
       const long long off = piece * kCopyPiece;
       return (uint32_t)min((long long)kCopyPiece, shard_bytes - off);
@@ -219,10 +237,19 @@ __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* ba
       bulk_wait_read_all();      // the ring slot may be refilled once the store has read it
       ++drained;
       next_store += n_copy;
+      ++stored;
+      if (p.mode == kAllGather && stored >= 2 && (stored - 2) % per_group == 0 && stored - 2 > 0) {
+        bulk_wait_all_but_two(); // all but the two youngest stores have landed
+        announce_through(stored - 2);
+      }
     }
     bulk_wait_all();             // stores of this shard are complete in global memory
     fence_proxy_async_all();
     __threadfence();
+    if (p.mode == kAllGather) {
+      // the remaining groups, those in which this CTA had no piece included
+      for (; announced < p.groups; ++announced) red_release_gpu_add(p.group_flags + shard * kMaxGroups + announced, 1u);
+    }
     red_release_gpu_add(p.shard_flags + shard, 1u);
   }
   if (!ok) {
@@ -416,6 +443,7 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0, ready_shard = p.rank;
+      uint32_t ready_groups = 0;        // all-gather: groups of `ready_shard` known to have arrived
       uint32_t ready_mask = 0;          // gather-weight: slices known to have arrived
       bool ok = *abort_flag == 0;
       for (uint32_t qi = 0; ok; ++qi) {
@@ -455,12 +483,24 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
           }
           if (!ok) break;
         }
-        if (p.mode == kAllGather && shard != ready_shard) {
-          if (!wait_ge(p.shard_flags + shard, (unsigned)p.copy_ctas, false, abort_flag, p.status, 10)) { ok = false; break; }
-          fence_proxy_async_all();      // copied rows were written through the async proxy of other CTAs
-          ready_shard = shard;
-        }
         const int m0 = tm * C::kTileRows + (int)pair_rank * BM, n0 = tn * BN + (int)pair_rank * C::kBRows;
+        if (p.mode == kAllGather && shard != p.rank) {
+          if (shard != ready_shard) { ready_shard = shard; ready_groups = 0; }
+          // groups that hold this CTA's 128 rows of A
+          const long long row_bytes = (long long)p.k * 2;
+          const long long lo = (long long)(m0 - shard * p.m_local) * row_bytes;
+          const long long hi = lo + (long long)BM * row_bytes - 1;
+          const long long group_bytes = (long long)p.group_pieces * kCopyPiece;
+          bool waited = false;
+          for (int g = (int)(lo / group_bytes); g <= (int)(hi / group_bytes) && ok; ++g) {
+            if ((ready_groups >> g) & 1u) continue;
+            if (!wait_ge(p.group_flags + shard * kMaxGroups + g, (unsigned)p.copy_ctas, false, abort_flag, p.status, 10)) { ok = false; break; }
+            ready_groups |= 1u << g;
+            waited = true;
+          }
+          if (!ok) break;
+          if (waited) fence_proxy_async_all();      // copied rows were written through the async proxy of other CTAs
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kCommGemm, 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * kStageBytes;
@@ -714,7 +754,7 @@ struct AjbCommArgs {
   unsigned int* counter_ptrs[8];
   unsigned int* ready_ptrs[8];
   unsigned int* done_ptrs[8];
-  unsigned int* shard_flags;     // local scratch (>= 8 words) + 1 word CTA counter at index 8
+  unsigned int* shard_flags;     // local scratch of 272 words (16 + 8 ranks x 32 groups): flags, counters, group flags
   unsigned int expected_count;
   unsigned int epoch;
   int a_rows;                    // all-reduce: rows of `a` that exist (<= m; the tiles above them read zeros); 0 means m
@@ -768,12 +808,24 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   p.shard_flags = a.shard_flags;
   p.local_cta_counter = a.shard_flags + 8;
   p.tile_counter = a.shard_flags + 9;
+  p.group_flags = a.shard_flags + 16;
+  p.group_pieces = p.copy_ctas > 0 ? p.copy_ctas : 1;
+  p.groups = 1;
+  if (a.mode == kAllGather) {
+    // groups of at least four pieces per copy CTA (one fence per group), at most kMaxGroups of them per shard
+    const long long pieces = (p.shard_bytes + kCopyPiece - 1) / kCopyPiece;
+    const long long per_cta = (pieces + p.copy_ctas - 1) / p.copy_ctas;
+    long long per_group = (per_cta + kMaxGroups - 1) / kMaxGroups;
+    if (per_group < 4) per_group = 4;
+    p.group_pieces = (int)(per_group * p.copy_ctas);
+    p.groups = (int)((per_cta + per_group - 1) / per_group);
+  }
   p.expected_count = a.expected_count;
   p.out_local = a.out;
   p.ldc = a.ldc;
   p.epoch = a.epoch;
   p.status = device_status_buffer();
-  AJB_CUDA_OK(cudaMemsetAsync(a.shard_flags, 0, 16 * sizeof(unsigned int), s));
+  AJB_CUDA_OK(cudaMemsetAsync(a.shard_flags, 0, kScratchWords * sizeof(unsigned int), s));
 
   const void* a_ptr = a.mode == kAllGather ? a.gathered : a.a;
   const void* b_ptr = a.mode == kGatherWeight ? static_cast<const void*>(static_cast<const uint8_t*>(a.gathered) + a.b_offset_elems * 2) : a.b;

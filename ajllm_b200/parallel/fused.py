@@ -63,7 +63,7 @@ class FusedTensorParallel:
         self._flags = symm_mem.empty(64, dtype=torch.int32, device=device)
         self._flags.zero_()
         self._flag_ptrs = list(symm_mem.rendezvous(self._flags, group).buffer_ptrs)
-        self._local = torch.zeros(16, dtype=torch.int32, device=device)
+        self._local = torch.zeros(272, dtype=torch.int32, device=device)   # flags, counters, per-group arrival flags
         torch.cuda.synchronize(device)
         dist.barrier(group)
         fn = native.lib().ajb_comm_gemm

@@ -28,7 +28,7 @@ class Emulated:
         self.device = device
         # one flag array per "rank": [0:8] ready, [8:16] done, [16:24] arrival counters
         self.flags = [torch.zeros(64, dtype=torch.int32, device=device) for _ in range(TP)]
-        self.local = torch.zeros(16, dtype=torch.int32, device=device)
+        self.local = torch.zeros(272, dtype=torch.int32, device=device)
         self.epoch = 0
         self.expected = 0
         fn = native.lib().ajb_comm_gemm
