@@ -107,6 +107,7 @@ def main() -> None:
     run = lambda: em.launch(MODE_ALL_GATHER, m, n, k, out, b=w, gathered=gathered, stage=stage)
     t = timeit(run)
     print(f"all-gather -> GEMM   m{m} n{n} k{k}: {t * 1e3:8.1f} us {flops / t / 1e9:7.1f} TF  rel.err {rel(out, x.float() @ w.float().t()):.1e}", flush=True)
+    assert torch.equal(gathered, x), "every shard of the gathered activations must be in place after the kernel"
 
     # GEMM -> reduce-scatter: rank 0 multiplies its K slice; the peer's partial for rank 0's rows is placed by the host
     x1 = (torch.randn(m, k, device=dev) * 0.5).to(bf)       # the peer's activations (its K slice)

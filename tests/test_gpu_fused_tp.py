@@ -73,6 +73,11 @@ def _worker(rank: int, world: int, port: int, rows_local: int, results):
         ws = (torch.randn(n_local, d_model, device=device) * 0.05).to(torch.bfloat16)
         first = [fused.all_gather_gemm(xs, ws, False, n_local, d_model)[1].clone() for _ in range(2)]
         errors["repeat/ag"] = 0.0 if torch.equal(first[0], first[1]) else 1.0
+        # the kernel also leaves every rank's rows (its own included) in the gathered activations
+        got_rows = fused.all_gather_gemm(xs, ws, False, n_local, d_model)[0]
+        want_rows = torch.empty_like(got_rows)
+        dist.all_gather_into_tensor(want_rows, xs)
+        errors["ag/gathered"] = 0.0 if torch.equal(got_rows, want_rows) else 1.0
         xa = (torch.randn(rows_local * world, n_local, device=device) * 0.5).to(torch.bfloat16)
         wr = (torch.randn(d_model, n_local, device=device) * 0.05).to(torch.bfloat16)
         second = [fused.gemm_reduce_scatter(xa, wr, False, d_model, n_local).clone() for _ in range(2)]
