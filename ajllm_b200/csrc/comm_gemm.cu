@@ -786,12 +786,12 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   p.mode = a.mode; p.m = a.m; p.n = a.n; p.k = a.k; p.tp = a.tp; p.rank = a.rank;
   p.m_local = (a.mode == kAllReduce || a.mode == kGatherWeight) ? a.m : a.m / a.tp;
   const bool gathers = a.mode == kAllGather || a.mode == kGatherWeight;
-  // CTA pairs for the two training modes when every rank's rows split into 256-row tiles (AJB_COMM_PAIR=0: never)
+  // CTA pairs for the three training modes when every rank's rows split into 256-row tiles (AJB_COMM_PAIR=0: never)
   static const bool pairs_enabled = [] {
     const char* v = std::getenv("AJB_COMM_PAIR");
     return v == nullptr || v[0] != '0';
   }();
-  const bool pair = pairs_enabled && (a.mode == kAllGather || a.mode == kReduceScatter) && p.m_local % (2 * BM) == 0;
+  const bool pair = pairs_enabled && a.mode != kAllReduce && p.m_local % (2 * BM) == 0;   // decoding has too few rows
   p.copy_ctas = gathers ? a.copy_ctas : 0;
   if (pair) p.copy_ctas = (p.copy_ctas + 1) / 2 * 2;      // whole clusters copy
   p.shard_bytes = a.mode == kGatherWeight ? a.shard_elems * 2 : (long long)p.m_local * a.k * 2;
