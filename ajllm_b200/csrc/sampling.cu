@@ -61,12 +61,27 @@ struct RowStats {
   int argmax;
 };
 
-__device__ RowStats row_stats(const float* __restrict__ row, int vocab, float inv_t, float* red, int* red_i) {
+// Greedy rows (`need_sum` false) only need the argmax, i.e. one pass over the row. Rows that start on a 16-byte
+// boundary with a vocabulary that is a multiple of 4 are read as float4.
+__device__ RowStats row_stats(const float* __restrict__ row, int vocab, float inv_t, bool need_sum, float* red, int* red_i) {
   float mx = -INFINITY;
   int arg = 0;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float x = row[i];
-    if (x > mx) { mx = x; arg = i; }
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0 && (vocab & 3) == 0;
+  if (vec) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < (vocab >> 2); i += blockDim.x) {
+      const float4 v = row4[i];
+      // increasing index and a strict comparison keep the smallest index among equal values
+      if (v.x > mx) { mx = v.x; arg = 4 * i; }
+      if (v.y > mx) { mx = v.y; arg = 4 * i + 1; }
+      if (v.z > mx) { mx = v.z; arg = 4 * i + 2; }
+      if (v.w > mx) { mx = v.w; arg = 4 * i + 3; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float x = row[i];
+      if (x > mx) { mx = x; arg = i; }
+    }
   }
   const float gmax = block_max(mx, red);
   // smallest index among the maxima
@@ -78,12 +93,24 @@ __device__ RowStats row_stats(const float* __restrict__ row, int vocab, float in
   __syncthreads();
   int best = 0x7fffffff;
   for (int w = 0; w < (int)(blockDim.x >> 5); ++w) best = min(best, red_i[w]);
-  float s = 0.0f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += __expf((row[i] - gmax) * inv_t);
   RowStats out;
   out.max_logit = gmax;
-  out.sum_exp = block_sum(s, red);
   out.argmax = best;
+  out.sum_exp = 1.0f;
+  if (need_sum) {
+    float s = 0.0f;
+    if (vec) {
+      const float4* row4 = reinterpret_cast<const float4*>(row);
+      for (int i = threadIdx.x; i < (vocab >> 2); i += blockDim.x) {
+        const float4 v = row4[i];
+        s += __expf((v.x - gmax) * inv_t) + __expf((v.y - gmax) * inv_t) + __expf((v.z - gmax) * inv_t) +
+             __expf((v.w - gmax) * inv_t);
+      }
+    } else {
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += __expf((row[i] - gmax) * inv_t);
+    }
+    out.sum_exp = block_sum(s, red);
+  }
   return out;
 }
 
@@ -145,7 +172,7 @@ sample_rows_kernel(const float* __restrict__ logits, long long row_pitch, int vo
   const float* row = logits + (size_t)r * row_pitch;
   const float temp = temperature[r];
   const float inv_t = temp > 0.0f ? 1.0f / temp : 1.0f;
-  const RowStats st = row_stats(row, vocab, inv_t, red, red_i);
+  const RowStats st = row_stats(row, vocab, inv_t, temp > 0.0f, red, red_i);
   if (temp <= 0.0f) {
     if (threadIdx.x == 0) out_tokens[r] = st.argmax;
     return;
@@ -200,14 +227,14 @@ spec_verify_kernel(const float* __restrict__ target_logits, const float* __restr
   int accepted = 0;
   int next_token = -1;
   for (int i = 0; i < k; ++i) {
-    const RowStats ts = row_stats(trow + (size_t)i * vocab, vocab, inv_t, red, red_i);
+    const RowStats ts = row_stats(trow + (size_t)i * vocab, vocab, inv_t, temp > 0.0f, red, red_i);
     const int d = tokens[i];
     if (temp <= 0.0f) {
       if (d == ts.argmax) { ++accepted; continue; }
       next_token = ts.argmax;
       break;
     }
-    const RowStats ds = row_stats(drow + (size_t)i * vocab, vocab, inv_t, red, red_i);
+    const RowStats ds = row_stats(drow + (size_t)i * vocab, vocab, inv_t, true, red, red_i);
     const float* tr = trow + (size_t)i * vocab;
     const float* dr = drow + (size_t)i * vocab;
     const float p = __expf((tr[d] - ts.max_logit) * inv_t) / ts.sum_exp;
@@ -233,7 +260,7 @@ spec_verify_kernel(const float* __restrict__ target_logits, const float* __restr
   }
   if (next_token < 0) {   // every draft token accepted: bonus token from the last target row
     const float* tr = trow + (size_t)k * vocab;
-    const RowStats ts = row_stats(tr, vocab, inv_t, red, red_i);
+    const RowStats ts = row_stats(tr, vocab, inv_t, temp > 0.0f, red, red_i);
     if (temp <= 0.0f) {
       next_token = ts.argmax;
     } else {
