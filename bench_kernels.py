@@ -3,6 +3,7 @@ model, the attention kernels, the fused norm kernels, and the tensor-pipe probe.
 
     python bench_kernels.py                      # everything, full-size shapes
     python bench_kernels.py --case flash --small # a small case (for a profiler capture)
+    python bench_kernels.py --case decode        # decoding GEMMs (few rows) against cuBLAS, GB/s of weights
     python bench_kernels.py --case mma           # cycles per tcgen05.mma by shape / operand source
 
 Timing: CUDA events around 10 launches after 3 warm-up launches; operands are larger than L2 for the GEMM
@@ -117,9 +118,36 @@ def run_mma_probe(dev) -> None:
                   f"{per:6.1f} cycles ({100 * (n / 2) / per:5.1f} % of the pipe rate)", flush=True)
 
 
+def run_decode_gemm(dev, small: bool) -> None:
+    """Decoding GEMMs of the 8B block: few activation rows, weights streamed once per call (L2 flushed in between by a
+    256 MB memset whose own time is subtracted); bytes = the weight matrix."""
+    shapes = ((6144, 4096),) if small else ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    base = timeit(lambda: flush.zero_(), iters=20)
+    with torch.no_grad():
+        for rows in ((64,) if small else (16, 64, 128)):
+            for n, k in shapes:
+                x = torch.randn(rows, k, device=dev).to(torch.bfloat16)
+                w = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+
+                def ours():
+                    flush.zero_()
+                    ops.linear(x, w)
+
+                def library():
+                    flush.zero_()
+                    torch.matmul(x, w.t())
+
+                t_ours, t_lib = timeit(ours, iters=20) - base, timeit(library, iters=20) - base
+                gb = n * k * 2 / 1e6
+                print(f"decode rows {rows:3d} w [{n} x {k}]: ours {t_ours * 1e3:7.1f} us {gb / t_ours:6.0f} GB/s | "
+                      f"cuBLAS {t_lib * 1e3:7.1f} us {gb / t_lib:6.0f} GB/s", flush=True)
+                del w
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--case", default="all", choices=["all", "gemm", "flash", "flash64", "norm", "mma"])
+    ap.add_argument("--case", default="all", choices=["all", "gemm", "decode", "flash", "flash64", "norm", "mma"])
     ap.add_argument("--small", action="store_true", help="one small shape per case (a few hundred MB on the device)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -128,6 +156,8 @@ def main() -> None:
     torch.manual_seed(0)
     if args.case in ("all", "gemm"):
         run_gemm(dev, args.small)
+    if args.case in ("all", "decode"):
+        run_decode_gemm(dev, args.small)
     if args.case in ("all", "flash"):
         run_flash(dev, args.small)
     if args.case in ("all", "flash64"):
