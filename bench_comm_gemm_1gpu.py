@@ -7,6 +7,8 @@ free, not how well it hides a real one (that is `bench.py --gpus N` and tests/te
 
     python bench_comm_gemm_1gpu.py            # all modes, check + time
     python bench_comm_gemm_1gpu.py --small    # smaller shapes for a profiler capture
+    python bench_comm_gemm_1gpu.py --tp 8     # rank 0 of an 8-rank group: shard order, per-shard arrival groups and
+                                              # per-destination credits of the all-gather and reduce-scatter modes
 """
 
 from __future__ import annotations
@@ -20,7 +22,7 @@ from ajllm_b200.ops import native
 from ajllm_b200.parallel.fused import (MODE_ALL_GATHER, MODE_ALL_REDUCE, MODE_GATHER_WEIGHT, MODE_REDUCE_SCATTER,
                                        _CommArgs)
 
-TP, RANK = 2, 0
+TP, RANK = 2, 0          # --tp 4 / 8 emulate rank 0 of a larger group (all-gather and reduce-scatter modes)
 
 
 class Emulated:
@@ -40,10 +42,10 @@ class Emulated:
                tiles_for_count=0, a_rows=0, shard_elems=0, b_offset=0):
         self.epoch += 1
         self.expected += tiles_for_count * 4
-        # what the absent peer would have written into rank 0's words
-        self.flags[0][1] = self.epoch            # ready[1]
-        self.flags[0][8 + 1] = self.epoch        # done[1]
-        self.flags[0][16 + 1] = self.expected    # arrivals from rank 1
+        # what the absent peers would have written into rank 0's words
+        self.flags[0][1:TP] = self.epoch                 # ready[r]
+        self.flags[0][8 + 1:8 + TP] = self.epoch         # done[r]
+        self.flags[0][16 + 1:16 + TP] = self.expected    # arrivals from rank r
         args = _CommArgs()
         args.mode, args.m, args.n, args.k = mode, m, n, k
         args.tp, args.rank, args.b_mn_major, args.copy_ctas = TP, RANK, int(b_mn), 20
@@ -88,7 +90,10 @@ def rel(a, b):
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--tp", type=int, default=2, choices=[2, 4, 8], help="size of the emulated group (rank 0 runs)")
     args = ap.parse_args()
+    global TP
+    TP = args.tp
     dev = torch.device("cuda")
     torch.manual_seed(0)
     em = Emulated(dev)
@@ -100,7 +105,7 @@ def main() -> None:
     flops = 2 * m * n * k
 
     # all-gather -> GEMM: rank 0 owns rows [0, m_local), the "peer" staging buffer holds the other half
-    stage = [x[:m_local].contiguous(), x[m_local:].contiguous()]
+    stage = [x[r * m_local:(r + 1) * m_local].contiguous() for r in range(TP)]
     gathered = torch.zeros(m, k, device=dev, dtype=bf)
     gathered[:m_local].copy_(stage[0])
     out = torch.empty(m, n, device=dev, dtype=bf)
@@ -113,13 +118,19 @@ def main() -> None:
     x1 = (torch.randn(m, k, device=dev) * 0.5).to(bf)       # the peer's activations (its K slice)
     w1 = (torch.randn(n, k, device=dev) * 0.05).to(bf)
     recv = [torch.zeros(TP, m_local, n, device=dev, dtype=bf) for _ in range(TP)]
-    recv[0][1].copy_((x1[:m_local].float() @ w1.float().t()).to(bf))
+    peer_partial = x1[:m_local].float() @ w1.float().t()
+    for r in range(1, TP):
+        recv[0][r].copy_((peer_partial * (0.5 + 0.25 * r)).to(bf))
     out_rs = torch.empty(m_local, n, device=dev, dtype=bf)
     tiles = (m_local // 128) * ((n + 255) // 256)
     run = lambda: em.launch(MODE_REDUCE_SCATTER, m, n, k, out_rs, b=w, a=x, recv=recv, tiles_for_count=tiles)
     t = timeit(run)
-    want = x[:m_local].float() @ w.float().t() + recv[0][1].float()
+    want = x[:m_local].float() @ w.float().t() + sum(recv[0][r].float() for r in range(1, TP))
     print(f"GEMM -> reduce-scatter m{m} n{n} k{k}: {t * 1e3:8.1f} us {flops / t / 1e9:7.1f} TF  rel.err {rel(out_rs, want):.1e}", flush=True)
+
+    if TP != 2:      # the two remaining modes are emulated for a group of two only
+        print("kernel status", native.lib().ajb_check_status())
+        return
 
     # GEMM -> all-reduce (decoding rows)
     rows = 128
