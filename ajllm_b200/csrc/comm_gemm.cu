@@ -8,16 +8,22 @@
 // Both are one persistent kernel per rank built on the same tcgen05 main loop as gemm_bf16.cu
 // (TMA ring -> tcgen05.mma -> TMEM -> epilogue warps).
 //
-// ag_gemm: a few "copy" CTAs pull every peer's [M/tp, K] shard out of that peer's symmetric staging
-// buffer with bulk asynchronous copies (peer global -> shared -> local global; no multicast) and
-// publish one flag per shard; the GEMM CTAs walk the output tiles shard by shard, starting with the
-// shard that is already local, and their TMA producer waits for a shard's flag before touching it,
-// so each remote byte crosses NVLink once and the transfer hides behind the tiles of earlier shards.
+// The three training modes run on CTA pairs (clusters of two, tcgen05 cta_group::2, 256 x 256 tiles) whenever a
+// rank's rows split into 256-row tiles: the even CTA of a pair draws the tiles and issues the products, both CTAs
+// load, drain and store their 128 rows. Decoding (gemm_ar) and odd row counts use single CTAs on 128 x 256 tiles.
 //
-// gemm_rs: tiles are visited so that the rows owned by the other ranks come first; the epilogue stores
-// each bf16 partial tile straight into the owning rank's symmetric receive buffer (slot = this rank)
-// and bumps a counter there; after its last tile every CTA waits until all partials of its own rows
-// have arrived and sums them in fp32 into the local output.
+// ag_gemm: a few "copy" CTAs pull every peer's [M/tp, K] shard out of that peer's symmetric staging
+// buffer with bulk asynchronous copies (peer global -> shared -> local global; every CTA fetches its own
+// bytes) and publish a flag per group of pieces of a shard; the GEMM CTAs walk the output tiles shard by
+// shard, starting with the shard that is already local, and their TMA producer waits for the groups that
+// hold a tile's rows before touching them, so each remote byte crosses NVLink once and the transfer hides
+// behind the tiles of earlier rows.
+//
+// gemm_rs: consecutive tiles rotate over the shards (the stores to the peers are spread over the whole
+// kernel); the epilogue stores each bf16 partial tile straight into the owning rank's symmetric receive
+// buffer (slot = this rank); every epilogue warp credits the tiles it stored to their owners with one
+// release at the end; after its last tile every CTA waits until all partials of its own rows have arrived
+// and sums them in fp32 into the local output.
 //
 // gemm_ar (decoding, where M is a few hundred rows at most): the same epilogue stores each partial tile
 // into every rank's receive buffer (slot = this rank), and the closing reduction sums all tp slots over
