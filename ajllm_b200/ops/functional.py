@@ -186,6 +186,12 @@ def linear_skinny(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return out
 
 
+# Decoding GEMMs with few 128-row weight strips run as one cluster of CTAs per strip that sums its K slices through
+# distributed shared memory (csrc/gemm_decode_cluster.cu); AJB_DECODE_CLUSTER=0 keeps them on the split-K kernel pair.
+DECODE_CLUSTER_GEMM = os.environ.get("AJB_DECODE_CLUSTER", "1") != "0"
+_CLUSTER_SLICES: dict = {}      # (n, k) -> CTAs per weight strip that fit on the device at once, 0 = none
+
+
 def _linear_decode(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``x2 @ weight.T`` for at most 128 rows as ``(weight @ x2.T).T``: weight rows fill the 128-row side of the
     tensor-core tile, ``n / 128`` tiles times a few K slices stream the weights, partial products are tiny."""
@@ -193,6 +199,16 @@ def _linear_decode(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     n = weight.shape[0]
     tiles = (n + 127) // 128
     k_blocks = (k + 63) // 64
+    if DECODE_CLUSTER_GEMM:
+        # few 128-row strips: a cluster of CTAs per strip, K slices summed through distributed shared memory
+        slices = _CLUSTER_SLICES.get((n, k))
+        if slices is None:
+            slices = _CLUSTER_SLICES[(n, k)] = int(native.lib().ajb_gemm_decode_cluster_slices(n, k))
+        if slices >= 2:
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=x2.device)
+            native.call("ajb_gemm_bf16_decode_cluster", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+                        x2.stride(0), weight.stride(0), out.stride(0), slices, native.stream_ptr())
+            return out
     want = max(1, min(k_blocks // 4, (2 * 148 + tiles - 1) // tiles))      # about two CTAs' worth of work per SM
     per = (k_blocks + want - 1) // want
     split = (k_blocks + per - 1) // per

@@ -31,6 +31,8 @@ _SIGNATURES: dict[str, list] = {
     "ajb_gemm_bf16_pair": [c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long,
                            c_int, c_int, c_int, c_int, c_void],
     "ajb_gemm_pair_capacity": [],
+    "ajb_gemm_decode_cluster_slices": [c_int, c_int],
+    "ajb_gemm_bf16_decode_cluster": [c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_void],
     "ajb_gemm_bf16_batched": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_long, c_long,
                               c_long, c_int, c_int, c_int, c_void, c_int, c_void],
     "ajb_gemm_bf16_splitk": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_int, c_void],
@@ -118,7 +120,7 @@ class PeerTimeout(RuntimeError):
     def __init__(self, code: int) -> None:
         self.code, self.kernel_id, self.stage = code, (code & 0xFF) - 1, code >> 8
         names = {0: "gemm", 1: "flash forward", 2: "flash backward (dK/dV)", 3: "flash backward (dQ)", 4: "tensor-parallel gemm",
-                 5: "paged attention", 6: "fp8 gemm", 7: "expert exchange", 8: "flash backward (fused)", 9: "gradient reduce-scatter", 10: "gemm (CTA pairs)"}
+                 5: "paged attention", 6: "fp8 gemm", 7: "expert exchange", 8: "flash backward (fused)", 9: "gradient reduce-scatter", 10: "gemm (CTA pairs)", 11: "decoding gemm (cluster)"}
         super().__init__(f"kernel '{names.get(self.kernel_id, self.kernel_id)}' stopped waiting at stage {self.stage} "
                          f"(status word {code:#x}); its outputs are incomplete")
 

@@ -272,6 +272,24 @@ def test_batched_gemm_with_row_counts():
     assert _rel_err(wg.grad, torch.einsum("ern,erk->enk", g.float(), x.float())) < 5e-3
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 6144, 4096), (64, 4096, 14336), (128, 4096, 4096),
+                                   (37, 1000, 4104), (128, 6144, 520)])
+def test_decoding_gemm_with_cluster_reduction(m, n, k):
+    """Few rows, few 128-row weight strips: one cluster of CTAs per strip, K slices summed through distributed shared
+    memory (ragged n and k included), against an fp32 matmul; called twice in a row."""
+    from ajllm_b200.ops.functional import _linear_decode
+
+    torch.manual_seed(19)
+    x = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    w = (torch.randn(n, k, device=_dev()) * 0.05).to(torch.bfloat16)
+    with torch.no_grad():
+        for _ in range(2):
+            got = _linear_decode(x, w)
+    torch.cuda.synchronize()
+    assert native.lib().ajb_check_status() == 0
+    assert _rel_err(got, x.float() @ w.float().t()) < 5e-3
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (128, 6144, 4096), (256, 4096, 14336), (40, 1000, 264)])
 def test_split_k_linear_for_few_rows(m, n, k):
     from ajllm_b200.ops.functional import linear_skinny
