@@ -20,9 +20,13 @@ int ajb_sumsq_f32(const void* x, long long n, void* scratch, void* out, void* st
  * budget): the scratch is a 4 KB array built into the library instead of a caller buffer. This entry
  * point exists only in this library; the reference project has nothing like it.
  *   - allocates nothing, on the host or on the device;
- *   - accepts 0 <= n <= ajb_sumsq_f32_static_max_elements() and fails with a message otherwise;
+ *   - accepts 0 <= n <= ajb_sumsq_f32_static_max_elements() and fails with a message otherwise; with n == 0 the
+ *     input pointer may be null and out[0] becomes 0;
+ *   - `stream` must belong to the device that is current when the call is made (the scratch address is looked
+ *     up for the current device);
  *   - the first call on each device looks up the array's device address: make that call before any
- *     stream capture starts on that device;
+ *     stream capture starts on that device; concurrent first calls from several host threads are harmless
+ *     (each stores the same address);
  *   - all calls share the array: do not let two of them overlap on the GPU. */
 long long ajb_sumsq_f32_static_max_elements(void);
 int ajb_sumsq_f32_static(const void* x, long long n, void* out, void* stream);

@@ -46,7 +46,7 @@ struct DeviceStatus {
   unsigned int detail1;
 };
 DeviceStatus* device_status_buffer();   // kNumKernelIds entries, zero-initialised, per device
-int check_device_status(int kernel_id); // host: reads (synchronising on the stream's device) and clears
+int check_device_status_all();          // host: first non-zero status word of the current device (0 = none), cleared once read
 
 // Encodes a 2-D bf16/fp8/fp32 row-major tensor [rows, cols] (row pitch in bytes) for TMA with a
 // 128-byte swizzle. box_cols * elem_bytes must be <= 128.

@@ -646,7 +646,9 @@ static float* g_sumsq_static_address[16] = {nullptr};
 extern "C" long long ajb_sumsq_f32_static_max_elements() { return kSumsqStaticMaxElements; }
 
 extern "C" int ajb_sumsq_f32_static(const void* x, long long n, void* out, void* stream) {
-  AJB_REQUIRE(x != nullptr && out != nullptr, "sumsq_static: input and output pointers are required");
+  AJB_REQUIRE(out != nullptr, "sumsq_static: the output pointer is required");
+  // an empty input may come with a null pointer (an empty tensor has none): the kernels then read nothing and write 0
+  AJB_REQUIRE(x != nullptr || n == 0, "sumsq_static: the input pointer is required when n > 0");
   AJB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, "sumsq_static: input must be 16-byte aligned");
   AJB_REQUIRE(n >= 0 && n <= kSumsqStaticMaxElements,
               "sumsq_static: %lld elements is outside the supported range [0, %lld]; use ajb_sumsq_f32 with a "
@@ -654,6 +656,8 @@ extern "C" int ajb_sumsq_f32_static(const void* x, long long n, void* out, void*
   int device = -1;
   AJB_CUDA_OK(cudaGetDevice(&device));
   AJB_REQUIRE(device >= 0 && device < 16, "sumsq_static: device index %d is not supported", device);
+  // The address belongs to the current device: `stream` must be a stream of that device. Two host threads making
+  // the first call for one device at the same time both look the address up and store the same value.
   if (g_sumsq_static_address[device] == nullptr) {
     float* address = nullptr;
     AJB_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_sumsq_static_partials));

@@ -39,16 +39,19 @@ DeviceStatus* device_status_buffer() {
   return g_status[dev];
 }
 
-int check_device_status(int kernel_id) {
+// First non-zero status word of this device (0 = none), cleared once read. One copy covers every kernel's word, so a
+// caller that has just synchronised (a serving step after its token read-back) pays a few microseconds.
+int check_device_status_all() {
   DeviceStatus* buf = device_status_buffer();
   if (buf == nullptr) return 0;
-  DeviceStatus host;
-  if (cudaMemcpy(&host, buf + kernel_id, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (host.code != 0) {
-    set_error("kernel %d gave up waiting (stage %u, block %u, detail %u/%u)", kernel_id, host.code >> 8, host.block,
-              host.detail0, host.detail1);
-    cudaMemset(buf + kernel_id, 0, sizeof(host));
-    return (int)host.code;
+  DeviceStatus host[kNumKernelIds];
+  if (cudaMemcpy(host, buf, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  for (int k = 0; k < kNumKernelIds; ++k) {
+    if (host[k].code == 0) continue;
+    set_error("kernel %d gave up waiting (stage %u, block %u, detail %u/%u)", k, host[k].code >> 8, host[k].block,
+              host[k].detail0, host[k].detail1);
+    cudaMemset(buf + k, 0, sizeof(DeviceStatus));
+    return (int)host[k].code;
   }
   return 0;
 }
@@ -143,9 +146,5 @@ extern "C" int ajb_check_status() {
     ajb::set_error("device synchronize failed: %s", cudaGetErrorString(cudaGetLastError()));
     return -1;
   }
-  for (int k = 0; k < ajb::kNumKernelIds; ++k) {
-    int code = ajb::check_device_status(k);
-    if (code != 0) return code;
-  }
-  return 0;
+  return ajb::check_device_status_all();
 }

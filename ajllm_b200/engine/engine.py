@@ -171,8 +171,13 @@ class LLMEngine:
         prefill = [item for item in plan if item.is_prefill]
         decode = [item for item in plan if not item.is_prefill]
         if self.k and decode:
-            self._speculative_decode(decode)
-            decode = []
+            # a verify pass scores positions total_len - 1 .. total_len + k - 1: sequences closer than k tokens
+            # to the context limit take the plain one-token decode below for this step
+            roomy = [item for item in decode if item.seq.total_len + self.k <= self.model.context_length]
+            if roomy:
+                self._speculative_decode(roomy)
+            decode = [ScheduledSeq(item.seq, 1, False, True) for item in decode
+                      if item.seq.total_len + self.k > self.model.context_length]
         items, owners = [], []
         for item in prefill + decode:
             seq = item.seq
@@ -196,9 +201,19 @@ class LLMEngine:
                 if item.samples:
                     self._emit(seq, tokens[row], now)
                     row += 1
+        self._check_kernels()
         self.stats.steps += 1
         self.stats.busy_seconds += time.perf_counter() - tick
         return [self._to_output(seq) for seq in self._finished[done_before:]]
+
+    def _check_kernels(self) -> None:
+        """With projections fused with their collective, a rank whose peer stopped answering returns early with
+        incomplete sums: raise (``PeerTimeout``) instead of emitting tokens computed from them. The step has just read
+        its tokens back, so the device is idle and the check costs one small copy."""
+        tp = self.runner.tp
+        if tp is not None and getattr(tp, "fused", None) is not None:
+            from ajllm_b200.ops import native
+            native.check_status()
 
     def _speculative_decode_gpu(self, decode: list[ScheduledSeq]) -> None:
         """Same step with logits kept on the device: the sampler kernel proposes, the verify kernel decides,

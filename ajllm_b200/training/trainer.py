@@ -134,6 +134,29 @@ class Trainer:
         self.model.train()
         return results
 
+    def _check_kernels(self) -> None:
+        """Raise :class:`ajllm_b200.ops.native.PeerTimeout` when a kernel of this rank gave up a bounded wait
+        (its outputs, e.g. reduced gradients, are then incomplete). Synchronises the device."""
+        if self.device.type == "cuda":
+            from ajllm_b200.ops import native
+            native.check_status()
+
+    def _save(self, path: Path, step: int, metadata: dict[str, Any], best_validation_loss: float,
+              aliases: tuple[str, ...] = ()) -> Path:
+        """Checkpoint entered by every rank (state gathering is collective); refused after a kernel timeout so
+        that weights updated from incomplete gradients never reach the disk."""
+        self._check_kernels()
+        return save_checkpoint(path, self.model, self.optimizer, step, metadata,
+                               self._extra_state(best_validation_loss), aliases=aliases)
+
+    def _agreed(self, flag: bool) -> bool:
+        """Rank 0's view of a file-system fact, so that every rank takes the same branch into a collective."""
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+            return flag
+        box = [flag]
+        dist.broadcast_object_list(box, src=0)
+        return bool(box[0])
+
     def _extra_state(self, best_validation_loss: float) -> dict[str, Any]:
         return {"data_rng_state": self.generator.bit_generator.state, "best_validation_loss": best_validation_loss}
 
@@ -200,7 +223,7 @@ class Trainer:
 
                 if completed % log_interval == 0 or completed == 1:
                     if use_cuda:
-                        torch.cuda.synchronize()
+                        self._check_kernels()         # synchronises; a timed-out wait stops the run here
                         device_ms += sum(b.elapsed_time(e) for b, e in pending_events)
                         pending_events.clear()
                     loss_float = self._global_loss(loss_value)
@@ -225,30 +248,29 @@ class Trainer:
                     validation_loss = evaluation.get("validation_loss")
                     if validation_loss is not None and validation_loss < best_validation_loss:
                         best_validation_loss = validation_loss
-                        save_checkpoint(checkpoint_directory / "best.pt", self.model, self.optimizer, completed,
-                                        checkpoint_metadata, self._extra_state(best_validation_loss))
+                        self._save(checkpoint_directory / "best.pt", completed, checkpoint_metadata,
+                                   best_validation_loss)
 
                 if checkpoint_interval > 0 and completed % checkpoint_interval == 0:
-                    save_checkpoint(checkpoint_directory / f"step_{completed:08d}.pt", self.model, self.optimizer,
-                                    completed, checkpoint_metadata, self._extra_state(best_validation_loss),
-                                    aliases=("latest.pt",))
+                    self._save(checkpoint_directory / f"step_{completed:08d}.pt", completed, checkpoint_metadata,
+                               best_validation_loss, aliases=("latest.pt",))
         finally:
             stager.close()
 
-        final_path = save_checkpoint(checkpoint_directory / "final.pt", self.model, self.optimizer, max_steps,
-                                     checkpoint_metadata, self._extra_state(best_validation_loss),
-                                     aliases=("latest.pt",))
+        final_path = self._save(checkpoint_directory / "final.pt", max_steps, checkpoint_metadata,
+                                best_validation_loss, aliases=("latest.pt",))
         final_evaluation = self.evaluate(eval_batches, batch_size, context_length)
         validation_loss = final_evaluation.get("validation_loss")
         best_path = checkpoint_directory / "best.pt"
-        if validation_loss is not None and (validation_loss < best_validation_loss or not best_path.exists()):
+        # every rank enters a save (state gathering is collective), so the decision uses only values all ranks share:
+        # the evaluation result (already reduced over ranks) and rank 0's view of the file system
+        best_missing = self._agreed(not best_path.exists())
+        if validation_loss is not None and (validation_loss < best_validation_loss or best_missing):
             best_validation_loss = min(best_validation_loss, validation_loss)
-            save_checkpoint(best_path, self.model, self.optimizer, max_steps, checkpoint_metadata,
-                            self._extra_state(best_validation_loss))
-        elif validation_loss is None and is_main_process() and not best_path.exists():
+            self._save(best_path, max_steps, checkpoint_metadata, best_validation_loss)
+        elif validation_loss is None and best_missing:
             # no validation split: "best" resolves to the final weights
-            save_checkpoint(best_path, self.model, self.optimizer, max_steps, checkpoint_metadata,
-                            self._extra_state(best_validation_loss))
+            self._save(best_path, max_steps, checkpoint_metadata, best_validation_loss)
         summary = {
             "status": "completed",
             "steps": max_steps,

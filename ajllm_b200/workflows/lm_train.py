@@ -2,8 +2,15 @@
 
 Single process or one process per GPU under ``torchrun``. The ``parallel`` mapping chooses the mesh
 (``tp`` x ``fsdp`` with ``ep`` inside the data-parallel axis); ``acceleration.use_fsdp: true`` without a
-``parallel`` mapping means "shard over all ranks", as in the reference. ``acceleration.mixed_precision:
-bf16`` trains in bf16 with fp32 master weights and optimizer state (any layout, not only FSDP).
+``parallel`` mapping means "shard over all ranks", as in the reference.
+
+Precision. On the CPU the model trains in fp32, as the reference does by default. On a CUDA device every
+configuration computes in bf16 on this package's kernels with fp32 master weights, fp32 gradients and fp32
+optimizer state (any layout, not only FSDP): that is what ``acceleration.mixed_precision: bf16`` asks for,
+what an absent key gets (the reference's fp32 default would leave the tensor cores idle and run none of the
+kernels here), and what ``fp16`` is mapped to with a notice (same fp32 master weights, wider exponent, no
+loss scaling needed). ``acceleration.fused`` (default true on CUDA) runs tensor-parallel projections and
+the expert exchange as single kernels over symmetric NVLink memory instead of NCCL collectives.
 All ranks share one run directory (rank 0 draws the id); rank 0 writes the report, manifest,
 metrics and checkpoints.
 """
@@ -62,13 +69,17 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
     if world > 1:
         from ajllm_b200.parallel import init_distributed
         _, _, device = init_distributed(device.type)
+    precision_note = None
     if mixed is not None:
         if mixed not in ("fp16", "bf16"):
             raise ValueError(f"mixed_precision must be 'fp16', 'bf16', or null, got: {mixed}")
         if device.type != "cuda":
             raise ValueError(f"Mixed precision requires a CUDA device, got: {device.type}")
         if mixed == "fp16":
-            raise ValueError("fp16 training is not offered (no loss scaling); use bf16")
+            precision_note = "fp16 was requested: computing in bf16 with fp32 master weights (no loss scaling needed)"
+    elif device.type == "cuda":
+        precision_note = "no mixed_precision key: a CUDA device computes in bf16 with fp32 master weights and optimizer state"
+    compute_dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     seed_all(seed)
 
     experiment = str(data.get("experiment", "training"))
@@ -100,7 +111,8 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
     mesh = None
     sizes = {"tp": 1, "ep": 1, "fsdp": 1, "pp": 1}
     if world > 1:
-        from ajllm_b200.parallel import ParallelMesh, TensorParallel
+        from ajllm_b200.parallel import ParallelMesh
+        from ajllm_b200.parallel.contexts import make_expert_parallel, make_tensor_parallel
         defaults = dict(parallel_cfg)
         if "fsdp" not in defaults and "tp" not in defaults:
             defaults["fsdp"] = world
@@ -108,12 +120,12 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
         if sizes["pp"] != 1 and (sizes["tp"] != 1 or sizes["fsdp"] != 1 or sizes["ep"] != 1):
             raise ValueError("pipeline parallelism runs on its own here: set tp = fsdp = ep = 1 (pp = world size)")
         mesh = ParallelMesh(tp=sizes["tp"], fsdp=sizes["fsdp"], ep=sizes["ep"], pp=sizes["pp"])
-        if sizes["tp"] > 1:
-            tp = TensorParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size)
-        if sizes["ep"] > 1:
-            ep = TensorParallel(mesh.ep.group, mesh.ep.rank, mesh.ep.size)
+        fused = acceleration.get("fused")
+        tp = make_tensor_parallel(mesh.tp, device, None if fused is None else bool(fused))
+        ep = make_expert_parallel(mesh.ep, device, None if fused is None else bool(fused))
+    from ajllm_b200.parallel.contexts import expert_exchange_backend, tp_backend
     checkpointing = str(acceleration.get("activation_checkpointing", "layer" if use_fsdp else "none"))
-    dtype = torch.bfloat16 if mixed == "bf16" else torch.float32
+    dtype = compute_dtype
     model = build_model(model_cfg, vocab_size, bool(acceleration.get("use_flash_attention", False)), tp=tp, ep=ep,
                         activation_checkpointing="none" if use_fsdp else checkpointing)
     model = model.to(device=device, dtype=dtype)
@@ -167,10 +179,15 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
         print(f"  gradient accumulation: {int(training_cfg.get('gradient_accumulation_steps', 1))}")
         print(f"  model parameters on this rank: {parameter_count:,}")
         print(f"  FSDP: {'enabled' if use_fsdp else 'disabled'}  mixed precision: {mixed or 'disabled'}")
+        print(f"  compute dtype: {str(dtype).replace('torch.', '')}  master weights / optimizer state: float32")
+        if precision_note:
+            print(f"  precision note: {precision_note}")
+        print(f"  tensor-parallel projections: {tp_backend(tp)}  expert exchange: {expert_exchange_backend(ep)}")
         print(f"  activation checkpointing: {checkpointing}")
     manifest = {"experiment": experiment, "dataset": dataset_cfg["name"], "tokenizer": tokenizer_cfg["name"],
                 "model": model_cfg["name"], "parameter_count": parameter_count, "device": str(device),
-                "world_size": world, "parallel": sizes}
+                "world_size": world, "parallel": sizes, "compute_dtype": str(dtype).replace("torch.", ""),
+                "tp_backend": tp_backend(tp), "expert_exchange": expert_exchange_backend(ep)}
     if _is_main():
         write_manifest(run_directory / "manifest.json", "training_run", manifest)
     trainer = Trainer(model, train_dataset, validation_dataset, run_directory, data, device, seed, optimizer=optimizer,

@@ -125,6 +125,18 @@ def test_speculative_greedy_is_lossless_and_self_draft_accepts_everything(models
     assert self_engine.cache.allocator.free_blocks == 64 and self_engine.draft_cache.allocator.free_blocks == 64
 
 
+def test_speculative_decoding_runs_into_the_context_limit_like_the_plain_engine(models):
+    target, draft = models
+    gen = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 300, (n,), generator=gen).tolist() for n in (100, 90)]
+    params = SamplingParams(100, 0.0, None)
+    plain = LLMEngine(target, num_blocks=64).generate(prompts, params)
+    spec = LLMEngine(target, num_blocks=64, draft_model=draft, num_speculative_tokens=4).generate(prompts, params)
+    assert [o.finish_reason for o in plain] == ["context", "context"]
+    assert [o.finish_reason for o in spec] == ["context", "context"]
+    assert [o.output for o in spec] == [o.output for o in plain]
+
+
 def test_rejection_sampling_preserves_the_target_distribution():
     torch.manual_seed(0)
     gen = torch.Generator().manual_seed(0)

@@ -69,3 +69,72 @@ def test_resume_refuses_a_truncated_checkpoint(tmp_path):
         load_checkpoint(path, model)
     # the atomic writer never leaves a half-written file under the final name
     assert not list(tmp_path.glob("*.tmp"))
+
+
+def _tiny_trainer(tmp_path, validation: bool = False, device=None, model=None, optimizer=None, **kwargs):
+    from ajllm_b200.models import build_model
+    from ajllm_b200.training.data import SyntheticTokens
+    from ajllm_b200.training.trainer import Trainer
+    from tests.helpers import TINY_MODEL
+
+    model = model if model is not None else build_model(TINY_MODEL, 30)
+    config = {"training": {"batch_size": 2, "max_steps": 2}, "optimizer": {"max_lr": 1e-3},
+              "logging": {"log_interval": 1, "eval_interval": 0, "eval_batches": 1, "checkpoint_interval": 1}}
+    data = SyntheticTokens(30, length=4096, seed=1)
+    return Trainer(model, data, data if validation else None, tmp_path, config, device or torch.device("cpu"), 0,
+                   optimizer=optimizer, **kwargs)
+
+
+def test_a_kernel_timeout_stops_training_before_any_checkpoint_is_written(tmp_path, monkeypatch):
+    from ajllm_b200.ops import native
+    from ajllm_b200.training.trainer import Trainer
+
+    trainer = _tiny_trainer(tmp_path)
+
+    def timed_out(self):
+        raise native.PeerTimeout(0x1e0a)
+    monkeypatch.setattr(Trainer, "_check_kernels", timed_out)
+    with pytest.raises(native.PeerTimeout):
+        trainer.train({})
+    assert not list((tmp_path / "checkpoints").glob("*.pt"))
+
+
+def test_the_status_words_are_read_on_a_cuda_device(monkeypatch):
+    from ajllm_b200.ops import native
+    from ajllm_b200.training.trainer import Trainer
+
+    calls = []
+    monkeypatch.setattr(native, "check_status", lambda: calls.append(1))
+    trainer = object.__new__(Trainer)
+    trainer.device = torch.device("cpu")
+    trainer._check_kernels()
+    assert not calls
+    trainer.device = torch.device("cuda", 0)
+    trainer._check_kernels()
+    assert calls == [1]
+
+
+def _fsdp_without_validation(rank, world, directory):
+    from pathlib import Path
+
+    from ajllm_b200.models import build_model
+    from ajllm_b200.parallel import ParallelMesh
+    from ajllm_b200.parallel.fsdp import ShardedDataParallel
+    from tests.helpers import TINY_MODEL
+
+    mesh = ParallelMesh(tp=1, fsdp=world)
+    torch.manual_seed(0)
+    model = ShardedDataParallel(build_model(TINY_MODEL, 30), mesh.dp.group, learning_rate=1e-3)
+    trainer = _tiny_trainer(Path(directory), model=model, optimizer=model.optimizer, data_rank=rank, data_world=world,
+                            loss_reduce_group=mesh.dp.group)
+    summary = trainer.train({})
+    assert summary["status"] == "completed"
+    if rank == 0:
+        names = {p.name for p in (Path(directory) / "checkpoints").iterdir()}
+        assert {"final.pt", "latest.pt", "best.pt"} <= names, names
+
+
+def test_sharded_training_without_a_validation_split_finishes_and_writes_best(tmp_path):
+    from tests.conftest import run_ranks
+
+    run_ranks(_fsdp_without_validation, 2, str(tmp_path), timeout=120.0)

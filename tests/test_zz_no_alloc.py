@@ -63,3 +63,15 @@ def test_static_scratch_entry_rejects_oversized_input():
     assert status != 0
     message = native.lib().ajb_last_error().decode()
     assert "outside the supported range" in message
+
+
+def test_static_scratch_entry_accepts_an_empty_input():
+    device = torch.device("cuda", 0)
+    fn, _ = _static_entry()
+    empty = torch.empty(0, device=device, dtype=torch.float32)
+    assert empty.data_ptr() == 0
+    out = torch.full((1,), -1.0, dtype=torch.float32, device=device)
+    status = fn(empty.data_ptr() or None, 0, out.data_ptr(), native.stream_ptr())
+    assert status == 0, native.lib().ajb_last_error()
+    torch.cuda.synchronize()
+    assert float(out) == 0.0
