@@ -18,7 +18,7 @@
 #include "common.cuh"
 
 namespace ajb {
-namespace flash {
+namespace attn {
 
 constexpr int BLK = 128;
 constexpr int kBwdThreads = 192;
@@ -981,7 +981,7 @@ static int launch_bwd(const void* qkv, const void* out, const void* dout, const 
   return 0;
 }
 
-}  // namespace flash
+}  // namespace attn
 }  // namespace ajb
 
 // delta: scratch [batch, heads, seq] fp32 (written here). dqkv: packed gradient rows, same layout as qkv.
@@ -995,9 +995,9 @@ extern "C" int ajb_flash_bwd(const void* qkv, const void* out, const void* dout,
   AJB_REQUIRE(heads % kv_heads == 0, "flash: kv_heads must divide heads");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (head_dim == 128)
-    return flash::launch_bwd<128>(qkv, out, dout, lse, delta, dqkv, dq_acc, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
+    return attn::launch_bwd<128>(qkv, out, dout, lse, delta, dqkv, dq_acc, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
   if (head_dim == 64)
-    return flash::launch_bwd<64>(qkv, out, dout, lse, delta, dqkv, dq_acc, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
+    return attn::launch_bwd<64>(qkv, out, dout, lse, delta, dqkv, dq_acc, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
   set_error("flash: head_dim %d is not supported by the tensor-core kernel (64 and 128 are)", head_dim);
   return 2;
 }

@@ -27,7 +27,7 @@
 #include "common.cuh"
 
 namespace ajb {
-namespace flash {
+namespace attn {
 
 namespace f128 {
 
@@ -483,5 +483,5 @@ int launch_bwd_fused_hd128(const void* qkv, const void* dout, const void* lse, c
   return 0;
 }
 
-}  // namespace flash
+}  // namespace attn
 }  // namespace ajb

@@ -15,7 +15,7 @@
 #include "common.cuh"
 
 namespace ajb {
-namespace flash {
+namespace attn {
 
 constexpr int BLOCK_M = 128;  // queries per CTA
 constexpr int BLOCK_N = 128;  // keys per step
@@ -343,7 +343,7 @@ static int launch_fwd(const void* qkv, void* out, void* lse, int batch, int seq,
   return 0;
 }
 
-}  // namespace flash
+}  // namespace attn
 }  // namespace ajb
 
 // qkv: packed [batch, seq, row_stride] bf16 with q heads first, then k heads, then v heads.
@@ -353,8 +353,8 @@ extern "C" int ajb_flash_fwd(const void* qkv, void* out, void* lse, int batch, i
   AJB_REQUIRE(heads % kv_heads == 0, "flash: kv_heads must divide heads");
   AJB_REQUIRE(row_stride % 8 == 0, "flash: row stride must be a multiple of 8 elements");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (head_dim == 128) return flash::launch_fwd<128>(qkv, out, lse, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
-  if (head_dim == 64) return flash::launch_fwd<64>(qkv, out, lse, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
+  if (head_dim == 128) return attn::launch_fwd<128>(qkv, out, lse, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
+  if (head_dim == 64) return attn::launch_fwd<64>(qkv, out, lse, batch, seq, heads, kv_heads, row_stride, causal, scale, s);
   set_error("flash: head_dim %d is not supported by the tensor-core kernel (64 and 128 are)", head_dim);
   return 2;
 }

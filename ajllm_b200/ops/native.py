@@ -50,7 +50,6 @@ _SIGNATURES: dict[str, list] = {
     "ajb_adamw_flat": [c_void, c_void, c_void, c_void, c_void, c_long, c_float, c_float, c_float, c_float,
                        c_float, c_void, c_float, c_void],
     "ajb_add_bf16": [c_void, c_void, c_void, c_long, c_void],
-    "ajb_mma_probe": [c_int, c_int, c_int, c_int, c_int, c_void, c_void],
     "ajb_flash_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_float, c_void],
     "ajb_fp8_quantize_rows": [c_void, c_void, c_void, c_int, c_int, c_void],
     "ajb_fp8_block_gemm": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_void],

@@ -296,7 +296,7 @@ def run_reference(args) -> None:
         begin.record()
         for s in range(args.warmup, total_steps):
             loss = one_step(mine[s])
-            float(loss)
+            float(loss.detach())
         end.record()
         barrier()
         wall_ms = (time.perf_counter() - t0) * 1e3

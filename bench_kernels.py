@@ -4,7 +4,6 @@ model, the attention kernels, the fused norm kernels, and the tensor-pipe probe.
     python bench_kernels.py                      # everything, full-size shapes
     python bench_kernels.py --case flash --small # a small case (for a profiler capture)
     python bench_kernels.py --case decode        # decoding GEMMs (few rows) against cuBLAS, GB/s of weights
-    python bench_kernels.py --case mma           # cycles per tcgen05.mma by shape / operand source
 
 Timing: CUDA events around 10 launches after 3 warm-up launches; operands are larger than L2 for the GEMM
 and norm cases. FLOP counts: 2 m n k for a GEMM; attention forward 4 B H T^2 d / 2 (causal), backward
@@ -103,21 +102,6 @@ def run_norm(dev, small: bool) -> None:
     print(f"add + rmsnorm bwd [{rows} x {dim}]: {t * 1e3:8.1f} us {nbytes / t / 1e6:7.0f} GB/s", flush=True)
 
 
-def run_mma_probe(dev) -> None:
-    cycles = torch.zeros(1, dtype=torch.int64, device=dev)
-    iters = 256
-    names = {0: "shared, K-major", 1: "shared, MN-major", 2: "tensor memory"}
-    print("cycles per tcgen05.mma (M 128, K 16, bf16); ideal = N / 2")
-    for n in (64, 128, 256):
-        for a_src, b_mn, commit in ((0, 0, 0), (1, 1, 0), (2, 1, 0), (0, 0, 4), (0, 0, 1)):
-            for _ in range(2):
-                native.call("ajb_mma_probe", n, a_src, b_mn, commit, iters, cycles.data_ptr(), native.stream_ptr())
-            torch.cuda.synchronize()
-            per = int(cycles.item()) / (iters * 8)
-            print(f"  N {n:3d}  A {names[a_src]:16s}  B {'MN' if b_mn else 'K '}-major  commit every {commit or '-':>2}: "
-                  f"{per:6.1f} cycles ({100 * (n / 2) / per:5.1f} % of the pipe rate)", flush=True)
-
-
 def run_decode_gemm(dev, small: bool) -> None:
     """Decoding GEMMs of the 8B block: few activation rows, weights streamed once per call (L2 flushed in between by a
     256 MB memset whose own time is subtracted); bytes = the weight matrix."""
@@ -147,7 +131,7 @@ def run_decode_gemm(dev, small: bool) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--case", default="all", choices=["all", "gemm", "decode", "flash", "flash64", "norm", "mma"])
+    ap.add_argument("--case", default="all", choices=["all", "gemm", "decode", "flash", "flash64", "norm"])
     ap.add_argument("--small", action="store_true", help="one small shape per case (a few hundred MB on the device)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -164,8 +148,6 @@ def main() -> None:
         run_flash(dev, args.small, head_dim=64)
     if args.case in ("all", "norm"):
         run_norm(dev, args.small)
-    if args.case in ("all", "mma"):
-        run_mma_probe(dev)
     print("kernel status", native.lib().ajb_check_status())
 
 

@@ -16,7 +16,7 @@ def _dev():
 
 
 def _rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
-    return float((got.float() - want.float()).norm() / want.float().norm().clamp_min(1e-12))
+    return float((got.detach().float() - want.detach().float()).norm() / want.detach().float().norm().clamp_min(1e-12))
 
 
 def test_native_library_is_loaded():
