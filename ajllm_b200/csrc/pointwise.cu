@@ -282,6 +282,24 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate_up, con
   }
 }
 
+// SiLU feed-forward activation (the reference's non-gated option): y = x * sigmoid(x); with `dy` the derivative
+// dy * sigmoid(x) * (1 + x * (1 - sigmoid(x))) is written instead.
+__global__ void silu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                            __nv_bfloat16* __restrict__ out, long long total_vec) {
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vec;
+       idx += (long long)gridDim.x * blockDim.x) {
+    float a[8], d[8], o[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(x)[idx], a);
+    if (dy != nullptr) unpack8(reinterpret_cast<const Bf16x8*>(dy)[idx], d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sig = 1.0f / (1.0f + __expf(-a[i]));
+      o[i] = dy != nullptr ? d[i] * sig * (1.0f + a[i] * (1.0f - sig)) : a[i] * sig;
+    }
+    reinterpret_cast<Bf16x8*>(out)[idx] = pack8(o);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ cross-entropy
 // One block per row: online (max, sum-exp) over the vocabulary, loss += lse - logit[target];
 // optionally overwrite the row with (softmax - onehot) * grad_scale.
@@ -547,6 +565,15 @@ extern "C" int ajb_swiglu_bwd(const void* gate_up, const void* dact, void* dgate
   if (total <= 0) return 0;
   swiglu_bwd_kernel<<<grid_for(total, 256), 256, 0, STREAM(stream)>>>((const bf16*)gate_up, (const bf16*)dact,
                                                                        (bf16*)dgate_up, total);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// out = silu(x) (dy == nullptr) or dy * silu'(x); n elements, a multiple of 8.
+extern "C" int ajb_silu(const void* x, const void* dy, void* out, long long n, void* stream) {
+  AJB_REQUIRE(n % 8 == 0, "silu: element count must be a multiple of 8");
+  if (n <= 0) return 0;
+  silu_kernel<<<grid_for(n / 8, 256), 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)dy, (bf16*)out, n / 8);
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -4,6 +4,7 @@ from ajllm_b200.ops import native, reference
 from ajllm_b200.ops.functional import (
     add_rms_norm,
     cross_entropy,
+    eager_cuda,
     embedding,
     gemm,
     gemm_batched,
@@ -19,6 +20,6 @@ from ajllm_b200.ops.functional import (
 )
 
 __all__ = [
-    "native", "reference", "add_rms_norm", "cross_entropy", "embedding", "gemm", "linear",
+    "native", "reference", "eager_cuda", "add_rms_norm", "cross_entropy", "embedding", "gemm", "linear",
     "linear_cross_entropy", "paged_attention_ragged", "rms_norm", "rope_attention", "silu", "split_packed_qkv", "swiglu_interleaved",
 ]

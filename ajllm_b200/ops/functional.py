@@ -9,6 +9,7 @@ interleaves gate (even) and up (odd) columns so the activation pairs sit side by
 
 from __future__ import annotations
 
+import contextlib
 import math
 import os
 
@@ -35,6 +36,35 @@ DETERMINISTIC_WGRAD = os.environ.get("AJB_DETERMINISTIC", "0") == "1"
 
 def _is_cuda(t: torch.Tensor) -> bool:
     return t.device.type == "cuda"
+
+
+# CUDA tensors run the kernels of this package, which compute in bf16 (fp32 lives in the optimizer's master weights,
+# gradients and moments). Another dtype on a GPU is an error rather than a silent drop to eager PyTorch; a caller that
+# wants eager math on purpose (the `baseline` arm of the acceleration benchmark) says so with `eager_cuda()`.
+_EAGER_CUDA_ALLOWED = False
+
+
+@contextlib.contextmanager
+def eager_cuda():
+    """Inside this block non-bf16 CUDA tensors take the plain PyTorch math of :mod:`ajllm_b200.ops.reference`."""
+    global _EAGER_CUDA_ALLOWED
+    previous, _EAGER_CUDA_ALLOWED = _EAGER_CUDA_ALLOWED, True
+    try:
+        yield
+    finally:
+        _EAGER_CUDA_ALLOWED = previous
+
+
+def _native(t: torch.Tensor, op: str) -> bool:
+    """True when ``t`` goes to the CUDA kernels; False for the oracle math (CPU tensors, or eager CUDA on request)."""
+    if t.device.type != "cuda":
+        return False
+    if t.dtype == torch.bfloat16:
+        return True
+    if _EAGER_CUDA_ALLOWED:
+        return False
+    raise TypeError(f"{op}: CUDA tensors must be bfloat16 (got {t.dtype}); cast the model with .to(torch.bfloat16) - "
+                    "fp32 master weights are kept by the optimizer - or wrap the call in ops.eager_cuda()")
 
 
 # ----------------------------------------------------------------------------- GEMM
@@ -112,7 +142,7 @@ class _BatchedLinearFn(torch.autograd.Function):
 def linear_batched(x: torch.Tensor, weight: torch.Tensor, valid_rows: torch.Tensor | None = None,
                    segment_rows: int = 0) -> torch.Tensor:
     """Stacked-expert projection ``[E, rows, in] x [E, out, in] -> [E, rows, out]``."""
-    if _is_cuda(x) and x.dtype == torch.bfloat16:
+    if _native(x, "linear_batched"):
         return _BatchedLinearFn.apply(x, weight, valid_rows, segment_rows)
     return torch.einsum("erk,enk->ern", x, weight)
 
@@ -228,7 +258,7 @@ def _linear_decode(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``x @ weight.T`` for a bias-free ``[out, in]`` weight (``ajllm/modeling/layers.py:33``)."""
-    if _is_cuda(x) and x.dtype == torch.bfloat16:
+    if _native(x, "linear"):
         if not torch.is_grad_enabled() and weight.shape[0] % 8 == 0:
             x2 = x.reshape(-1, x.shape[-1])
             if x2.shape[0] <= _SKINNY_ROWS and x2.stride(-1) == 1 and weight.stride(-1) == 1:
@@ -295,7 +325,7 @@ class _AddRmsNormFn(torch.autograd.Function):
 
 def add_rms_norm(x: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, eps: float = 1e-5):
     """Residual add fused with RMSNorm: returns ``(x + delta, rmsnorm(x + delta) * gain)``."""
-    if _is_cuda(x) and x.dtype == torch.bfloat16:
+    if _native(x, "rms_norm"):
         return _AddRmsNormFn.apply(x, delta, gain, eps)
     h = x if delta is None else x + delta
     return h, reference.rms_norm(h, gain, eps)
@@ -360,7 +390,7 @@ def rope_attention(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tenso
     ``qkv`` must be a buffer the caller no longer needs un-rotated (the output of the projection GEMM).
     """
     B, T, _ = qkv.shape
-    if _is_cuda(qkv) and qkv.dtype == torch.bfloat16:
+    if _native(qkv, "rope_attention"):
         use_rope = cos is not None
         if use_rope and (cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape[0] < T):
             raise ValueError("RoPE tables must be fp32 and cover the sequence length")
@@ -411,12 +441,33 @@ class _SwigluFn(torch.autograd.Function):
 
 def swiglu_interleaved(gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up`` where even columns are gate and odd columns are up."""
-    if _is_cuda(gate_up) and gate_up.dtype == torch.bfloat16:
+    if _native(gate_up, "swiglu"):
         return _SwigluFn.apply(gate_up)
     return reference.swiglu_interleaved(gate_up)
 
 
+class _SiluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        flat = x.contiguous()
+        out = torch.empty_like(flat)
+        native.call("ajb_silu", flat.data_ptr(), None, out.data_ptr(), flat.numel(), native.stream_ptr())
+        ctx.save_for_backward(flat)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (flat,) = ctx.saved_tensors
+        g = grad_out.contiguous()
+        dx = torch.empty_like(flat)
+        native.call("ajb_silu", flat.data_ptr(), g.data_ptr(), dx.data_ptr(), flat.numel(), native.stream_ptr())
+        return dx
+
+
 def silu(x: torch.Tensor) -> torch.Tensor:
+    """``x * sigmoid(x)`` (``ajllm/modeling/activations.py:11``)."""
+    if _native(x, "silu") and x.numel() % 8 == 0:
+        return _SiluFn.apply(x)
     return reference.silu(x)
 
 
@@ -453,7 +504,7 @@ class _EmbeddingFn(torch.autograd.Function):
 
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """Row gather ``table[ids]`` (``ajllm/modeling/layers.py:53``)."""
-    if _is_cuda(table) and table.dtype == torch.bfloat16:
+    if _native(table, "embedding"):
         return _EmbeddingFn.apply(ids, table)
     return table[ids]
 
@@ -461,6 +512,14 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 # ----------------------------------------------------------------------------- LM head + cross-entropy
 
 _CE_ROWS_PER_CHUNK = 8192
+
+
+def _logits_chunk(rows: int, vocab: int, device) -> torch.Tensor:
+    """``[rows, vocab]`` bf16 scratch whose row pitch is a multiple of 8 elements: the logits are read back by TMA as a
+    GEMM operand, which needs 16-byte aligned rows whatever the vocabulary size. The columns past ``vocab`` are never
+    read (the tensor maps end at ``vocab``)."""
+    pitch = (vocab + 7) // 8 * 8
+    return torch.empty(rows, pitch, dtype=torch.bfloat16, device=device)[:, :vocab]
 
 
 class _LinearCrossEntropyFn(torch.autograd.Function):
@@ -483,13 +542,13 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         grad_w = main if main is not None else torch.zeros(vocab, dim, dtype=torch.float32, device=h2.device)
         inv = float(loss_scale) / rows
         chunk = min(rows, _CE_ROWS_PER_CHUNK)
-        logits = torch.empty(chunk, vocab, dtype=torch.bfloat16, device=h2.device)
+        logits = _logits_chunk(chunk, vocab, h2.device)
         for start in range(0, rows, chunk):
             r = min(chunk, rows - start)
             hs = h2[start:start + r]
             gemm(hs, weight, logits, r, vocab, dim)
             native.call("ajb_ce_fwd_bwd", logits.data_ptr(), tgt[start:start + r].data_ptr(), loss_sum.data_ptr(),
-                        r, vocab, vocab, inv, 1, stream)
+                        r, vocab, logits.stride(0), inv, 1, stream)
             gemm(logits, weight, grad_h[start:start + r], r, dim, vocab, b_mn_major=True)
             gemm(logits, hs, grad_w, vocab, dim, r, a_mn_major=True, b_mn_major=True, epilogue=EPI_ACCUM_F32)
         ctx.save_for_backward(grad_h, None if main is not None else grad_w)
@@ -516,12 +575,12 @@ def _linear_cross_entropy_eval(hidden, weight, targets) -> torch.Tensor:
     rows, vocab = h2.shape[0], weight.shape[0]
     loss_sum = torch.zeros(1, dtype=torch.float32, device=h2.device)
     chunk = min(rows, _CE_ROWS_PER_CHUNK)
-    logits = torch.empty(chunk, vocab, dtype=torch.bfloat16, device=h2.device)
+    logits = _logits_chunk(chunk, vocab, h2.device)
     for start in range(0, rows, chunk):
         r = min(chunk, rows - start)
         gemm(h2[start:start + r], weight, logits, r, vocab, dim)
         native.call("ajb_ce_fwd_bwd", logits.data_ptr(), tgt[start:start + r].data_ptr(), loss_sum.data_ptr(),
-                    r, vocab, vocab, 0.0, 0, native.stream_ptr())
+                    r, vocab, logits.stride(0), 0.0, 0, native.stream_ptr())
     return (loss_sum / rows).reshape(())
 
 
@@ -534,7 +593,7 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, targets: to
     On the GPU the gradients are produced during the forward call, so the caller must backpropagate the
     returned loss with a unit (or scalar) upstream gradient.
     """
-    if _is_cuda(hidden) and hidden.dtype == torch.bfloat16:
+    if _native(hidden, "linear_cross_entropy"):
         if torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad):
             return _LinearCrossEntropyFn.apply(hidden, weight, targets, loss_scale)
         return _linear_cross_entropy_eval(hidden, weight, targets)

@@ -43,6 +43,7 @@ _SIGNATURES: dict[str, list] = {
     "ajb_rope_qk": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_void],
     "ajb_swiglu_fwd": [c_void, c_void, c_long, c_int, c_void],
     "ajb_swiglu_bwd": [c_void, c_void, c_void, c_long, c_int, c_void],
+    "ajb_silu": [c_void, c_void, c_void, c_long, c_void],
     "ajb_ce_fwd_bwd": [c_void, c_void, c_void, c_int, c_int, c_long, c_float, c_int, c_void],
     "ajb_embedding_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],
     "ajb_embedding_bwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],

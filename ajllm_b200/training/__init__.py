@@ -11,4 +11,5 @@ from ajllm_b200.training.trainer import Trainer, optimizer_step
 __all__ = [
     "load_checkpoint", "save_checkpoint", "BatchStager", "SyntheticTokens", "TokenDataset", "RunLogger",
     "cross_entropy", "AdamW", "FlatAdamW", "clip_gradients", "warmup_cosine_learning_rate", "Trainer",
+    "optimizer_step",
 ]

@@ -4,7 +4,8 @@ Counterpart of the reference's ``ajllm/workflows/benchmark_distributed.py`` (fou
 forward / backward / optimizer / total, JSON + CSV + figure). The configurations keep the reference's names; here
 they select:
 
-* ``baseline``                  fp32 parameters, plain PyTorch math (no native kernel is used for fp32),
+* ``baseline``                  fp32 parameters, plain PyTorch math requested explicitly (``ops.eager_cuda()``; without
+                                that request an fp32 CUDA tensor is refused by the ops layer),
 * ``flash_attention``           bf16 parameters: the tcgen05 GEMM / attention / fused pointwise kernels,
 * ``fsdp_ac``                   ``baseline`` under fully sharded data parallelism with per-layer recomputation,
 * ``flash_attention_fsdp_ac``   ``flash_attention`` under the same wrapper.
@@ -115,6 +116,16 @@ def _stats(samples: list[float], peaks: list[float]) -> PhaseStats:
 
 
 def _worker(args: argparse.Namespace, config: str, rank: int, world: int) -> BenchmarkResult:
+    import contextlib
+
+    from ajllm_b200.ops.functional import eager_cuda
+
+    # the two fp32 arms are the eager-PyTorch baselines of the comparison
+    with (contextlib.nullcontext() if "flash_attention" in config else eager_cuda()):
+        return _worker_body(args, config, rank, world)
+
+
+def _worker_body(args: argparse.Namespace, config: str, rank: int, world: int) -> BenchmarkResult:
     from ajllm_b200.models import build_model
     from ajllm_b200.training.optim import FlatAdamW
 

@@ -177,8 +177,6 @@ def test_cross_entropy_and_fused_head(rows, vocab):
     pad = (vocab + 7) // 8 * 8
     w = (torch.randn(pad, dim, device=_dev()) * 0.05).to(torch.bfloat16)[:vocab].requires_grad_()
     t = torch.randint(0, vocab, (rows,), device=_dev())
-    if vocab % 8:
-        pytest.skip("fused head needs an 8-aligned vocabulary row pitch; padded vocabularies are the supported case")
     loss = ops.linear_cross_entropy(h, w, t)
     loss.backward()
     hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
