@@ -44,11 +44,13 @@ def inference_dtype(device: torch.device, run_config: dict[str, Any]) -> torch.d
     return torch.bfloat16 if device.type == "cuda" else torch.float32
 
 
-def load_model_from_run(run_directory: Path, checkpoint_selector: str, device: torch.device
+def load_model_from_run(run_directory: Path, checkpoint_selector: str, device: torch.device, tp=None
                         ) -> tuple[torch.nn.Module, dict[str, Any], dict[str, Any]]:
+    """``tp`` (a :class:`~ajllm_b200.parallel.TensorParallel`) makes every rank load its own slice of the
+    un-sharded checkpoint."""
     run_config = load_run_configuration(run_directory)
     vocab_size = int(run_config["_runtime"]["vocab_size"])
-    model = build_model(run_config["model"], vocab_size).to(device=device, dtype=inference_dtype(device, run_config))
+    model = build_model(run_config["model"], vocab_size, tp=tp).to(device=device, dtype=inference_dtype(device, run_config))
     checkpoint = load_checkpoint(select_checkpoint(run_directory, checkpoint_selector), model)
     model.eval()
     return model, run_config, checkpoint

@@ -4,11 +4,17 @@
 All prompts and their ``samples_per_prompt`` copies are submitted to the continuous-batching engine at
 once instead of being generated one after another; ``engine:`` may set ``block_size``,
 ``max_num_seqs``, ``quantization: fp8`` and ``speculative: {draft_run_directory, k}``.
+
+Launched with one process per GPU (``torchrun``), the model is served tensor-parallel over all ranks:
+every rank loads its slice of the checkpoint, row-parallel projections end in the fused
+GEMM -> all-reduce kernel (``acceleration.fused: false`` or ``AJB_FUSED_TP=0``: NCCL), every rank runs
+the same scheduler and sampler from the same seeds, and rank 0 writes the results.
 """
 
 from __future__ import annotations
 
 import json
+import os
 import time
 from pathlib import Path
 from typing import Any
@@ -38,7 +44,16 @@ def run(config: LoadedConfig) -> dict[str, Any]:
     seed = int(data.get("seed", 42))
     seed_all(seed)
     checkpoint = str(data.get("checkpoint", "best"))
-    model, train_cfg, _ = load_model_from_run(training_run, checkpoint, device)
+    tp = None
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        from ajllm_b200.parallel import ParallelMesh, init_distributed
+        from ajllm_b200.parallel.contexts import make_tensor_parallel
+        _, _, device = init_distributed(device.type)
+        fused = (data.get("acceleration", {}) or {}).get("fused")
+        tp = make_tensor_parallel(ParallelMesh(tp=world).tp, device, None if fused is None else bool(fused))
+    main = tp is None or tp.rank == 0
+    model, train_cfg, _ = load_model_from_run(training_run, checkpoint, device, tp=tp)
     tok_dir, tok_manifest = open_tokenizer_artifact(config.project_root, train_cfg["tokenizer"]["name"])
     tokenizer = Tokenizer.from_files(tok_dir / tok_manifest["files"]["vocab"], tok_dir / tok_manifest["files"]["merges"],
                                      tok_manifest.get("special_tokens", []))
@@ -54,7 +69,7 @@ def run(config: LoadedConfig) -> dict[str, Any]:
     spec = engine_cfg.get("speculative") or {}
     if spec.get("draft_run_directory"):
         draft, _, _ = load_model_from_run(project_path(config.project_root, spec["draft_run_directory"]),
-                                          str(spec.get("checkpoint", "best")), device)
+                                          str(spec.get("checkpoint", "best")), device, tp=tp)
         k = int(spec.get("k", 4))
     engine = LLMEngine(model, block_size=int(engine_cfg.get("block_size", 16)),
                        max_num_seqs=int(engine_cfg.get("max_num_seqs", 256)),
@@ -79,17 +94,20 @@ def run(config: LoadedConfig) -> dict[str, Any]:
             "text": tokenizer.decode(full), "token_count": len(full),
             "elapsed_seconds": out.latency_seconds if out.latency_seconds is not None else elapsed,
         })
+    from ajllm_b200.parallel.contexts import tp_backend
     out_dir = ArtifactPaths(config.project_root).task_run("generations", name)
-    out_dir.mkdir(parents=True, exist_ok=True)
     payload = {
         "training_run": str(training_run), "checkpoint": checkpoint,
         "parameters": {"max_new_tokens": max_new, "temperature": temperature, "top_p": top_p,
                        "samples_per_prompt": samples, "seed": seed},
         "throughput": {"output_tokens": engine.stats.output_tokens, "elapsed_seconds": elapsed,
                        "output_tokens_per_second": engine.stats.output_tokens / max(elapsed, 1e-9)},
+        "tensor_parallel": {"size": world, "backend": tp_backend(tp)},
         "results": results,
     }
-    with (out_dir / "results.json").open("w", encoding="utf-8") as handle:
-        json.dump(payload, handle, indent=2, ensure_ascii=False)
-    write_manifest(out_dir / "manifest.json", "generation", {k_: v for k_, v in payload.items() if k_ != "results"})
+    if main:
+        out_dir.mkdir(parents=True, exist_ok=True)
+        with (out_dir / "results.json").open("w", encoding="utf-8") as handle:
+            json.dump(payload, handle, indent=2, ensure_ascii=False)
+        write_manifest(out_dir / "manifest.json", "generation", {k_: v for k_, v in payload.items() if k_ != "results"})
     return {"output_dir": str(out_dir), **payload}

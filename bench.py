@@ -1,15 +1,28 @@
-"""Headline benchmark: training tokens/s of the dense 1.3B-class decoder (24 layers, d_model 2048,
-16 heads x 128, 8 KV heads, SwiGLU 5632, vocab 32000, seq 4096, global batch 32 sequences, bf16 with
-fp32 AdamW master weights, no activation checkpointing) on N GPUs of one node, tensor-parallel over N.
+"""Benchmarks of record. Headline: training tokens/s of the dense 1.3B-class decoder (24 layers, d_model 2048,
+16 heads x 128, 8 KV heads, SwiGLU 5632, vocab 32000, seq 4096, global batch 32 sequences, bf16 with fp32 AdamW
+master weights, no activation checkpointing) on N GPUs of one node, tensor-parallel over N.
 
     python bench.py --gpus 1 --steps 5 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29511 bench.py --gpus 8 --steps 5 --warmup 3
     python bench.py --impl reference ...        # the unmodified reference from baseline/_ref
 
-Rank 0 prints one JSON line. ``value`` is device-timed (CUDA events, max over ranks) with the step's
-token batches already resident on the GPU; ``e2e`` times the same steps through the training API with
-every micro-batch copied from pinned host memory and the loss read back each step.
+Rank 0 prints one JSON line. ``value`` is device-timed (CUDA events, max over ranks) with the step's token batches
+already resident on the GPU; ``e2e`` times the same steps through the training API with every micro-batch copied
+from pinned host memory and the loss read back each step.
+
+After the headline workload the same invocation measures the other workloads of the benchmark suite as short runs and
+attaches them under ``secondary`` of the same JSON line (``--no-secondary`` skips them):
+
+    dense1p3b_mha16   the headline model with 16 KV heads, the shape the reference arm is limited to
+    dense8b_fsdp      8B decoder, fully sharded over N, micro-batch 2 x 8192 per GPU, accumulation 4, per-layer recompute
+    moe64e_ep         64-expert top-6 MoE (+2 shared experts), expert parallel over N inside the sharded runtime
+    serve_8b          8B decoder behind the paged-KV engine, tensor-parallel over N (bench_serve.py --suite)
+
+Each secondary workload runs in child processes of its own (one per rank, own rendezvous port, a time limit), started
+after this process has released the GPU, so a failure there cannot take the headline number with it. ``--workload``
+runs one of them directly. The reference arm does the same with the workloads the reference can express
+(``dense8b_fsdp`` with its own FSDP wrapper, ``serve_8b`` with its ``generate()`` on a few requests).
 """
 
 from __future__ import annotations
@@ -17,7 +30,9 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import subprocess
 import sys
+import tempfile
 import time
 from pathlib import Path
 
@@ -33,7 +48,6 @@ GLOBAL_BATCH = 32
 SEQ = 4096
 METRIC = "train tokens/sec"
 
-# Secondary workloads (`--workload`): the flagship line above stays the default.
 DENSE_8B = {"name": "dense_8b", "context_length": 8192, "d_model": 4096, "num_layers": 32, "num_heads": 32,
             "num_kv_heads": 8, "d_ff": 14336, "position_encoding": {"type": "rope", "theta": 500000.0},
             "init": {"type": "normal", "std": 0.02}}
@@ -42,6 +56,10 @@ MOE_64E = {"name": "moe_64e", "context_length": 4096, "d_model": 2048, "num_laye
            "moe": {"num_experts": 64, "top_k": 6, "shared_experts": 2, "d_ff": 1408, "aux_loss_coef": 0.01,
                    "capacity_factor": 1.25},
            "position_encoding": {"type": "rope", "theta": 10000.0}, "init": {"type": "normal", "std": 0.02}}
+
+# bytes of training state per parameter: bf16 working copy, fp32 master, gradient and two moments
+STATE_BYTES_PER_PARAM = 18
+GPU_BYTES = 180e9
 
 
 def parse_args():
@@ -54,9 +72,14 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
     ap.add_argument("--seq", type=int, default=SEQ)
-    ap.add_argument("--workload", default="dense1p3b_tp", choices=["dense1p3b_tp", "dense8b_fsdp", "moe64e_ep"],
+    ap.add_argument("--kv-heads", type=int, default=0, help="dense1p3b_tp only: KV heads (16 = the reference arm's shape)")
+    ap.add_argument("--workload", default="dense1p3b_tp",
+                    choices=["dense1p3b_tp", "dense8b_fsdp", "moe64e_ep", "serve_8b"],
                     help="dense8b_fsdp: 8B, FSDP over N, micro-batch 2 x 8192 per GPU, accumulation 4, per-layer "
-                         "checkpointing; moe64e_ep: 64-expert top-6 MoE, EP = N with FSDP, 8 x 4096 per GPU")
+                         "checkpointing; moe64e_ep: 64-expert top-6 MoE, EP = N with FSDP, 8 x 4096 per GPU; "
+                         "serve_8b: the serving suite of bench_serve.py")
+    ap.add_argument("--no-secondary", action="store_true", help="headline workload only")
+    ap.add_argument("--child", action="store_true", help=argparse.SUPPRESS)
     return ap.parse_args()
 
 
@@ -90,13 +113,14 @@ def synthetic_batches(global_batch: int, seq: int, micro: int, count: int, pin: 
 
 
 # =============================================================================================== ours
-def run_ours(args) -> None:
+def run_ours(args) -> dict | None:
     import torch
     import torch.distributed as dist
 
     from ajllm_b200.models import build_model
     from ajllm_b200.ops import native
-    from ajllm_b200.parallel import ParallelMesh, TensorParallel, init_distributed, tp_optimizer_classes
+    from ajllm_b200.parallel import ParallelMesh, init_distributed, tp_optimizer_classes
+    from ajllm_b200.parallel.contexts import make_tensor_parallel, tp_backend
     from ajllm_b200.training import FlatAdamW, optimizer_step
     from ajllm_b200.utils.timing import ClockSampler, max_over_ranks
 
@@ -109,20 +133,12 @@ def run_ours(args) -> None:
     config["context_length"] = args.seq
     if args.layers:
         config["num_layers"] = args.layers
+    if args.kv_heads:
+        config["num_kv_heads"] = args.kv_heads
     tp = None
     classes = None
     if world > 1:
-        mesh = ParallelMesh(tp=world)
-        fused = None
-        if os.environ.get("AJB_FUSED_TP", "1") != "0":
-            try:
-                from ajllm_b200.parallel.fused import FusedTensorParallel
-                fused = FusedTensorParallel(mesh.tp.group, device)
-            except Exception as error:  # noqa: BLE001 - reported in the JSON line
-                fused = None
-                if rank == 0:
-                    print(f"[bench] fused TP unavailable, using NCCL collectives: {error}", file=sys.stderr)
-        tp = TensorParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size, fused=fused)
+        tp = make_tensor_parallel(ParallelMesh(tp=world).tp, device)
         classes = tp_optimizer_classes(tp)
     micro = args.micro_batch or {1: 8, 2: 8, 4: 16, 8: 32}.get(world, 8)
     micro = min(micro, args.global_batch)
@@ -167,7 +183,7 @@ def run_ours(args) -> None:
     clocks = sampler.stop()
     launches = native.launch_count - launches0
     ms = max_over_ranks(begin.elapsed_time(end), device)
-    final_loss = float(loss) * (world if tp is not None else 1)
+    final_loss = float(loss.detach()) * (world if tp is not None else 1)
     tokens = args.global_batch * args.seq * args.steps
     value = tokens / (ms / 1e3)
 
@@ -192,25 +208,28 @@ def run_ours(args) -> None:
     readback = []
     for step_batches in timed:
         loss, norm = optimizer_step(model, optimizer, host_feed(step_batches), accumulation, 1.0)
-        readback.append(float(loss))          # device -> host read of the step's result
+        readback.append(float(loss.detach()))          # device -> host read of the step's result
     end2.record()
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
     e2e_ms = max_over_ranks(max(begin2.elapsed_time(end2), wall_ms), device)
     h2d = args.global_batch * (args.seq + 1) * 8
     status = native.lib().ajb_check_status()
+    overlap = getattr(model, "overlap_description", None)
 
+    payload = None
     if rank == 0:
         base = baseline_value()
-        emit({
+        kv = config["num_kv_heads"]
+        payload = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (value / base) if base else None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": "dense-1.3B (24L d2048 16h/8kv hd128 ffn5632 vocab32000)", "params": params * (world if False else 1),
+            "config": {"model": f"dense-1.3B (24L d2048 16h/{kv}kv hd128 ffn5632 vocab32000)", "params_on_rank": params,
                        "global_batch": args.global_batch, "seq_len": args.seq, "micro_batch": micro,
                        "grad_accumulation": accumulation, "parallelism": f"tp{world}",
-                       "tp_backend": ("fused-symmetric-memory" if (tp is not None and tp.fused is not None) else ("nccl" if tp else "none")),
+                       "tp_backend": tp_backend(tp), "overlap": overlap,
                        "optimizer": "AdamW fp32 master, global-norm clip 1.0", "activation_checkpointing": "off",
                        "l2": "inputs larger than L2 (multi-GB working set per step)",
                        "layers_override": args.layers or None},
@@ -220,127 +239,25 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches, "final_loss": final_loss, "kernel_status": status,
             "valid": not args.layers and args.global_batch == GLOBAL_BATCH and args.seq == SEQ,
-        })
+        }
+    # release the GPU before any secondary workload starts in a child process
+    del model, optimizer, feeds, loss, norm
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    torch.cuda.empty_cache()
+    return payload
 
 
-# =============================================================================================== reference
-def run_reference(args) -> None:
-    ref_root = ROOT / "baseline" / "_ref"
-    if not (ref_root / "ajllm" / "__init__.py").is_file():
-        emit({"impl": "reference", "unavailable": "baseline/_ref holds no reference install"})
-        return
-    sys.path.insert(0, str(ref_root))
-    try:
-        import torch
-        import torch.distributed as dist
-        from ajllm.modeling.factory import build_model
-        from ajllm.training.distributed import FullyShardedDataParallel
-        from ajllm.training.losses import cross_entropy
-        from ajllm.training.optimizers import AdamW
-        from ajllm.training.trainer import clip_gradients
-    except Exception as error:  # noqa: BLE001
-        emit({"impl": "reference", "unavailable": f"reference import failed: {type(error).__name__}: {error}"[:300]})
-        return
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
-    torch.manual_seed(0)
-    # the reference has no grouped KV heads: same shape with 16 full heads (1.364 B parameters)
-    config = {"name": "dense_1p3b_mha", "context_length": args.seq, "d_model": 2048, "num_layers": args.layers or 24,
-              "num_heads": 16, "d_ff": 5632, "position_encoding": {"type": "rope", "theta": 10000.0}}
-    try:
-        model = build_model(config, VOCAB, use_flash_attention=True).to(device)
-        model = FullyShardedDataParallel(model, compute_dtype=torch.bfloat16)
-        optimizer = AdamW(model.parameters(), learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1)
-        # no gradient accumulation in the reference: the optimizer steps on every micro-batch
-        micro = args.micro_batch or 4
-        per_rank = args.global_batch // world
-        micro = min(micro, per_rank)
-        total_steps = args.warmup + args.steps
-        host_steps = synthetic_batches(args.global_batch, args.seq, micro, total_steps, pin=True)
-        mine = [[b for i, b in enumerate(step) if i % world == rank] for step in host_steps]
-
-        def one_step(step_batches):
-            last = None
-            for batch in step_batches:
-                t = batch.to(device, non_blocking=True)
-                logits = model(t[:, :-1])
-                loss = cross_entropy(logits, t[:, 1:])
-                optimizer.zero_grad(set_to_none=True)
-                loss.backward()
-                model.finish_gradient_synchronization()
-                clip_gradients(model.parameters(), 1.0)
-                optimizer.step()
-                last = loss
-            return last
-
-        def barrier():
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-
-        for s in range(args.warmup):
-            one_step(mine[s])
-        barrier()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        begin.record()
-        for s in range(args.warmup, total_steps):
-            loss = one_step(mine[s])
-            float(loss.detach())
-        end.record()
-        barrier()
-        wall_ms = (time.perf_counter() - t0) * 1e3
-        ms = begin.elapsed_time(end)
-        if world > 1:
-            box = torch.tensor([ms, wall_ms], device=device, dtype=torch.float64)
-            dist.all_reduce(box, op=dist.ReduceOp.MAX)
-            ms, wall_ms = float(box[0]), float(box[1])
-        flash_used = None
-        try:
-            from ajllm.modeling import flash_attention as fa
-            cache = getattr(fa.flash_fwd_kernel, "device_caches", None) or getattr(fa.flash_fwd_kernel, "cache", None)
-            flash_used = bool(cache) and any(bool(v) for v in (cache.values() if hasattr(cache, "values") else [cache]))
-        except Exception:  # noqa: BLE001
-            pass
-        tokens = args.global_batch * args.seq * args.steps
-        if rank == 0:
-            emit({
-                "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
-                "config": {"model": "dense-1.3B as the reference can express it: MHA 16 heads (1.364B params)",
-                           "global_batch": args.global_batch, "seq_len": args.seq, "micro_batch": micro,
-                           "parallelism": f"reference FSDP over {world} (its only parallelism), bf16 compute, Triton flash attention",
-                           "note": "no gradient accumulation in the reference: optimizer step per micro-batch",
-                           "triton_flash_kernel_compiled": flash_used},
-                "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s",
-                        "h2d_bytes_per_step": args.global_batch * (args.seq + 1) * 8, "d2h_bytes_per_step": 4},
-            })
-    except Exception as error:  # noqa: BLE001
-        if rank == 0:
-            emit({"impl": "reference", "unavailable": f"reference run failed: {type(error).__name__}: {error}"[:400]})
-    if world > 1 and dist.is_initialized():
-        dist.destroy_process_group()
-
-
-def run_sharded(args) -> None:
+def run_sharded(args) -> dict | None:
     """Weak-scaling workloads on the fully-sharded runtime (8B dense; 64-expert MoE with expert parallelism)."""
     import torch
     import torch.distributed as dist
 
     from ajllm_b200.models import build_model
     from ajllm_b200.ops import native
-    from ajllm_b200.parallel import ParallelMesh, TensorParallel, init_distributed
+    from ajllm_b200.parallel import ParallelMesh, init_distributed
+    from ajllm_b200.parallel.contexts import expert_exchange_backend, make_expert_parallel
     from ajllm_b200.training import FlatAdamW, optimizer_step
     from ajllm_b200.utils.timing import ClockSampler, max_over_ranks
 
@@ -357,15 +274,10 @@ def run_sharded(args) -> None:
     torch.manual_seed(0)
     ep = None
     mesh = None
-    fused_ep = False
     if world > 1:
         mesh = ParallelMesh(tp=1, fsdp=world, ep=world if moe else 1)
         if moe:
-            ep = TensorParallel(mesh.ep.group, mesh.ep.rank, mesh.ep.size)
-            if os.environ.get("AJB_FUSED_EP", "1") != "0":
-                from ajllm_b200.parallel.moe_exchange import FusedExpertExchange
-                ep.exchange = FusedExpertExchange(mesh.ep.group, device)
-                fused_ep = True
+            ep = make_expert_parallel(mesh.ep, device)
     with torch.device(device):
         model = build_model(config, vocab, ep=ep, activation_checkpointing="layer" if world == 1 else "none")
     model = model.to(device=device, dtype=torch.bfloat16)
@@ -406,7 +318,7 @@ def run_sharded(args) -> None:
     losses = []
     for s in range(args.warmup, total_steps):
         loss, norm = optimizer_step(model, optimizer, feed(host[s]), accumulation, 1.0)
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     end.record()
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
@@ -415,32 +327,272 @@ def run_sharded(args) -> None:
     wall_ms = max_over_ranks(wall_ms, device)
     tokens = world * per_gpu_batch * (4 if not moe else 1) * seq * args.steps
     peak = torch.cuda.max_memory_allocated(device) / 2**30
+    payload = None
     if rank == 0:
-        emit({
+        payload = {
             "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": config["name"], "params_on_rank": params_local, "per_gpu_batch": per_gpu_batch,
                        "seq_len": seq, "micro_batch": micro, "grad_accumulation": accumulation,
                        "parallelism": (f"ep{world} x fsdp{world}" if moe else f"fsdp{world}") if world > 1 else "single",
-                       "expert_exchange": ("fused-symmetric-memory" if fused_ep else "nccl-all-to-all") if moe else None,
-                       "activation_checkpointing": "per layer", "layers_override": args.layers or None},
+                       "expert_exchange": expert_exchange_backend(ep) if moe else None,
+                       "activation_checkpointing": "per layer", "layers_override": args.layers or None,
+                       "timed_region": "includes the pinned-host to device copy of every micro-batch and the loss read-back"},
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons")},
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": accumulation * micro * (seq + 1) * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": native.launch_count - launches0, "final_loss": losses[-1], "peak_memory_gib": peak,
             "kernel_status": native.lib().ajb_check_status(),
-        })
+        }
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return payload
+
+
+# =============================================================================================== reference
+def _reference_imports():
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "ajllm" / "__init__.py").is_file():
+        return None, "baseline/_ref holds no reference install"
+    sys.path.insert(0, str(ref_root))
+    try:
+        import ajllm.modeling.factory  # noqa: F401
+        import ajllm.training.distributed  # noqa: F401
+    except Exception as error:  # noqa: BLE001
+        return None, f"reference import failed: {type(error).__name__}: {error}"[:300]
+    return ref_root, None
+
+
+def _is_oom(error: BaseException) -> bool:
+    import torch
+    return isinstance(error, torch.cuda.OutOfMemoryError) or "out of memory" in str(error).lower()
+
+
+def run_reference(args) -> dict | None:
+    """The unmodified reference driven through its own public API: ``build_model(use_flash_attention=True)`` (its
+    Triton kernels), ``FullyShardedDataParallel(bf16)``, ``cross_entropy``, ``clip_gradients``, ``AdamW``. It has no
+    gradient accumulation, so it is given the largest micro-batch that fits (fewest optimizer passes per batch)."""
+    _, problem = _reference_imports()
+    if problem:
+        return {"impl": "reference", "unavailable": problem}
+    import torch
+    import torch.distributed as dist
+    from ajllm.modeling.factory import build_model
+    from ajllm.training.distributed import FullyShardedDataParallel
+    from ajllm.training.losses import cross_entropy
+    from ajllm.training.optimizers import AdamW
+    from ajllm.training.trainer import clip_gradients
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    big = args.workload == "dense8b_fsdp"
+    if big:
+        # the 8B shape as the reference can express it: 32 full heads (8.84 B parameters), every rank 2 x 8192 tokens
+        # per optimizer step (it cannot accumulate the 4 micro-batches of the configuration)
+        config = {"name": "dense_8b_mha", "context_length": 8192, "d_model": 4096, "num_layers": args.layers or 32,
+                  "num_heads": 32, "d_ff": 14336, "position_encoding": {"type": "rope", "theta": 500000.0}}
+        vocab, seq, global_batch = 128256, 8192, 2 * world
+        candidates = [args.micro_batch] if args.micro_batch else [2, 1]
+    else:
+        # the reference has no grouped KV heads: same shape with 16 full heads (1.364 B parameters)
+        config = {"name": "dense_1p3b_mha", "context_length": args.seq, "d_model": 2048, "num_layers": args.layers or 24,
+                  "num_heads": 16, "d_ff": 5632, "position_encoding": {"type": "rope", "theta": 10000.0}}
+        vocab, seq, global_batch = VOCAB, args.seq, args.global_batch
+        per_rank = global_batch // world
+        candidates = [args.micro_batch] if args.micro_batch else [m for m in (16, 8, 4, 2, 1) if m <= per_rank]
+    total_steps = args.warmup + args.steps
+    tried: list[int] = []
+
+    def attempt(micro: int) -> dict:
+        torch.manual_seed(0)
+        model = build_model(config, vocab, use_flash_attention=True).to(device)
+        model = FullyShardedDataParallel(model, compute_dtype=torch.bfloat16)
+        optimizer = AdamW(model.parameters(), learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1)
+        gen = torch.Generator().manual_seed(0)
+        host_steps = []
+        for _ in range(total_steps):
+            tokens = torch.randint(0, vocab, (global_batch, seq + 1), generator=gen, dtype=torch.int64)
+            pieces = [tokens[i:i + micro].contiguous().pin_memory() for i in range(0, global_batch, micro)]
+            host_steps.append([b for i, b in enumerate(pieces) if i % world == rank])
+
+        def one_step(step_batches):
+            last = None
+            for batch in step_batches:
+                t = batch.to(device, non_blocking=True)
+                logits = model(t[:, :-1])
+                loss = cross_entropy(logits, t[:, 1:])
+                optimizer.zero_grad(set_to_none=True)
+                loss.backward()
+                model.finish_gradient_synchronization()
+                clip_gradients(model.parameters(), 1.0)
+                optimizer.step()
+                last = loss
+            return last
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for s in range(args.warmup):
+            one_step(host_steps[s])
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        begin.record()
+        for s in range(args.warmup, total_steps):
+            loss = one_step(host_steps[s])
+            float(loss.detach())
+        end.record()
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        ms = begin.elapsed_time(end)
+        if world > 1:
+            box = torch.tensor([ms, wall_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(box, op=dist.ReduceOp.MAX)
+            ms, wall_ms = float(box[0]), float(box[1])
+        tokens = global_batch * seq * args.steps
+        return {
+            "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak" if big else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "reference",
+            "config": {"model": ("dense-8B as the reference can express it: MHA 32 heads (8.84B params)" if big else
+                                 "dense-1.3B as the reference can express it: MHA 16 heads (1.364B params)"),
+                       "global_batch": global_batch, "seq_len": seq, "micro_batch": micro,
+                       "micro_batches_tried": list(tried),
+                       "parallelism": f"reference FSDP over {world} (its only parallelism), bf16 compute, Triton flash attention",
+                       "note": "no gradient accumulation in the reference: optimizer step per micro-batch; "
+                               "the largest micro-batch that fits is used"},
+            "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": global_batch * (seq + 1) * 8, "d2h_bytes_per_step": 4},
+            "peak_memory_gib": torch.cuda.max_memory_allocated(device) / 2**30,
+        }
+
+    payload, last_error = None, None
+    for micro in candidates:
+        tried.append(micro)
+        failed = 0
+        try:
+            payload = attempt(micro)
+        except Exception as error:  # noqa: BLE001 - out of memory moves on to a smaller micro-batch
+            # keep the text only: the exception's traceback would pin the failed attempt's tensors
+            last_error = f"{type(error).__name__}: {error}"
+            failed = 1 if _is_oom(error) else 2
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        # every rank must take the same branch: a rank that ran out of memory stops the others too
+        if world > 1:
+            flag = torch.tensor([failed], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            failed = int(flag)
+        if failed == 0:
+            break
+        payload = None
+        if failed == 2:
+            break
+    if payload is None:
+        why = last_error if last_error is not None else "a peer rank failed"
+        payload = {"impl": "reference", "unavailable": f"reference run failed (micro-batches tried {tried}): {why}"[:400]}
+    if world > 1 and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    torch.cuda.empty_cache()
+    return payload if rank == 0 else None
+
+
+# =============================================================================================== secondary workloads
+def _fits(params: float, world: int, what: str) -> str | None:
+    need = params * STATE_BYTES_PER_PARAM / world
+    if need > 0.8 * GPU_BYTES:
+        return (f"skipped at {world} GPU(s): {what} holds {params / 1e9:.1f} B parameters x {STATE_BYTES_PER_PARAM} bytes of "
+                f"training state = {need / 1e9:.0f} GB per GPU")
+    return None
+
+
+def _child(script: str, extra: list[str], port_offset: int, limit_s: float) -> dict:
+    """Run ``script`` in a child of this rank (same RANK / WORLD_SIZE, a rendezvous port of its own) and return the
+    JSON line its rank 0 printed. The child is killed by its exact pid when it exceeds ``limit_s``."""
+    env = dict(os.environ)
+    if "MASTER_PORT" in env:
+        env["MASTER_PORT"] = str(int(env["MASTER_PORT"]) + port_offset)
+    env.setdefault("MASTER_ADDR", "127.0.0.1")
+    # the child hosts its own rendezvous store instead of joining the launcher's
+    env.pop("TORCHELASTIC_USE_AGENT_STORE", None)
+    rank = int(env.get("RANK", "0"))
+    with tempfile.NamedTemporaryFile("w+", suffix=f".rank{rank}.log", delete=False) as log:
+        proc = subprocess.Popen([sys.executable, str(ROOT / script), *extra], stdout=log, stderr=subprocess.STDOUT,
+                                env=env, cwd=str(ROOT))
+        try:
+            code = proc.wait(timeout=limit_s)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            proc.wait()
+            code = "time limit"
+        log.seek(0)
+        text = log.read()
+    os.unlink(log.name)
+    for line in reversed(text.splitlines()):
+        line = line.strip()
+        if line.startswith("{") and line.endswith("}"):
+            try:
+                return json.loads(line)
+            except ValueError:
+                continue
+    return {"error": f"no result (exit {code}): " + text[-400:].replace("\n", " | ")}
+
+
+def run_secondary(args, impl: str) -> dict:
+    world = args.gpus
+    common = ["--gpus", str(world), "--child", "--no-secondary", "--impl", impl]
+    out: dict = {}
+    if impl == "ours":
+        out["dense1p3b_mha16"] = _child("bench.py", [*common, "--workload", "dense1p3b_tp", "--kv-heads", "16",
+                                                     "--steps", "3", "--warmup", "3"], 11, 240)
+        skip = _fits(8.03e9, world, "the 8B decoder")
+        out["dense8b_fsdp"] = {"skipped": skip} if skip else _child(
+            "bench.py", [*common, "--workload", "dense8b_fsdp", "--steps", "2", "--warmup", "3"], 13, 420)
+        skip = _fits(13.9e9, world, "the 64-expert model")
+        out["moe64e_ep"] = {"skipped": skip} if skip else _child(
+            "bench.py", [*common, "--workload", "moe64e_ep", "--steps", "3", "--warmup", "3"], 15, 300)
+        out["serve_8b"] = _child("bench_serve.py", ["--gpus", str(world), "--suite"], 17, 480)
+    else:
+        out["dense8b_fsdp"] = _child("bench.py", [*common, "--workload", "dense8b_fsdp", "--steps", "2", "--warmup", "3"],
+                                     13, 420)
+        out["serve_8b"] = _child("bench_serve.py", ["--gpus", str(world), "--impl", "reference", "--requests", "3"], 17, 420)
+        out["moe64e_ep"] = {"impl": "reference", "unavailable": "the reference has no mixture-of-experts layer and no expert parallelism"}
+    return out
+
+
+def main() -> None:
+    args = parse_args()
+    if args.workload == "serve_8b":
+        extra = ["--gpus", str(args.gpus), "--suite"] + (["--impl", "reference", "--requests", "3"] if args.impl == "reference" else [])
+        os.execv(sys.executable, [sys.executable, str(ROOT / "bench_serve.py"), *extra])
+    if args.impl == "reference":
+        payload = run_reference(args)
+    elif args.workload != "dense1p3b_tp":
+        payload = run_sharded(args)
+    else:
+        payload = run_ours(args)
+    rank = int(os.environ.get("RANK", "0"))
+    headline = args.workload == "dense1p3b_tp" and not args.child
+    if headline and not args.no_secondary and os.environ.get("AJB_BENCH_SECONDARY", "1") != "0":
+        secondary = run_secondary(args, args.impl)          # every rank starts its children; rank 0 keeps the results
+        if payload is not None:
+            payload["secondary"] = secondary
+    if rank == 0 and payload is not None:
+        emit(payload)
 
 
 if __name__ == "__main__":
-    arguments = parse_args()
-    if arguments.impl == "reference":
-        run_reference(arguments)
-    elif arguments.workload != "dense1p3b_tp":
-        run_sharded(arguments)
-    else:
-        run_ours(arguments)
+    main()

@@ -173,3 +173,25 @@ def test_train_workflow_on_two_ranks(project, mode):
         config["acceleration"] = {"use_fsdp": True}
         config["parallel"] = {"fsdp": 2, "ep": 2}
     run_ranks(_train_rank, 2, str(project), config)
+
+
+def _generate_tensor_parallel(rank, world, root, run_dir, want):
+    from pathlib import Path
+
+    out = lm_generate.run(loaded(Path(root), {"name": "g_tp", "run_directory": run_dir, "checkpoint": "final",
+                                              "prompts": ["The night train", "A small robot"], "max_new_tokens": 6,
+                                              "temperature": 0.0, "device": "cpu"}))
+    assert out["tensor_parallel"] == {"size": 2, "backend": "nccl"}
+    assert [r["completions"][0]["text"] for r in out["results"]] == want
+    assert Path(out["output_dir"]).is_dir() == (rank == 0) or rank != 0
+
+
+def test_generate_serves_tensor_parallel_over_two_ranks(project):
+    from tests.conftest import run_ranks
+
+    first = lm_train.run(loaded(project, train_config(project, max_steps=1)))
+    single = lm_generate.run(loaded(project, {"name": "g_one", "run_directory": first["run_directory"], "checkpoint": "final",
+                                              "prompts": ["The night train", "A small robot"], "max_new_tokens": 6,
+                                              "temperature": 0.0, "device": "cpu"}))
+    want = [r["completions"][0]["text"] for r in single["results"]]
+    run_ranks(_generate_tensor_parallel, 2, str(project), first["run_directory"], want)
