@@ -36,6 +36,16 @@
 // starting with the columns whose weights are already local, so the first products run while the rest
 // of the unit, including parameters this GEMM does not use, is still arriving.
 //
+// Buffers that peers touch are double-buffered on the parity of the call number, and no call ends in an all-ranks
+// handshake. Gathering modes: a call announces "my staging buffer holds call g" (ready), every rank tells the owners
+// when it has finished reading their buffers (done = g), and call g only makes sure, before it returns, that the peers
+// reported done for call g - 1, i.e. that the staging buffer the NEXT call will overwrite is no longer read. Reducing
+// modes: the call number q and the arrival count that means "all partial tiles of call q are here" live in device
+// memory and are advanced by the last CTA of each call (so a captured CUDA graph can replay the kernel); a rank
+// stores into a peer's receive buffer of parity q & 1 only after that peer reported done for call q - 2, and reports
+// its own done = q once it has summed its rows. A rank therefore waits for a peer only when it needs that peer's
+// data, or a buffer that peer has not released yet.
+//
 // Every wait on another CTA or another GPU is bounded (see common.cuh); on expiry the kernel records a
 // status word, skips the dependent work and exits through the normal teardown.
 #include <string.h>
@@ -101,15 +111,16 @@ struct Params {
   int group_pieces;                      // pieces per group (a multiple of copy_ctas)
   int groups;                            // groups per shard
   // reduce-scatter
-  void* recv_ptrs[kMaxRanks];            // each rank's symmetric [tp, m_local, n] receive buffer (all-reduce: m_local = m)
+  void* recv_ptrs[2][kMaxRanks];         // each rank's two symmetric [tp, m_local, n] receive buffers (all-reduce: m_local = m); parity = call & 1
   unsigned int* counter_ptrs[kMaxRanks]; // each rank's symmetric arrival counters, one per source rank
-  unsigned int expected_count;           // counter value that means "all partials of this call arrived"
+  unsigned int* reduce_state;            // local: [0] reducing calls completed, [1] arrival count reached by them
   void* out_local;                       // [m_local, n] bf16 (reduce-scatter) / [m, n] bf16 (all-gather)
   long long ldc;
   // cross-rank handshakes (symmetric flag words)
   unsigned int* ready_ptrs[kMaxRanks];   // ready_ptrs[p][r] : rank r's staging buffer holds this call's data
-  unsigned int* done_ptrs[kMaxRanks];    // done_ptrs[p][r]  : rank r no longer touches rank p's buffers for this call
-  unsigned int epoch;
+  unsigned int* done_ptrs[kMaxRanks];    // done_ptrs[p][r]  : gathering: rank r has read rank p's staging buffer of that call;
+                                         //                    reducing: rank r has summed its receive buffer of that call
+  unsigned int epoch;                    // gathering modes: number of this call (host-counted)
   unsigned int* local_cta_counter;       // local, zeroed by the host before launch
   unsigned int* tile_counter;            // local, zeroed by the host before launch
   DeviceStatus* status;
@@ -265,12 +276,15 @@ __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* ba
       if (mbar_try_wait(&bars[drained % kCopyBufs], (drained / kCopyBufs) & 1)) ++drained;
     }
   }
-  // last copy CTA to finish tells the peers that it no longer reads their staging buffers, then waits for
-  // the same message from everyone so that the next call may overwrite this rank's buffer
+  // The last copy CTA to finish tells the peers that this rank no longer reads their staging buffers of this call.
+  // It does not wait for the same message about this call: the staging buffers alternate, so what must be true
+  // before this kernel returns is only that the peers are done with the PREVIOUS call's buffer, the one the next
+  // call overwrites; they said so long ago.
   if (atomicAdd(p.local_cta_counter, 1u) == (unsigned)(n_copy - 1)) {
+    __threadfence();
     for (int r = 0; r < p.tp; ++r) st_release_sys(p.done_ptrs[r] + p.rank, p.epoch);
     for (int r = 0; r < p.tp; ++r)
-      if (!wait_ge(p.done_ptrs[p.rank] + r, p.epoch, true, nullptr, p.status, 22)) break;
+      if (!wait_ge(p.done_ptrs[p.rank] + r, p.epoch - 1u, true, nullptr, p.status, 22)) break;
   }
 }
 
@@ -285,9 +299,9 @@ struct TileQueue {
 // TP * U independent 16-byte loads in flight before it adds anything (TP = 0: rank count known only at run time,
 // U loads in flight per slot).
 template <int TP, int U>
-__device__ __forceinline__ void sum_slots(const Params& p) {
+__device__ __forceinline__ void sum_slots(const Params& p, int parity) {
   const long long vec_total = (long long)p.m_local * p.n / 8;
-  const uint4* base = reinterpret_cast<const uint4*>(p.recv_ptrs[p.rank]);
+  const uint4* base = reinterpret_cast<const uint4*>(p.recv_ptrs[parity][p.rank]);
   uint4* out = reinterpret_cast<uint4*>(p.out_local);
   const long long stride = (long long)gridDim.x * kThreads;
   const int tp = TP > 0 ? TP : p.tp;
@@ -424,6 +438,12 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
   if (PAIR) cluster_sync_all();    // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // reducing modes: this call's number, receive-buffer parity and the arrival count that completes it (device state,
+  // advanced by the last CTA of the call, after every CTA has read it)
+  const bool reduces = p.mode == kReduceScatter || p.mode == kAllReduce;
+  const unsigned int reduce_call = reduces ? p.reduce_state[0] + 1u : 0u;
+  const unsigned int reduce_expected = reduces ? p.reduce_state[1] + (unsigned)((p.m_local / BM) * tiles_n * 4) : 0u;
+  const int parity = (int)(reduce_call & 1u);
 
   if (is_copy_cta) {
     // phase 1 of a copy CTA: move remote shards (thread 0 drives the bulk copies), then compute like the rest
@@ -615,6 +635,12 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
     // rank r and, once all stores have landed, tells rank r with one release. A release per tile would stall
     // the epilogue for longer than the tile's MMAs take.
     unsigned int stored_tiles = 0;   // lane r: tiles this warp stored into rank r's receive buffer
+    if (reduces) {
+      // rank `lane` must have summed (and so released) its receive buffer of this parity, last used two calls ago
+      bool released = true;
+      if (lane < p.tp) released = wait_ge(p.done_ptrs[p.rank] + lane, reduce_call - 2u, true, abort_flag, p.status, 32);
+      ok = __all_sync(0xffffffffu, released);
+    }
     for (uint32_t qi = 0; ok; ++qi) {
       const int slot = qi % kQueue;
       // pairs: the peer's slot is written and marked full by the leader, hence the cluster-scope acquire
@@ -665,7 +691,7 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
         if (bytes > 0) {
           for (int r = 0; r < p.tp; ++r) {
             const int peer = (p.rank + r) % p.tp;
-            bulk_s2g(reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[peer]) + ((long long)p.rank * p.m_local + row) * p.n + col0,
+            bulk_s2g(reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[parity][peer]) + ((long long)p.rank * p.m_local + row) * p.n + col0,
                      my_row, (uint32_t)bytes);
           }
         }
@@ -675,7 +701,7 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
           dst = reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row * p.ldc + col0;
         } else {
           // partial sums of shard `shard` go to that rank's receive buffer, slot = this rank
-          dst = reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[shard]) +
+          dst = reinterpret_cast<__nv_bfloat16*>(p.recv_ptrs[parity][shard]) +
                 ((long long)p.rank * p.m_local + (row - shard * p.m_local)) * p.n + col0;
         }
         if (bytes > 0) bulk_s2g(dst, my_row, (uint32_t)bytes);
@@ -706,27 +732,28 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
     if (threadIdx.x == 0) {
       bool ok = *abort_flag == 0;
       for (int r = 0; r < p.tp && ok; ++r)
-        ok = wait_ge(p.counter_ptrs[p.rank] + r, p.expected_count, true, nullptr, p.status, 30);
+        ok = wait_ge(p.counter_ptrs[p.rank] + r, reduce_expected, true, nullptr, p.status, 30);
       *arrived = ok ? 1 : 0;
     }
     __syncthreads();
     if (*arrived) {
       switch (p.tp) {
-        case 2: sum_slots<2, 8>(p); break;
-        case 4: sum_slots<4, 4>(p); break;
-        case 8: sum_slots<8, 2>(p); break;
-        default: sum_slots<0, 4>(p); break;
+        case 2: sum_slots<2, 8>(p, parity); break;
+        case 4: sum_slots<4, 4>(p, parity); break;
+        case 8: sum_slots<8, 2>(p, parity); break;
+        default: sum_slots<0, 4>(p, parity); break;
       }
     }
     __syncthreads();
-    // the last CTA tells the peers that this rank is done reading its receive buffer, and waits for the
-    // same from everyone: after the kernel, every rank may write into every receive buffer again
+    // The last CTA advances the device-side call state and tells the peers that this rank has summed (released) its
+    // receive buffer of this call; nobody waits here: a peer checks the release when it next needs that buffer.
     if (threadIdx.x == 0) {
       __threadfence();
       if (atomicAdd(p.local_cta_counter, 1u) == gridDim.x - 1) {
-        for (int r = 0; r < p.tp; ++r) st_release_sys(p.done_ptrs[r] + p.rank, p.epoch);
-        for (int r = 0; r < p.tp; ++r)
-          if (!wait_ge(p.done_ptrs[p.rank] + r, p.epoch, true, nullptr, p.status, 31)) break;
+        p.reduce_state[0] = reduce_call;
+        p.reduce_state[1] = reduce_expected;
+        __threadfence();
+        for (int r = 0; r < p.tp; ++r) st_release_sys(p.done_ptrs[r] + p.rank, reduce_call);
       }
     }
   }
@@ -755,14 +782,15 @@ struct AjbCommArgs {
   const void* b;                 // local weight shard
   void* out;                     // all-gather, all-reduce: [m, n]; reduce-scatter: [m / tp, n]
   void* gathered;                // all-gather: local [m, k] buffer that receives every shard
-  const void* stage_ptrs[8];
-  void* recv_ptrs[8];
+  const void* stage_ptrs[8];     // gathering modes: every rank's staging buffer of this call's parity
+  void* recv_ptrs[8];            // reducing modes: every rank's receive buffer for odd calls ...
+  void* recv_ptrs_even[8];       // ... and for even calls (the kernel knows the call number, the host need not)
   unsigned int* counter_ptrs[8];
   unsigned int* ready_ptrs[8];
-  unsigned int* done_ptrs[8];
+  unsigned int* done_ptrs[8];    // the flag words of this call's class (gathering and reducing calls count separately)
   unsigned int* shard_flags;     // local scratch of 272 words (16 + 8 ranks x 32 groups): flags, counters, group flags
-  unsigned int expected_count;
-  unsigned int epoch;
+  unsigned int* reduce_state;    // reducing modes: 2 local words, zero at start, owned by the kernel afterwards
+  unsigned int epoch;            // gathering modes: number of this gathering call (1, 2, ...)
   int a_rows;                    // all-reduce: rows of `a` that exist (<= m; the tiles above them read zeros); 0 means m
   long long shard_elems;         // gather-weight: bf16 elements per rank slice of the flat buffer (multiple of 8)
   long long b_offset_elems;      // gather-weight: first element of W inside the gathered buffer (multiple of 8)
@@ -805,7 +833,8 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   p.b_row_bytes = (long long)a.k * 2;
   for (int r = 0; r < a.tp; ++r) {
     p.stage_ptrs[r] = a.stage_ptrs[r];
-    p.recv_ptrs[r] = a.recv_ptrs[r];
+    p.recv_ptrs[1][r] = a.recv_ptrs[r];
+    p.recv_ptrs[0][r] = a.recv_ptrs_even[r];
     p.counter_ptrs[r] = a.counter_ptrs[r];
     p.ready_ptrs[r] = a.ready_ptrs[r];
     p.done_ptrs[r] = a.done_ptrs[r];
@@ -826,7 +855,8 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
     p.group_pieces = (int)(per_group * p.copy_ctas);
     p.groups = (int)((per_cta + per_group - 1) / per_group);
   }
-  p.expected_count = a.expected_count;
+  p.reduce_state = a.reduce_state;
+  AJB_REQUIRE(gathers || a.reduce_state != nullptr, "comm_gemm: reducing modes need the two state words");
   p.out_local = a.out;
   p.ldc = a.ldc;
   p.epoch = a.epoch;

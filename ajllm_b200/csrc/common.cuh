@@ -57,7 +57,8 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, CUtensorMapDataType d
                        uint64_t d2, uint64_t rows, uint64_t cols, uint64_t d2_pitch_bytes,
                        uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols);
 
-int sm_count();
+int sm_count();            // SMs a kernel launched by this host thread may fill (the thread's budget, else all)
+int sm_count_physical();   // SMs of the current device
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------------------------

@@ -295,7 +295,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 template <typename Kernel>
 static int resident_pairs(Kernel kernel) {
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((unsigned)sm_count() / 2 * 2, 1, 1);
+  config.gridDim = dim3((unsigned)sm_count_physical() / 2 * 2, 1, 1);
   config.blockDim = dim3(kThreads, 1, 1);
   config.dynamicSmemBytes = kSmemBytes;
   cudaLaunchAttribute attr[1];
@@ -308,9 +308,9 @@ static int resident_pairs(Kernel kernel) {
   int clusters = 0;
   if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
     cudaGetLastError();
-    clusters = sm_count() / 2;
+    clusters = sm_count_physical() / 2;
   }
-  return clusters < sm_count() / 2 ? clusters : sm_count() / 2;
+  return clusters < sm_count_physical() / 2 ? clusters : sm_count_physical() / 2;
 }
 
 template <bool A_MN, bool B_MN>
@@ -356,7 +356,8 @@ int capacity() {
     }
     pairs = resident_pairs(kernel);
   }
-  return pairs;
+  // under an SM budget (see sm_count) only that many SMs' worth of pairs are launched
+  return pairs < sm_count() / 2 ? pairs : sm_count() / 2;
 }
 
 int run(const void* a, const void* b, void* c, int m, int n, int k, long long lda, long long ldb, long long ldc,

@@ -184,7 +184,9 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 }
 
 // out[c] (+)= sum_r in[r, c]. One CTA owns 32 columns; its 8 warps take every 8th row (a warp reads 128
-// contiguous bytes per row) and their partial sums meet in shared memory in a fixed order.
+// contiguous bytes per row) and their partial sums meet in shared memory in a fixed order. Accumulation is one
+// atomic add per column, so two launches on different streams (two micro-batches in flight) may target the same
+// gradient buffer.
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in, float* __restrict__ out, int rows,
                                                      int cols, int accumulate) {
   __shared__ float part[8][32];
@@ -205,7 +207,8 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ i
     float s = 0.0f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) s += part[w][lane];
-    out[c] = accumulate ? out[c] + s : s;
+    if (accumulate) atomicAdd(out + c, s);
+    else out[c] = s;
   }
 }
 

@@ -56,7 +56,7 @@ int check_device_status_all() {
   return 0;
 }
 
-int sm_count() {
+int sm_count_physical() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
   if (g_sm_count[dev] == 0) {
@@ -65,6 +65,16 @@ int sm_count() {
     g_sm_count[dev] = n;
   }
   return g_sm_count[dev];
+}
+
+// SM budget of the calling host thread: kernels that size their grid from sm_count() (the persistent GEMMs, the
+// tensor-parallel GEMMs, the grid-stride pointwise kernels) then occupy at most that many SMs, so that a kernel
+// launched on another stream finds the rest of the device free at once instead of queueing behind a full wave.
+static thread_local int g_sm_budget = 0;
+
+int sm_count() {
+  const int physical = sm_count_physical();
+  return (g_sm_budget > 0 && g_sm_budget < physical) ? g_sm_budget : physical;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -138,6 +148,14 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, CUtensorMapDataType d
 }  // namespace ajb
 
 extern "C" const char* ajb_last_error() { return ajb::last_error(); }
+
+// 0 (or a value >= the device's SM count) lifts the budget. Returns the previous budget of this thread.
+extern "C" int ajb_set_sm_budget(int sms) {
+  const int previous = ajb::g_sm_budget;
+  ajb::g_sm_budget = sms > 0 ? sms : 0;
+  return previous;
+}
+extern "C" int ajb_sm_count() { return ajb::sm_count_physical(); }
 
 // Returns 0 when no kernel has reported an expired wait since the last call; otherwise the status
 // code of the first one found (and clears it). Synchronises the device.

@@ -117,6 +117,92 @@ class TransformerLM(nn.Module):
             stream = layer.forward_postnorm(stream, shape)
         return stream
 
+    # ------------------------------------------------------------------ several micro-batches in flight
+    @property
+    def interleave(self) -> int:
+        """Micro-batches that :meth:`loss_interleaved` runs side by side (1: the feature is off)."""
+        if self.moe or self.norm_placement != "pre" or self.activation_checkpointing != "none":
+            return 1
+        return int(getattr(self.tp, "interleave", 1)) if self.tp is not None else int(getattr(self, "_interleave", 1))
+
+    @property
+    def overlap_description(self) -> str | None:
+        if self.interleave > 1:
+            return (f"{self.interleave} micro-batches in flight on streams of their own; fused projections limited to the "
+                    "SM share their NVLink transfer can feed; weight gradients on a side stream")
+        return None
+
+    def _microbatch_streams(self, count: int, device) -> list:
+        streams = getattr(self, "_mb_streams", None)
+        if streams is None or len(streams) < count:
+            from ajllm_b200.ops import functional
+            # micro-batch streams outrank the weight-gradient stream: when SMs free up, the critical path goes first
+            streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(count)]
+            self._mb_streams = streams
+            if functional.wgrad_stream() is None:
+                functional.set_wgrad_stream(torch.cuda.Stream(device=device))
+        return streams[:count]
+
+    def loss_interleaved(self, batches: list[tuple[torch.Tensor, torch.Tensor]], loss_scale: float = 1.0) -> list[torch.Tensor]:
+        """:meth:`loss` of several micro-batches whose kernels are issued block by block in turn, each micro-batch on
+        a stream of its own (and, under tensor parallelism, with its own fused-communication context), so that one
+        micro-batch's link-bound projections overlap the other's attention and pointwise work. Backpropagate all
+        returned losses in ONE ``torch.autograd.backward(losses)`` call (autograd then alternates between the
+        micro-batches in the same way, each on its forward stream), then call :meth:`join_streams`.
+
+        In-place gradient accumulations that are not atomic are kept apart: weight gradients all go through one side
+        stream (:func:`ajllm_b200.ops.functional.wgrad_accumulate`), and the LM head's loss-and-gradient chunks of one
+        micro-batch start only when the previous micro-batch's are done."""
+        count = len(batches)
+        device = batches[0][0].device
+        main = torch.cuda.current_stream()
+        streams = self._microbatch_streams(count, device)
+        from ajllm_b200.ops import functional
+        functional.wgrad_stream().wait_stream(main)
+        states, shapes = [], []
+        for index, (token_ids, _) in enumerate(batches):
+            B, T = token_ids.shape
+            if T > self.context_length:
+                raise ValueError(f"Input length {T} exceeds context length {self.context_length}")
+            streams[index].wait_stream(main)
+            with torch.cuda.stream(streams[index]):
+                stream = self.token_embeddings(self._local_tokens(token_ids.reshape(-1)))
+                if self.position_embeddings is not None:
+                    positions = torch.arange(T, device=device).repeat(B)
+                    stream = stream + self.position_embeddings(self._local_tokens(positions))
+            states.append((stream, None))
+            shapes.append((B, T))
+        for layer in self.layers:
+            for index in range(count):
+                if self.tp is not None:
+                    self.tp.select(index)
+                with torch.cuda.stream(streams[index]):
+                    states[index] = layer.forward_prenorm(states[index][0], states[index][1], shapes[index])
+        losses = []
+        head_done = None
+        share = float(getattr(self, "data_parallel_share", 1.0))
+        if self.tp is not None and self.tp.size > 1:
+            share = share / self.tp.size
+        for index, (_, targets) in enumerate(batches):
+            with torch.cuda.stream(streams[index]):
+                hidden = self.final_norm.add_and_norm(states[index][0], states[index][1])[1]
+                if head_done is not None:
+                    streams[index].wait_event(head_done)
+                local_targets = self._local_tokens(targets.reshape(-1))
+                losses.append(ops.linear_cross_entropy(hidden, self.head_weight, local_targets, loss_scale) * share)
+                head_done = streams[index].record_event()
+        if self.tp is not None:
+            self.tp.select(0)
+        return losses
+
+    def join_streams(self) -> None:
+        """The current stream waits for the micro-batch streams and for the weight-gradient stream."""
+        from ajllm_b200.ops import functional
+        main = torch.cuda.current_stream()
+        for stream in getattr(self, "_mb_streams", None) or []:
+            main.wait_stream(stream)
+        functional.join_wgrad_stream()
+
     def aux_loss(self) -> torch.Tensor | None:
         terms = [layer.feed_forward.last_aux_loss for layer in self.layers
                  if isinstance(layer.feed_forward, MoEFeedForward) and layer.feed_forward.last_aux_loss is not None]

@@ -67,6 +67,46 @@ def _native(t: torch.Tensor, op: str) -> bool:
                     "fp32 master weights are kept by the optimizer - or wrap the call in ops.eager_cuda()")
 
 
+# ----------------------------------------------------------------------------- weight-gradient stream
+
+# Weight-gradient GEMMs accumulate into the optimizer's fp32 buffer and nothing in the backward pass reads their
+# result, so they need not sit on the critical path: with a side stream set, each one is issued there (ordered after
+# the kernels that produced its operands) and runs beside whatever the main stream does next - in particular beside
+# a tensor-parallel projection that is waiting on NVLink with most SMs idle. All of them share the one stream, so
+# the read-modify-write accumulations into one buffer stay serialised even when several micro-batches are in flight.
+_WGRAD_STREAM: "torch.cuda.Stream | None" = None
+
+
+def set_wgrad_stream(stream) -> None:
+    global _WGRAD_STREAM
+    _WGRAD_STREAM = stream
+
+
+def wgrad_stream():
+    return _WGRAD_STREAM
+
+
+def join_wgrad_stream() -> None:
+    """The current stream waits for every weight gradient issued so far (call before the optimizer reads them)."""
+    if _WGRAD_STREAM is not None:
+        torch.cuda.current_stream().wait_stream(_WGRAD_STREAM)
+
+
+def wgrad_accumulate(grad_out: torch.Tensor, activations: torch.Tensor, main_grad: torch.Tensor, n: int, k: int,
+                     m: int) -> None:
+    """``main_grad[n, k] += grad_out[m, n]^T @ activations[m, k]`` (fp32 accumulation in place)."""
+    side = _WGRAD_STREAM
+    if side is None or not grad_out.is_cuda:
+        gemm(grad_out, activations, main_grad, n, k, m, a_mn_major=True, b_mn_major=True, epilogue=wgrad_epilogue())
+        return
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        gemm(grad_out, activations, main_grad, n, k, m, a_mn_major=True, b_mn_major=True, epilogue=wgrad_epilogue())
+    # the operands were allocated on the producing stream: keep their memory out of reuse until the side stream is done
+    grad_out.record_stream(side)
+    activations.record_stream(side)
+
+
 # ----------------------------------------------------------------------------- GEMM
 
 
@@ -178,7 +218,7 @@ class _LinearFn(torch.autograd.Function):
             main = getattr(weight, "main_grad", None)
             if main is not None:
                 # fp32 accumulation straight into the optimizer's gradient buffer
-                gemm(g2, x2, main, n, k, m, a_mn_major=True, b_mn_major=True, epilogue=wgrad_epilogue())
+                wgrad_accumulate(g2, x2, main, n, k, m)
                 weight.main_grad_written = True
             else:
                 grad_w = torch.empty(n, k, dtype=torch.bfloat16, device=g2.device)

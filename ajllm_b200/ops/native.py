@@ -8,6 +8,7 @@ absent raises: there is no silent eager fallback on a GPU.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from pathlib import Path
@@ -31,6 +32,8 @@ _SIGNATURES: dict[str, list] = {
     "ajb_gemm_bf16_pair": [c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long,
                            c_int, c_int, c_int, c_int, c_void],
     "ajb_gemm_pair_capacity": [],
+    "ajb_set_sm_budget": [c_int],
+    "ajb_sm_count": [],
     "ajb_gemm_decode_cluster_slices": [c_int, c_int],
     "ajb_gemm_bf16_decode_cluster": [c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_void],
     "ajb_gemm_bf16_batched": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_long, c_long,
@@ -131,6 +134,21 @@ def check_status(raise_on_timeout: bool = True) -> int:
     if code > 0 and raise_on_timeout:
         raise PeerTimeout(code)
     return code
+
+
+@contextlib.contextmanager
+def sm_budget(sms: int | None):
+    """Kernels launched by this thread inside the block size their grids for at most ``sms`` SMs (``None`` or 0: no
+    change), which leaves the rest of the device to kernels running on other streams."""
+    if not sms:
+        yield
+        return
+    fn = lib().ajb_set_sm_budget
+    previous = fn(int(sms))
+    try:
+        yield
+    finally:
+        fn(int(previous))
 
 
 def stream_ptr() -> int:

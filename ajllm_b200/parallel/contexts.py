@@ -27,16 +27,43 @@ def _wants_fused(fused: bool | None, device: torch.device, size: int, switch: st
     return True if fused is None else bool(fused)
 
 
-def make_tensor_parallel(axis: AxisGroup, device: torch.device, fused: bool | None = None) -> TensorParallel | None:
+def interleaved_microbatches(tp_size: int, device: torch.device) -> int:
+    """How many micro-batches a tensor-parallel training step keeps in flight on streams of their own. From four
+    ranks on, most fused projections wait on NVLink longer than they compute (the bytes per rank stay the same while
+    the products shrink with 1 / tp), so a second micro-batch fills the idle SMs; ``AJB_TP_INTERLEAVE`` overrides."""
+    if device.type != "cuda":
+        return 1
+    forced = os.environ.get("AJB_TP_INTERLEAVE")
+    if forced is not None:
+        return max(1, int(forced))
+    return 2 if tp_size >= 4 else 1
+
+
+def make_tensor_parallel(axis: AxisGroup, device: torch.device, fused: bool | None = None,
+                         interleave: int | None = None) -> TensorParallel | None:
     """Context for ``axis`` (``None`` when the axis has one rank). A failure to set up the symmetric buffers
-    raises: a GPU run does not silently fall back to the slower composition."""
+    raises: a GPU run does not silently fall back to the slower composition. ``interleave`` (default: by group size)
+    creates that many fused contexts so that micro-batches on different streams never share buffers or flags."""
     if axis.size <= 1:
         return None
-    context = None
-    if _wants_fused(fused, device, axis.size, "AJB_FUSED_TP"):
-        from ajllm_b200.parallel.fused import FusedTensorParallel
-        context = FusedTensorParallel(axis.group, device)
-    return TensorParallel(axis.group, axis.rank, axis.size, fused=context)
+    if not _wants_fused(fused, device, axis.size, "AJB_FUSED_TP"):
+        return TensorParallel(axis.group, axis.rank, axis.size)
+    from ajllm_b200.parallel.fused import FusedTensorParallel
+    count = interleave if interleave is not None else interleaved_microbatches(axis.size, device)
+    contexts = [FusedTensorParallel(axis.group, device) for _ in range(max(1, count))]
+    if len(contexts) > 1:
+        # two fused kernels (one per micro-batch stream) must be resident together on every rank, whatever order the
+        # hardware picks them in: each gets at most half of the device
+        for context in contexts:
+            context.sm_cap = context._sms // 2 // 2 * 2 - 2
+    tp = TensorParallel(axis.group, axis.rank, axis.size, fused=contexts[0])
+    tp.fused_contexts = contexts
+    tp.interleave = len(contexts)
+    # weight-gradient GEMMs leave the critical path: they run beside the link-bound fused projections
+    from ajllm_b200.ops import functional
+    if functional.wgrad_stream() is None and os.environ.get("AJB_WGRAD_STREAM", "1") != "0":
+        functional.set_wgrad_stream(torch.cuda.Stream(device=device))
+    return tp
 
 
 def make_expert_parallel(axis: AxisGroup, device: torch.device, fused: bool | None = None) -> TensorParallel | None:

@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from ajllm_b200.ops import native
-from ajllm_b200.ops.functional import gemm, wgrad_epilogue
+from ajllm_b200.ops.functional import gemm, wgrad_accumulate
 from ajllm_b200.utils.timing import nvtx_range
 
 _MAX_RANKS = 8
@@ -33,9 +33,10 @@ class _CommArgs(ctypes.Structure):
         ("ldb", ctypes.c_longlong), ("ldc", ctypes.c_longlong),
         ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("out", ctypes.c_void_p), ("gathered", ctypes.c_void_p),
         ("stage_ptrs", ctypes.c_void_p * _MAX_RANKS), ("recv_ptrs", ctypes.c_void_p * _MAX_RANKS),
+        ("recv_ptrs_even", ctypes.c_void_p * _MAX_RANKS),
         ("counter_ptrs", ctypes.c_void_p * _MAX_RANKS), ("ready_ptrs", ctypes.c_void_p * _MAX_RANKS),
         ("done_ptrs", ctypes.c_void_p * _MAX_RANKS),
-        ("shard_flags", ctypes.c_void_p), ("expected_count", ctypes.c_uint), ("epoch", ctypes.c_uint),
+        ("shard_flags", ctypes.c_void_p), ("reduce_state", ctypes.c_void_p), ("epoch", ctypes.c_uint),
         ("a_rows", ctypes.c_int), ("shard_elems", ctypes.c_longlong), ("b_offset_elems", ctypes.c_longlong),
     ]
 
@@ -55,15 +56,28 @@ class FusedTensorParallel:
         if not 2 <= self.size <= _MAX_RANKS:
             raise ValueError("fused tensor parallelism supports 2..8 ranks")
         self.copy_ctas = int(copy_ctas or os.environ.get("AJB_COPY_CTAS", "20"))
-        self.epoch = 0
-        self.expected_count = 0
-        self._stage = self._recv = None
-        self._stage_ptrs = self._recv_ptrs = None
-        # flag words: [0:8] ready, [8:16] done, [16:24] arrival counters
+        # Buffers that peers read (staging) or write (receive) exist twice and alternate with the call number, so a
+        # call never waits for its peers to finish the same call (csrc/comm_gemm.cu explains the protocol). Gathering
+        # calls are counted here; reducing calls are counted on the device so that CUDA graphs can replay them.
+        self.gather_calls = 0
+        self._stage = [None, None]
+        self._recv = [None, None]
+        self._stage_ptrs = [None, None]
+        self._recv_ptrs = [None, None]
+        # flag words: [0:8] ready, [8:16] done (gathering), [16:24] arrival counters, [24:32] done (reducing)
         self._flags = symm_mem.empty(64, dtype=torch.int32, device=device)
         self._flags.zero_()
         self._flag_ptrs = list(symm_mem.rendezvous(self._flags, group).buffer_ptrs)
         self._local = torch.zeros(272, dtype=torch.int32, device=device)   # flags, counters, per-group arrival flags
+        self._reduce_state = torch.zeros(4, dtype=torch.int32, device=device)   # [calls completed, arrivals expected]
+        # SM budget of the fused kernels. A call whose NVLink transfer takes longer than its tensor work cannot use
+        # the whole device: it is given the share of the SMs that keeps its products in step with the link, and the
+        # rest stays free for kernels on other streams (weight gradients, a second micro-batch). "auto" computes that
+        # share per call; `sm_cap` bounds it (two fused kernels of two micro-batch streams must fit side by side).
+        mode = os.environ.get("AJB_FUSED_SM_BUDGET", "auto")
+        self.sm_budget_mode = mode if mode in ("auto", "off") else int(mode)
+        self.sm_cap: int | None = None
+        self._sms = int(native.lib().ajb_sm_count())
         torch.cuda.synchronize(device)
         dist.barrier(group)
         fn = native.lib().ajb_comm_gemm
@@ -73,26 +87,28 @@ class FusedTensorParallel:
 
     # ------------------------------------------------------------------ symmetric buffers (grown on demand)
     def _ensure(self, which: str, nbytes: int):
-        current = getattr(self, f"_{which}")
-        if current is not None and current.numel() - self.GUARD_BYTES >= nbytes:
+        """Both parities of a buffer kind grow together (a collective: every rank reaches the same sizes in the same
+        call because the shapes are the same on every rank)."""
+        buffers = getattr(self, f"_{which}")
+        if buffers[0] is not None and buffers[0].numel() - self.GUARD_BYTES >= nbytes:
             return
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
         size = max(nbytes, 1 << 20)
-        # a guard page behind the payload: peers write into this buffer with raw pointers, and a pattern that
-        # survives (`guards_intact`) shows that none of them ran past the end
-        buf = self._symm.empty(size + self.GUARD_BYTES, dtype=torch.uint8, device=self.device)
-        buf[size:].fill_(self.GUARD_PATTERN)
-        ptrs = list(self._symm.rendezvous(buf, self.group).buffer_ptrs)
-        setattr(self, f"_{which}", buf)
-        setattr(self, f"_{which}_ptrs", ptrs)
+        pointers = getattr(self, f"_{which}_ptrs")
+        for parity in (0, 1):
+            # a guard page behind the payload: peers write into this buffer with raw pointers, and a pattern that
+            # survives (`guards_intact`) shows that none of them ran past the end
+            buf = self._symm.empty(size + self.GUARD_BYTES, dtype=torch.uint8, device=self.device)
+            buf[size:].fill_(self.GUARD_PATTERN)
+            pointers[parity] = list(self._symm.rendezvous(buf, self.group).buffer_ptrs)
+            buffers[parity] = buf
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
     def guards_intact(self) -> bool:
         """True when the guard bytes behind every symmetric buffer still hold their pattern."""
-        for which in ("stage", "recv"):
-            buf = getattr(self, f"_{which}")
+        for buf in (*self._stage, *self._recv):
             if buf is not None and not bool((buf[-self.GUARD_BYTES:] == self.GUARD_PATTERN).all()):
                 return False
         return True
@@ -103,7 +119,8 @@ class FusedTensorParallel:
     def _launch(self, mode: int, m: int, n: int, k: int, b: torch.Tensor, b_mn: bool, out: torch.Tensor,
                 a: torch.Tensor | None = None, gathered: torch.Tensor | None = None, a_rows: int = 0,
                 shard_elems: int = 0, b_offset_elems: int = 0) -> None:
-        self.epoch += 1
+        gathers = mode in (MODE_ALL_GATHER, MODE_GATHER_WEIGHT)
+        parity = self.gather_calls & 1          # gathering: _next_stage() advanced the count and filled this parity
         args = _CommArgs()
         args.mode, args.m, args.n, args.k = mode, m, n, k
         args.tp, args.rank, args.b_mn_major, args.copy_ctas = self.size, self.rank, int(b_mn), self.copy_ctas
@@ -113,32 +130,57 @@ class FusedTensorParallel:
         args.b, args.out = b.data_ptr(), out.data_ptr()
         args.gathered = gathered.data_ptr() if gathered is not None else None
         args.a_rows = a_rows
-        if mode in (MODE_REDUCE_SCATTER, MODE_ALL_REDUCE):
-            rows = m if mode == MODE_ALL_REDUCE else m // self.size
-            tiles = (rows // self.BLOCK_M) * ((n + self.BLOCK_N - 1) // self.BLOCK_N)
-            self.expected_count += tiles * 4          # one count per epilogue warp per tile
         for r in range(self.size):
-            args.stage_ptrs[r] = self._stage_ptrs[r] if self._stage_ptrs else None
-            args.recv_ptrs[r] = self._recv_ptrs[r] if self._recv_ptrs else None
+            args.stage_ptrs[r] = self._stage_ptrs[parity][r] if (gathers and self._stage_ptrs[parity]) else None
+            args.recv_ptrs[r] = self._recv_ptrs[1][r] if self._recv_ptrs[1] else None
+            args.recv_ptrs_even[r] = self._recv_ptrs[0][r] if self._recv_ptrs[0] else None
             args.ready_ptrs[r] = self._flag_ptrs[r]
-            args.done_ptrs[r] = self._flag_ptrs[r] + 8 * 4
+            args.done_ptrs[r] = self._flag_ptrs[r] + (8 if gathers else 24) * 4
             args.counter_ptrs[r] = self._flag_ptrs[r] + 16 * 4
         args.shard_flags = self._local.data_ptr()
-        args.expected_count = self.expected_count & 0xFFFFFFFF
-        args.epoch = self.epoch & 0xFFFFFFFF
+        args.reduce_state = self._reduce_state.data_ptr()
+        args.epoch = self.gather_calls & 0xFFFFFFFF
         native.launch_count += 1
-        with nvtx_range(("ag_gemm", "gemm_rs", "gemm_ar", "gw_gemm")[mode]):
+        with nvtx_range(("ag_gemm", "gemm_rs", "gemm_ar", "gw_gemm")[mode]), native.sm_budget(self._budget(mode, m, n, k)):
             status = self._fn(ctypes.byref(args), native.stream_ptr())
         if status != 0:
             raise RuntimeError(f"ajb_comm_gemm failed: {native.lib().ajb_last_error().decode()}")
+
+    # measured on this kind of box: peer copies reach about 770 GB/s per direction, cuBLAS-class bf16 GEMMs about
+    # 1.39 PFLOP/s sustained
+    LINK_BYTES_PER_S, TENSOR_FLOPS = 750e9, 1.3e15
+
+    def _budget(self, mode: int, m: int, n: int, k: int) -> int | None:
+        """SMs for one fused call (None: the whole device)."""
+        if self.sm_budget_mode == "off" or mode == MODE_ALL_REDUCE:
+            return self.sm_cap
+        if self.sm_budget_mode != "auto":
+            want = int(self.sm_budget_mode)
+        else:
+            moved = (self.size - 1) / self.size * m * (n if mode == MODE_REDUCE_SCATTER else k) * 2
+            if mode == MODE_GATHER_WEIGHT:
+                moved = (self.size - 1) / self.size * n * k * 2
+            link_s = moved / self.LINK_BYTES_PER_S
+            tensor_s = 2.0 * m * n * k / self.TENSOR_FLOPS
+            share = min(1.0, 1.3 * tensor_s / max(link_s, 1e-9))      # 30 % headroom over the break-even share
+            want = max(40, int(self._sms * share) // 2 * 2)
+        if self.sm_cap is not None:
+            want = min(want, self.sm_cap)
+        return None if want >= self._sms - 8 else want
+
+    def _next_stage(self, nbytes: int) -> torch.Tensor:
+        """Opens the next gathering call: the staging buffer of its parity, free to overwrite because the previous call
+        did not return before every peer had finished reading it (two calls ago)."""
+        self._ensure("stage", nbytes)
+        self.gather_calls += 1
+        return self._stage[self.gather_calls & 1][:nbytes]
 
     # ------------------------------------------------------------------ raw fused ops
     def all_gather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, b_mn: bool, n: int, k: int):
         """Returns ``(gathered [M, k], out [M, n])`` with ``out = gathered @ op(weight)``."""
         m_local = x_local.shape[0]
         m = m_local * self.size
-        self._ensure("stage", m_local * k * 2)
-        stage = self._stage[: m_local * k * 2].view(torch.bfloat16).view(m_local, k)
+        stage = self._next_stage(m_local * k * 2).view(torch.bfloat16).view(m_local, k)
         stage.copy_(x_local)
         gathered = torch.empty(m, k, dtype=torch.bfloat16, device=self.device)
         gathered[self.rank * m_local:(self.rank + 1) * m_local].copy_(x_local)   # the kernel moves only remote shards
@@ -180,8 +222,7 @@ class FusedTensorParallel:
         if rows % self.BLOCK_M != 0 or x.dtype != torch.bfloat16 or shard.dtype != torch.bfloat16:
             raise ValueError("gather_weight_gemm needs bf16 operands and a multiple of 128 rows")
         shard_elems = shard.numel()
-        self._ensure("stage", shard_elems * 2)
-        self._stage[: shard_elems * 2].view(torch.bfloat16).copy_(shard.reshape(-1))
+        self._next_stage(shard_elems * 2).view(torch.bfloat16).copy_(shard.reshape(-1))
         flat = out_flat if out_flat is not None else torch.empty(self.size * shard_elems, dtype=torch.bfloat16, device=self.device)
         if flat.numel() != self.size * shard_elems or flat.dtype != torch.bfloat16 or not flat.is_contiguous():
             raise ValueError("out_flat must be a contiguous bf16 buffer of world * shard elements")
@@ -212,8 +253,7 @@ def _wgrad(grad_out: torch.Tensor, activations: torch.Tensor, weight: torch.Tens
     n, k = weight.shape
     main = getattr(weight, "main_grad", None)
     if main is not None:
-        gemm(grad_out, activations, main, n, k, grad_out.shape[0], a_mn_major=True, b_mn_major=True,
-             epilogue=wgrad_epilogue())
+        wgrad_accumulate(grad_out, activations, main, n, k, grad_out.shape[0])
         weight.main_grad_written = True
         return None
     out = torch.empty(n, k, dtype=torch.bfloat16, device=grad_out.device)

@@ -71,6 +71,13 @@ class TensorParallel:
         self.size = size if size is not None else (dist.get_world_size(group) if group is not None else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if group is not None else 0)
         self.fused = fused          # optional ajllm_b200.parallel.fused.FusedTensorParallel
+        # one fused context per micro-batch in flight (each has its own symmetric buffers and flag words);
+        # `select(i)` makes context i the one the next forward calls use (backward passes keep the one they saw)
+        self.fused_contexts = [fused] if fused is not None else []
+
+    def select(self, index: int) -> None:
+        if self.fused_contexts:
+            self.fused = self.fused_contexts[index % len(self.fused_contexts)]
 
     # ----- layout helpers
     def local_rows(self, flat: torch.Tensor) -> torch.Tensor:

@@ -209,7 +209,15 @@ class FlatAdamW:
         self._class_sumsq = torch.zeros(len(self.classes), dtype=torch.float32, device=device)
 
     # -------------------------------------------------------------- gradient plumbing
+    def _join_side_streams(self) -> None:
+        """Weight-gradient GEMMs may run on a side stream (``ops.functional.wgrad_accumulate``): everything that reads
+        or clears the gradient buffer first makes the current stream wait for them."""
+        if self.grad.is_cuda:
+            from ajllm_b200.ops import functional
+            functional.join_wgrad_stream()
+
     def zero_grad(self, set_to_none: bool = True) -> None:
+        self._join_side_streams()
         self.grad.zero_()
         for _, p in self.named_params:
             p.grad = None
@@ -247,6 +255,7 @@ class FlatAdamW:
     @torch.no_grad()
     def step(self, max_norm: float = 0.0) -> torch.Tensor:
         """Reduce, clip by global norm, update. Returns the (pre-clip) gradient norm as a device scalar."""
+        self._join_side_streams()
         self.collect_grads()
         self.reduce_grads()
         sumsq = self.global_sumsq()

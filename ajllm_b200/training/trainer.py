@@ -55,12 +55,27 @@ def optimizer_step(model, optimizer, next_batch, accumulation: int, gradient_cli
     device scalars (the loss is the mean over the micro-batches); nothing is read back to the host."""
     optimizer.zero_grad(set_to_none=True)
     total = None
+    together = int(getattr(model, "interleave", 1))
+    if together > 1 and accumulation % together == 0:
+        # several micro-batches in flight: their kernels alternate block by block on streams of their own
+        for _ in range(accumulation // together):
+            batches = [next_batch() for _ in range(together)]
+            losses = model.loss_interleaved(batches, 1.0 / accumulation)
+            torch.autograd.backward(losses)
+            model.join_streams()
+            for loss in losses:
+                piece = loss.detach().float() / accumulation
+                total = piece if total is None else total + piece
+        return total, optimizer.step(gradient_clip)
     for _ in range(accumulation):
         inputs, targets = next_batch()
         loss = model.loss(inputs, targets, 1.0 / accumulation)
         loss.backward()
         piece = loss.detach().float() / accumulation
         total = piece if total is None else total + piece
+    join = getattr(model, "join_streams", None)
+    if join is not None and total is not None and total.is_cuda:
+        join()              # weight gradients issued on the side stream are complete before the optimizer reads them
     return total, optimizer.step(gradient_clip)
 
 

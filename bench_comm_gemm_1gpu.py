@@ -14,60 +14,14 @@ free, not how well it hides a real one (that is `bench.py --gpus N` and tests/te
 from __future__ import annotations
 
 import argparse
-import ctypes
 
 import torch
 
 from ajllm_b200.ops import native
-from ajllm_b200.parallel.fused import (MODE_ALL_GATHER, MODE_ALL_REDUCE, MODE_GATHER_WEIGHT, MODE_REDUCE_SCATTER,
-                                       _CommArgs)
+from ajllm_b200.parallel.emulated_group import (MODE_ALL_GATHER, MODE_ALL_REDUCE, MODE_GATHER_WEIGHT,
+                                                MODE_REDUCE_SCATTER, EmulatedGroup)
 
-TP, RANK = 2, 0          # --tp 4 / 8 emulate rank 0 of a larger group (all-gather and reduce-scatter modes)
-
-
-class Emulated:
-    def __init__(self, device) -> None:
-        self.device = device
-        # one flag array per "rank": [0:8] ready, [8:16] done, [16:24] arrival counters
-        self.flags = [torch.zeros(64, dtype=torch.int32, device=device) for _ in range(TP)]
-        self.local = torch.zeros(272, dtype=torch.int32, device=device)
-        self.epoch = 0
-        self.expected = 0
-        fn = native.lib().ajb_comm_gemm
-        fn.argtypes = [ctypes.POINTER(_CommArgs), ctypes.c_void_p]
-        fn.restype = ctypes.c_int
-        self.fn = fn
-
-    def launch(self, mode, m, n, k, out, b=None, b_mn=False, a=None, gathered=None, stage=None, recv=None,
-               tiles_for_count=0, a_rows=0, shard_elems=0, b_offset=0):
-        self.epoch += 1
-        self.expected += tiles_for_count * 4
-        # what the absent peers would have written into rank 0's words
-        self.flags[0][1:TP] = self.epoch                 # ready[r]
-        self.flags[0][8 + 1:8 + TP] = self.epoch         # done[r]
-        self.flags[0][16 + 1:16 + TP] = self.expected    # arrivals from rank r
-        args = _CommArgs()
-        args.mode, args.m, args.n, args.k = mode, m, n, k
-        args.tp, args.rank, args.b_mn_major, args.copy_ctas = TP, RANK, int(b_mn), 20
-        args.ldb = b.stride(0) if (b is not None and b.dim() == 2) else k
-        args.ldc = out.stride(0)
-        args.a = a.data_ptr() if a is not None else None
-        args.b = b.data_ptr() if b is not None else None
-        args.out = out.data_ptr()
-        args.gathered = gathered.data_ptr() if gathered is not None else None
-        for r in range(TP):
-            args.stage_ptrs[r] = stage[r].data_ptr() if stage is not None else None
-            args.recv_ptrs[r] = recv[r].data_ptr() if recv is not None else None
-            args.ready_ptrs[r] = self.flags[r].data_ptr()
-            args.done_ptrs[r] = self.flags[r].data_ptr() + 8 * 4
-            args.counter_ptrs[r] = self.flags[r].data_ptr() + 16 * 4
-        args.shard_flags = self.local.data_ptr()
-        args.expected_count = self.expected & 0xFFFFFFFF
-        args.epoch = self.epoch & 0xFFFFFFFF
-        args.a_rows, args.shard_elems, args.b_offset_elems = a_rows, shard_elems, b_offset
-        status = self.fn(ctypes.byref(args), native.stream_ptr())
-        if status != 0:
-            raise RuntimeError(native.lib().ajb_last_error().decode())
+TP = 2          # --tp 4 / 8 emulate rank 0 of a larger group (all-gather and reduce-scatter modes)
 
 
 def timeit(fn, iters=5, warmup=2):
@@ -96,7 +50,7 @@ def main() -> None:
     TP = args.tp
     dev = torch.device("cuda")
     torch.manual_seed(0)
-    em = Emulated(dev)
+    em = EmulatedGroup(dev, TP)
     m, n, k = (8192, 2048, 2048) if args.small else (16384, 4096, 4096)
     m_local = m // TP
     bf = torch.bfloat16
