@@ -16,6 +16,11 @@
 // partial row sums) are exchanged through shared memory; P is assembled in rows 0..31 of the operand
 // tile, so only the first quarter of O is meaningful and the first warp alone rescales and stores it.
 //
+// Long contexts at small batch: with `splits` > 1 the tiles of a sequence are divided over `splits` CTAs (grid z).
+// Each writes its un-normalised fp32 output rows and (reference maximum, row sum) to a workspace, and a second small
+// kernel merges the parts with the usual log-sum-exp weights. One CTA per (sequence, KV head) walks a 4k context as
+// 32 dependent tile steps while most SMs idle; eight CTAs walk four steps each.
+//
 // Layouts: q [tokens, Hq, hd] bf16 (rows of a sequence are contiguous, `q_start[seq]` is its first
 // row); caches [num_blocks, block_size = 16, Hkv, hd] bf16; block_tables [num_seqs, max_blocks] int32;
 // out like q.
@@ -49,6 +54,9 @@ struct Params {
   int max_blocks;
   int heads, kv_heads, q_len;
   float scale;
+  int splits;                 // CTAs per (sequence, KV head); > 1: partial results go to the workspace
+  float* part_o;              // [tokens, Hq, splits, hd] fp32, un-normalised
+  float2* part_ml;            // [tokens, Hq, splits] (reference maximum in log2 units, row sum); sum 0 = no keys seen
   DeviceStatus* status;
 };
 
@@ -85,7 +93,11 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int group = p.heads / p.kv_heads;
   const int rows = group * p.q_len;                 // real rows, packed head-major: row = h_in_group * q_len + i
   const int ctx = p.context_lens[seq];
-  const int n_tiles = (ctx + TILE - 1) / TILE;
+  const int all_tiles = (ctx + TILE - 1) / TILE;
+  // this CTA's share of the sequence's tiles: [t0, t0 + n_tiles)
+  const int per_split = (all_tiles + p.splits - 1) / p.splits;
+  const int t0 = min(all_tiles, (int)blockIdx.z * per_split);
+  const int n_tiles = min(all_tiles - t0, per_split);
   const int active_quarters = (rows + 31) / 32;
   const int* table = p.block_tables + (size_t)seq * p.max_blocks;
 
@@ -135,7 +147,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         uint8_t* sK = sKV + s * 2 * C::kTile;
         uint8_t* sV = sK + C::kTile;
         mbar_arrive_expect_tx(&kv_full[s], 2 * C::kTile);
-        const int first_block = j * (TILE / BLOCK_TOKENS);
+        const int first_block = (t0 + j) * (TILE / BLOCK_TOKENS);
         const int blocks_here = min(TILE / BLOCK_TOKENS, (ctx + BLOCK_TOKENS - 1) / BLOCK_TOKENS - first_block);
 #pragma unroll 1
         for (int b = 0; b < TILE / BLOCK_TOKENS; ++b) {
@@ -220,7 +232,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int s = j & 1;
       if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kPagedKernelId, 6)) { ok = false; break; }
       tc_fence_after_sync();
-      const int k0 = j * TILE + quarter * 32;
+      const int k0 = (t0 + j) * TILE + quarter * 32;
       uint32_t sv[32];
       tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * TILE + quarter * 32), sv);
       tc_wait_ld();
@@ -280,11 +292,29 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     float sums[4] = {0.f, 0.f, 0.f, 0.f};
     if (ok && n_tiles > 0) ok = exchange((uint32_t)n_tiles, l_run, sums);
+    const size_t out_row = (size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h;
+    if (p.splits > 1 && quarter == 0 && real && (n_tiles == 0 || !ok))
+      p.part_ml[out_row * p.splits + blockIdx.z] = make_float2(0.0f, 0.0f);        // nothing to merge from this part
     if (ok && quarter == 0 && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
       tc_fence_after_sync();
       const float l_all = (sums[0] + sums[1]) + (sums[2] + sums[3]);
       const float inv_l = l_all > 0.0f ? 1.0f / l_all : 0.0f;
-      __nv_bfloat16* dst = p.out + ((size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h) * HD;
+      __nv_bfloat16* dst = p.out + out_row * HD;
+      if (p.splits > 1) {
+        if (real) p.part_ml[out_row * p.splits + blockIdx.z] = make_float2(m_run == -INFINITY ? 0.0f : m_run * sl, l_all);
+        float* part = p.part_o + (out_row * p.splits + blockIdx.z) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
+          tc_wait_ld();
+          if (real) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<uint4*>(part + c * 32)[i] = make_uint4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t ov[32];
@@ -318,7 +348,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int s = j & 1;
       if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kPagedKernelId, 6)) { ok = false; break; }
       tc_fence_after_sync();
-      const int k0 = j * TILE;
+      const int k0 = (t0 + j) * TILE;
       uint32_t pk[64];
       float alpha = 1.0f;
       bool moved = false;
@@ -388,11 +418,28 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
     }
+    const size_t out_row = (size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h;
+    if (p.splits > 1 && real && (n_tiles == 0 || !ok))
+      p.part_ml[out_row * p.splits + blockIdx.z] = make_float2(0.0f, 0.0f);        // nothing to merge from this part
     if (ok && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
       tc_fence_after_sync();
-      if (active) {
+      if (active && p.splits > 1) {
+        if (real) p.part_ml[out_row * p.splits + blockIdx.z] = make_float2(m_run == -INFINITY ? 0.0f : m_run * sl, l_run);
+        float* part = p.part_o + (out_row * p.splits + blockIdx.z) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::kOCol + c * 32), ov);
+          tc_wait_ld();
+          if (real) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<uint4*>(part + c * 32)[i] = make_uint4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
+          }
+        }
+      } else if (active) {
         const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-        __nv_bfloat16* dst = p.out + ((size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h) * HD;
+        __nv_bfloat16* dst = p.out + out_row * HD;
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t ov[32];
@@ -422,10 +469,47 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
 }
 
+// out[row, head, :] = sum_z w_z O_z / sum_z w_z l_z with w_z = 2^(m_z - max m): one warp per (row, head).
+template <int HD>
+__global__ void merge_splits_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, int q_len, int heads,
+                                    int splits, long long pairs /* sequences * q_len * heads */) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  if (w >= pairs) return;
+  const long long local_row = w / heads;
+  const int head = (int)(w - local_row * heads);
+  const int seq = (int)(local_row / q_len), i = (int)(local_row - (long long)seq * q_len);
+  const size_t out_row = (size_t)(q_start[seq] + i) * heads + head;
+  float m_max = -INFINITY;
+  for (int z = 0; z < splits; ++z) {
+    const float2 ml = part_ml[out_row * splits + z];
+    if (ml.y > 0.0f) m_max = fmaxf(m_max, ml.x);
+  }
+  constexpr int kPerLane = HD / 32;
+  float acc[kPerLane];
+#pragma unroll
+  for (int c = 0; c < kPerLane; ++c) acc[c] = 0.0f;
+  float l_all = 0.0f;
+  for (int z = 0; z < splits; ++z) {
+    const float2 ml = part_ml[out_row * splits + z];
+    if (!(ml.y > 0.0f)) continue;
+    const float weight = exp2f(ml.x - m_max);
+    l_all += weight * ml.y;
+    const float* src = part_o + (out_row * splits + z) * HD;
+#pragma unroll
+    for (int c = 0; c < kPerLane; ++c) acc[c] += weight * src[c * 32 + lane];
+  }
+  const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+#pragma unroll
+  for (int c = 0; c < kPerLane; ++c) out[out_row * HD + c * 32 + lane] = __float2bfloat16(acc[c] * inv);
+}
+
 template <int HD>
 static int launch(const void* q, const void* k_cache, const void* v_cache, const void* block_tables,
                   const void* context_lens, const void* q_start, void* out, int num_seqs, int num_blocks, int max_blocks,
-                  int heads, int kv_heads, int q_len, float scale, cudaStream_t stream) {
+                  int heads, int kv_heads, int q_len, float scale, int splits, void* part_o, void* part_ml,
+                  cudaStream_t stream) {
   using C = Cfg<HD>;
   CUtensorMap map_k, map_v;
   const uint64_t row_pitch = (uint64_t)kv_heads * HD * 2;
@@ -445,11 +529,21 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, const
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_tables = (const int*)block_tables;
   p.context_lens = (const int*)context_lens; p.q_start = (const int*)q_start; p.max_blocks = max_blocks;
   p.heads = heads; p.kv_heads = kv_heads; p.q_len = q_len; p.scale = scale; p.status = device_status_buffer();
+  p.splits = splits; p.part_o = (float*)part_o; p.part_ml = (float2*)part_ml;
   if ((heads / kv_heads) * q_len <= 32)
-    paged_attention_kernel<HD, true><<<dim3(num_seqs, kv_heads), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
+    paged_attention_kernel<HD, true><<<dim3(num_seqs, kv_heads, splits), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
   else
-    paged_attention_kernel<HD, false><<<dim3(num_seqs, kv_heads), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
+    paged_attention_kernel<HD, false><<<dim3(num_seqs, kv_heads, splits), kThreads, C::kSmem, stream>>>(map_k, map_v, p);
   AJB_CUDA_OK(cudaGetLastError());
+  if (splits > 1) {
+    const long long pairs = (long long)num_seqs * q_len * heads;
+    const int threads = 128;
+    const long long blocks = (pairs * 32 + threads - 1) / threads;
+    merge_splits_kernel<HD><<<(unsigned)blocks, threads, 0, stream>>>((const float*)part_o, (const float2*)part_ml,
+                                                                      (__nv_bfloat16*)out, (const int*)q_start, q_len, heads,
+                                                                      splits, pairs);
+    AJB_CUDA_OK(cudaGetLastError());
+  }
   return 0;
 }
 
@@ -457,11 +551,16 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, const
 }  // namespace ajb
 
 // Every sequence of the launch contributes exactly q_len new rows; (heads / kv_heads) * q_len <= 64.
+// splits > 1 divides every sequence's tiles over that many CTAs: part_o must hold rows * heads * splits * head_dim
+// floats and part_ml rows * heads * splits * 2 floats, where rows = the total number of query rows of the batch.
 extern "C" int ajb_paged_attention(const void* q, const void* k_cache, const void* v_cache, const void* block_tables,
                                    const void* context_lens, const void* q_start, void* out, int num_seqs,
                                    int num_blocks, int block_size, int max_blocks, int heads, int kv_heads,
-                                   int head_dim, int q_len, float scale, void* stream) {
+                                   int head_dim, int q_len, float scale, int splits, void* part_o, void* part_ml,
+                                   void* stream) {
   using namespace ajb;
+  AJB_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+              "paged attention: splits must be in [1, 64] and come with a workspace");
   AJB_REQUIRE(block_size == paged::BLOCK_TOKENS, "paged attention: cache block size must be %d", paged::BLOCK_TOKENS);
   AJB_REQUIRE(heads % kv_heads == 0 && (heads / kv_heads) * q_len <= paged::kMaxRows && q_len >= 1,
               "paged attention: (heads / kv_heads) * q_len = %d exceeds %d", (heads / kv_heads) * q_len, paged::kMaxRows);
@@ -469,10 +568,10 @@ extern "C" int ajb_paged_attention(const void* q, const void* k_cache, const voi
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (head_dim == 128)
     return paged::launch<128>(q, k_cache, v_cache, block_tables, context_lens, q_start, out, num_seqs, num_blocks,
-                              max_blocks, heads, kv_heads, q_len, scale, s);
+                              max_blocks, heads, kv_heads, q_len, scale, splits, part_o, part_ml, s);
   if (head_dim == 64)
     return paged::launch<64>(q, k_cache, v_cache, block_tables, context_lens, q_start, out, num_seqs, num_blocks,
-                             max_blocks, heads, kv_heads, q_len, scale, s);
+                             max_blocks, heads, kv_heads, q_len, scale, splits, part_o, part_ml, s);
   set_error("paged attention: head_dim %d is not supported (64 and 128 are)", head_dim);
   return 2;
 }

@@ -285,6 +285,26 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate_up, con
   }
 }
 
+// Head repacking: rows of `heads` heads of `src_hd` elements each -> rows of `heads` heads of `dst_hd` elements. A wider
+// destination head is zero-filled behind the copied part, a narrower one keeps the leading part. The attention kernels
+// are built for 64- and 128-wide heads; other head sizes (the reference's own flagship has 32) run on them through
+// this zero padding, which changes neither the scores (zeros add nothing to q . k) nor the kept output columns.
+__global__ void repack_heads_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows,
+                                    int heads, int src_hd, int dst_hd, long long src_stride, long long dst_stride) {
+  const int dst_vec = dst_hd >> 3, src_vec = src_hd >> 3;
+  const long long per_row = (long long)heads * dst_vec;
+  const long long total = rows * per_row;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long row = idx / per_row;
+    const int rem = (int)(idx - row * per_row);
+    const int head = rem / dst_vec, v = rem - head * dst_vec;
+    uint4 q = make_uint4(0u, 0u, 0u, 0u);
+    if (v < src_vec) q = reinterpret_cast<const uint4*>(src + row * src_stride + (long long)head * src_hd)[v];
+    reinterpret_cast<uint4*>(dst + row * dst_stride + (long long)head * dst_hd)[v] = q;
+  }
+}
+
 // SiLU feed-forward activation (the reference's non-gated option): y = x * sigmoid(x); with `dy` the derivative
 // dy * sigmoid(x) * (1 + x * (1 - sigmoid(x))) is written instead.
 __global__ void silu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
@@ -568,6 +588,18 @@ extern "C" int ajb_swiglu_bwd(const void* gate_up, const void* dact, void* dgate
   if (total <= 0) return 0;
   swiglu_bwd_kernel<<<grid_for(total, 256), 256, 0, STREAM(stream)>>>((const bf16*)gate_up, (const bf16*)dact,
                                                                        (bf16*)dgate_up, total);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ajb_repack_heads(const void* src, void* dst, long long rows, int heads, int src_hd, int dst_hd,
+                                long long src_stride, long long dst_stride, void* stream) {
+  AJB_REQUIRE(src_hd % 8 == 0 && dst_hd % 8 == 0 && src_stride % 8 == 0 && dst_stride % 8 == 0,
+              "repack_heads: head sizes and row strides must be multiples of 8 elements");
+  const long long total = rows * heads * (dst_hd / 8);
+  if (total <= 0) return 0;
+  repack_heads_kernel<<<grid_for(total, 256), 256, 0, STREAM(stream)>>>((const bf16*)src, (bf16*)dst, rows, heads, src_hd,
+                                                                        dst_hd, src_stride, dst_stride);
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }

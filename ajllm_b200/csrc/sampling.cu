@@ -61,13 +61,69 @@ struct RowStats {
   int argmax;
 };
 
+// Pass 1 for small batches: `chunks` CTAs per row each find the maximum (and its first index) of one slice of the
+// vocabulary, so that a handful of rows over a 128k vocabulary are read by a hundred CTAs instead of a handful.
+// part[(row * chunks + c) * 2] = {max as float bits, index}.
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float* __restrict__ logits, long long row_pitch, int vocab, int chunks, int* __restrict__ part) {
+  __shared__ float red[32];
+  __shared__ int red_i[32];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float* row = logits + (size_t)r * row_pitch;
+  const int per = ((vocab + chunks - 1) / chunks + 3) & ~3;
+  const int lo = c * per, hi = min(vocab, lo + per);
+  float mx = -INFINITY;
+  int arg = 0x7fffffff;
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  if (vec) {
+    const int hi4 = lo + ((hi - lo) & ~3);
+    for (int i = lo + 4 * (int)threadIdx.x; i < hi4; i += 4 * (int)blockDim.x) {
+      const float4 v = *reinterpret_cast<const float4*>(row + i);
+      if (v.x > mx) { mx = v.x; arg = i; }
+      if (v.y > mx) { mx = v.y; arg = i + 1; }
+      if (v.z > mx) { mx = v.z; arg = i + 2; }
+      if (v.w > mx) { mx = v.w; arg = i + 3; }
+    }
+    for (int i = hi4 + (int)threadIdx.x; i < hi; i += (int)blockDim.x) {
+      const float x = row[i];
+      if (x > mx) { mx = x; arg = i; }
+    }
+  } else {
+    for (int i = lo + (int)threadIdx.x; i < hi; i += (int)blockDim.x) {
+      const float x = row[i];
+      if (x > mx) { mx = x; arg = i; }
+    }
+  }
+  const float gmax = block_max(mx, red);
+  int cand = (mx == gmax && lo < hi) ? arg : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red_i[threadIdx.x >> 5] = cand;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int best = 0x7fffffff;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) best = min(best, red_i[w]);
+    part[((size_t)r * chunks + c) * 2] = __float_as_int(gmax);
+    part[((size_t)r * chunks + c) * 2 + 1] = best;
+  }
+}
+
 // Greedy rows (`need_sum` false) only need the argmax, i.e. one pass over the row. Rows that start on a 16-byte
 // boundary with a vocabulary that is a multiple of 4 are read as float4.
-__device__ RowStats row_stats(const float* __restrict__ row, int vocab, float inv_t, bool need_sum, float* red, int* red_i) {
+// With `part` (pass 1 done by argmax_chunks_kernel) the maximum comes from the `chunks` partial results.
+__device__ RowStats row_stats(const float* __restrict__ row, int vocab, float inv_t, bool need_sum, float* red, int* red_i,
+                              const int* __restrict__ part = nullptr, int chunks = 0) {
   float mx = -INFINITY;
   int arg = 0;
   const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0 && (vocab & 3) == 0;
-  if (vec) {
+  if (part != nullptr) {
+    // chunks are in index order, so a strict comparison keeps the smallest index among equal maxima
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+      const float v = __int_as_float(part[2 * c]);
+      if (v > mx) { mx = v; arg = part[2 * c + 1]; }
+    }
+  } else if (vec) {
     const float4* row4 = reinterpret_cast<const float4*>(row);
     for (int i = threadIdx.x; i < (vocab >> 2); i += blockDim.x) {
       const float4 v = row4[i];
@@ -165,14 +221,16 @@ __device__ int pick_by_mass(int vocab, float target, Weight weight, float* red, 
 __global__ void __launch_bounds__(kThreads)
 sample_rows_kernel(const float* __restrict__ logits, long long row_pitch, int vocab, const float* __restrict__ temperature,
                    const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
-                   const unsigned long long* __restrict__ counters, int* __restrict__ out_tokens) {
+                   const unsigned long long* __restrict__ counters, int* __restrict__ out_tokens,
+                   const int* __restrict__ part, int chunks) {
   __shared__ float red[32];
   __shared__ int red_i[32];
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_pitch;
   const float temp = temperature[r];
   const float inv_t = temp > 0.0f ? 1.0f / temp : 1.0f;
-  const RowStats st = row_stats(row, vocab, inv_t, temp > 0.0f, red, red_i);
+  const RowStats st = row_stats(row, vocab, inv_t, temp > 0.0f, red, red_i,
+                                part != nullptr ? part + (size_t)r * chunks * 2 : nullptr, chunks);
   if (temp <= 0.0f) {
     if (threadIdx.x == 0) out_tokens[r] = st.argmax;
     return;
@@ -278,14 +336,26 @@ spec_verify_kernel(const float* __restrict__ target_logits, const float* __restr
 }  // namespace sampling
 }  // namespace ajb
 
+// chunks > 1 (with `workspace` of rows * chunks * 2 ints): the row maxima are found by rows * chunks CTAs first, and
+// greedy rows then only combine `chunks` partial results.
 extern "C" int ajb_sample_rows(const void* logits, long long row_pitch, int rows, int vocab, const void* temperature,
                                const void* top_p, const void* seeds, const void* counters, void* out_tokens,
-                               void* stream) {
+                               int chunks, void* workspace, void* stream) {
   using namespace ajb;
   if (rows <= 0) return 0;
-  sampling::sample_rows_kernel<<<rows, sampling::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  AJB_REQUIRE(chunks >= 1 && chunks <= 512 && (chunks == 1 || workspace != nullptr),
+              "sample_rows: chunks must be in [1, 512] and come with a workspace");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int* part = nullptr;
+  if (chunks > 1) {
+    sampling::argmax_chunks_kernel<<<dim3(chunks, rows), 256, 0, s>>>((const float*)logits, row_pitch, vocab, chunks,
+                                                                      (int*)workspace);
+    AJB_CUDA_OK(cudaGetLastError());
+    part = (const int*)workspace;
+  }
+  sampling::sample_rows_kernel<<<rows, sampling::kThreads, 0, s>>>(
       (const float*)logits, row_pitch, vocab, (const float*)temperature, (const float*)top_p,
-      (const unsigned long long*)seeds, (const unsigned long long*)counters, (int*)out_tokens);
+      (const unsigned long long*)seeds, (const unsigned long long*)counters, (int*)out_tokens, part, chunks);
   AJB_CUDA_OK(cudaGetLastError());
   return 0;
 }

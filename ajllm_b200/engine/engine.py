@@ -54,6 +54,14 @@ def default_num_blocks(model, block_size: int, max_num_seqs: int) -> int:
     return max(per_seq + 1, min(max_num_seqs * per_seq, 1 << 16))
 
 
+def _cache_head_dim(head_dim: int, dtype, device) -> int:
+    """Width of a cached head: on a GPU the attention kernels' head size (other sizes are stored zero-padded)."""
+    if device.type == "cuda" and dtype == torch.bfloat16:
+        from ajllm_b200.ops.functional import kernel_head_dim
+        return kernel_head_dim(head_dim)
+    return head_dim
+
+
 class LLMEngine:
     def __init__(self, model, block_size: int = 16, num_blocks: int | None = None, max_num_seqs: int = 256,
                  max_batched_tokens: int = 8192, quantization: str | None = None, draft_model=None,
@@ -64,8 +72,8 @@ class LLMEngine:
         dtype = next(model.parameters()).dtype
         attn = model.layers[0].attention
         num_blocks = num_blocks or default_num_blocks(model, block_size, max_num_seqs)
-        self.cache = PagedKVCache(model.num_layers, num_blocks, block_size, attn.num_kv_heads, attn.head_dim,
-                                  dtype, device)
+        self.cache = PagedKVCache(model.num_layers, num_blocks, block_size, attn.num_kv_heads,
+                                  _cache_head_dim(attn.head_dim, dtype, device), dtype, device)
         self.runner = ModelRunner(model, self.cache, quantization)
         self.scheduler = Scheduler(self.cache, max_num_seqs, max_batched_tokens, model.context_length)
         self.k = num_speculative_tokens if draft_model is not None else 0
@@ -74,7 +82,7 @@ class LLMEngine:
             draft_model.eval()
             dattn = draft_model.layers[0].attention
             self.draft_cache = PagedKVCache(draft_model.num_layers, num_blocks, block_size, dattn.num_kv_heads,
-                                            dattn.head_dim, dtype, device)
+                                            _cache_head_dim(dattn.head_dim, dtype, device), dtype, device)
             self.draft_runner = ModelRunner(draft_model, self.draft_cache, None)
         self.stats = EngineStats()
         self.seed = seed

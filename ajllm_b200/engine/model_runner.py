@@ -7,11 +7,14 @@ sequence up to and including itself. Under tensor parallelism activations are re
 holds its own heads of the cache, and the two row-parallel projections end in an all-reduce.
 Weights may be bf16 tensors or block-scaled fp8 (:mod:`ajllm_b200.engine.quant`).
 
-Pure decoding steps (one new token per sequence) on one GPU are replayed from CUDA graphs: a step is a few
-hundred short kernels, and launching them one by one costs more host time than they run. One graph per
-batch-size bucket is captured on first use over static input buffers (token ids, positions, cache slots,
-block tables, context lengths); a step copies its inputs into those buffers and replays. Rows that pad a
-batch up to its bucket read and write a scratch cache block that no sequence owns.
+Pure decoding steps (one new token per sequence) are replayed from CUDA graphs: a step is a few hundred short
+kernels, and launching them one by one costs more host time than they run. One graph per batch-size bucket is
+captured on first use over static input buffers (token ids, positions, cache slots, block tables, context
+lengths); a step copies its inputs into those buffers and replays. Rows that pad a batch up to its bucket read
+and write a scratch cache block that no sequence owns. Under tensor parallelism the graphs contain the fused
+GEMM -> all-reduce kernels: their call numbers and arrival counts live in device memory and advance with every
+execution, captured or not, so every rank replays the same graph and the kernels pair up as in eager mode
+(NCCL collectives are not captured: without the fused kernels, tensor-parallel decoding launches step by step).
 """
 
 from __future__ import annotations
@@ -69,6 +72,12 @@ class ModelRunner:
         self.dtype = next(model.parameters()).dtype
         if model.norm_placement != "pre":
             raise ValueError("the serving engine supports pre-norm models")
+        # GPU kernels run at 64- or 128-wide heads: other head sizes are zero-padded after the rotation, cached padded,
+        # and the attention output is cut back (the softmax scale stays that of the true head size)
+        attn0 = model.layers[0].attention
+        self.head_dim = attn0.head_dim
+        self.kernel_head_dim = cache.head_dim
+        self.softmax_scale = 1.0 / (self.head_dim ** 0.5)
         self.weights = []
         for layer in model.layers:
             entry = {"qkv": layer.attention.qkv_proj.data, "out": layer.attention.output_proj.data}
@@ -86,11 +95,15 @@ class ModelRunner:
             elif quantization not in (None, "none", "bf16"):
                 raise ValueError(f"unknown quantization '{quantization}'")
             self.weights.append(entry)
-        # decoding graphs: one GPU, dense feed-forward blocks (expert routing has data-dependent shapes)
+        # decoding graphs: dense feed-forward blocks (expert routing has data-dependent shapes); with several ranks only
+        # when every row-parallel projection runs as the fused kernel (bf16 weights)
         self._graphs: dict[int, _DecodeGraph] = {}
         self._scratch_block: int | None = None
+        single = self.tp is None or self.tp.size == 1
+        fused_everywhere = (not single and getattr(self.tp, "fused", None) is not None
+                            and quantization in (None, "none", "bf16"))
         self.use_graphs = (self.device.type == "cuda" and self.dtype == torch.bfloat16
-                           and (self.tp is None or self.tp.size == 1)
+                           and (single or fused_everywhere)
                            and not any("moe" in w for w in self.weights)
                            and os.environ.get("AJB_DECODE_GRAPHS", "1") != "0")
 
@@ -113,15 +126,17 @@ class ModelRunner:
             qkv = _matmul(normed, w["qkv"])
             if attn.use_rope:
                 serving.rope_packed_(qkv, attn.rope_cos, attn.rope_sin, g.pos32, attn.num_heads, attn.num_kv_heads, attn.head_dim)
-            q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
+            qkv = self._padded_heads(qkv, attn)
+            q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, self.kernel_head_dim)
             cache.write(index, g.slots, k, v)
-            attended = serving.paged_attention_planned(q.contiguous(), cache.keys[index], cache.values[index], plan)
-            attended = _matmul(attended.reshape(n, -1), w["out"])
+            attended = serving.paged_attention_planned(q.contiguous(), cache.keys[index], cache.values[index], plan,
+                                                       self.softmax_scale)
+            attended = self._row_parallel(self._true_heads(attended.reshape(n, -1), attn), w["out"])
             stream, normed = layer.norm2.add_and_norm(stream, attended)
             if "w13" in w:
-                pending = _matmul(ops.swiglu_interleaved(_matmul(normed, w["w13"])), w["w2"])
+                pending = self._row_parallel(ops.swiglu_interleaved(_matmul(normed, w["w13"])), w["w2"])
             else:
-                pending = _matmul(ops.silu(_matmul(normed, w["w1"])), w["w2"])
+                pending = self._row_parallel(ops.silu(_matmul(normed, w["w1"])), w["w2"])
         hidden = model.final_norm.add_and_norm(stream, pending)[1]
         return ops.linear(hidden, model.head_weight).float()
 
@@ -185,6 +200,18 @@ class ModelRunner:
             g.tables[n:, 0].fill_(self._scratch_block)
         g.graph.replay()
         return g.logits[:n]
+
+    def _padded_heads(self, qkv: torch.Tensor, attn) -> torch.Tensor:
+        if self.kernel_head_dim == self.head_dim:
+            return qkv
+        from ajllm_b200.ops.functional import repack_heads
+        return repack_heads(qkv, attn.num_heads + 2 * attn.num_kv_heads, self.head_dim, self.kernel_head_dim)
+
+    def _true_heads(self, attended: torch.Tensor, attn) -> torch.Tensor:
+        if self.kernel_head_dim == self.head_dim:
+            return attended
+        from ajllm_b200.ops.functional import repack_heads
+        return repack_heads(attended, attn.num_heads, self.kernel_head_dim, self.head_dim)
 
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp is not None and self.tp.size > 1:
@@ -269,19 +296,23 @@ class ModelRunner:
                 if attn.use_rope:
                     serving.rope_packed_(qkv, attn.rope_cos, attn.rope_sin, pos32, attn.num_heads, attn.num_kv_heads,
                                          attn.head_dim)
-                q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
+                khd = self.kernel_head_dim
+                qkv = self._padded_heads(qkv, attn)
+                q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, khd)
                 cache.write(index, slot_t, k, v)
-                attended = torch.empty(ids.shape[0], attn.num_heads * attn.head_dim, dtype=qkv.dtype, device=dev)
+                attended = torch.empty(ids.shape[0], attn.num_heads * khd, dtype=qkv.dtype, device=dev)
                 for lo, hi in fresh:          # prompts starting from an empty cache: tiled kernel on the packed rows
-                    attended[lo:hi] = serving.prompt_attention(qkv[lo:hi], attn.num_heads, attn.num_kv_heads, attn.head_dim)
+                    attended[lo:hi] = serving.prompt_attention(qkv[lo:hi], attn.num_heads, attn.num_kv_heads, khd,
+                                                               self.softmax_scale)
                 if cached_rows is not None:
                     if all_cached:          # pure decode / verify step: no gather, no scatter
                         attended = serving.paged_attention_planned(q.contiguous(), cache.keys[index], cache.values[index],
-                                                                   paged_plan).reshape(ids.shape[0], -1)
+                                                                   paged_plan, self.softmax_scale).reshape(ids.shape[0], -1)
                     else:
                         part = serving.paged_attention_planned(q.index_select(0, cached_rows).contiguous(), cache.keys[index],
-                                                               cache.values[index], paged_plan)
+                                                               cache.values[index], paged_plan, self.softmax_scale)
                         attended.index_copy_(0, cached_rows, part.reshape(part.shape[0], -1))
+                attended = self._true_heads(attended, attn)
             else:
                 q, k, v = ops.split_packed_qkv(qkv, attn.num_heads, attn.num_kv_heads, attn.head_dim)
                 if attn.use_rope:

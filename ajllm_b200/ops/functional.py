@@ -378,6 +378,26 @@ def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float = 1e-5) -> torch.Te
 # ----------------------------------------------------------------------------- RoPE + attention
 
 
+def kernel_head_dim(head_dim: int) -> int:
+    """Head size the attention kernels run at: they exist for 64- and 128-wide heads, and any other size that is a
+    multiple of 8 (the reference's flagship model has 32) is zero-padded up to the next of the two."""
+    if head_dim % 8 or head_dim > 128:
+        raise ValueError(f"attention head size {head_dim} is not supported on the GPU (a multiple of 8, at most 128)")
+    return 64 if head_dim <= 64 else 128
+
+
+def repack_heads(x: torch.Tensor, heads: int, src_hd: int, dst_hd: int) -> torch.Tensor:
+    """``[..., heads * src_hd]`` -> ``[..., heads * dst_hd]``: widen every head with zeros or keep its leading part."""
+    lead = x.shape[:-1]
+    flat = x.reshape(-1, heads * src_hd)
+    if flat.stride(-1) != 1 or flat.stride(0) % 8:
+        flat = flat.contiguous()
+    out = torch.empty(flat.shape[0], heads * dst_hd, dtype=x.dtype, device=x.device)
+    native.call("ajb_repack_heads", flat.data_ptr(), out.data_ptr(), flat.shape[0], heads, src_hd, dst_hd,
+                flat.stride(0), out.stride(0), native.stream_ptr())
+    return out.view(*lead, heads * dst_hd)
+
+
 class _RopeAttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, cos, sin, num_heads, num_kv_heads, head_dim, causal, use_rope):
@@ -390,22 +410,29 @@ class _RopeAttentionFn(torch.autograd.Function):
             # rotates the q and k heads of the packed rows in place (positions = row % T)
             native.call("ajb_rope_qk", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), None, rows, T,
                         num_heads, num_kv_heads, head_dim, width, 0, stream)
-        out = torch.empty(B, T, num_heads * head_dim, dtype=torch.bfloat16, device=qkv.device)
-        lse = torch.empty(B, num_heads, T, dtype=torch.float32, device=qkv.device)
         scale = 1.0 / math.sqrt(head_dim)
+        khd = kernel_head_dim(head_dim)
+        all_heads = num_heads + 2 * num_kv_heads
+        if khd != head_dim:
+            qkv = repack_heads(qkv, all_heads, head_dim, khd)       # the kernels see zero-padded heads
+        out = torch.empty(B, T, num_heads * khd, dtype=torch.bfloat16, device=qkv.device)
+        lse = torch.empty(B, num_heads, T, dtype=torch.float32, device=qkv.device)
         native.call("ajb_flash_fwd", qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, num_heads,
-                    num_kv_heads, head_dim, width, int(causal), scale, stream)
+                    num_kv_heads, khd, all_heads * khd, int(causal), scale, stream)
         ctx.save_for_backward(qkv, out, lse, cos, sin)
         ctx.meta = (num_heads, num_kv_heads, head_dim, causal, use_rope, scale)
-        return out
+        return out if khd == head_dim else repack_heads(out, num_heads, khd, head_dim)
 
     @staticmethod
     def backward(ctx, grad_out):
         qkv, out, lse, cos, sin = ctx.saved_tensors
-        num_heads, num_kv_heads, head_dim, causal, use_rope, scale = ctx.meta
+        num_heads, num_kv_heads, true_head_dim, causal, use_rope, scale = ctx.meta
+        head_dim = kernel_head_dim(true_head_dim)
         B, T, width = qkv.shape
         stream = native.stream_ptr()
         grad_out = grad_out.contiguous()
+        if head_dim != true_head_dim:
+            grad_out = repack_heads(grad_out, num_heads, true_head_dim, head_dim)
         dqkv = torch.empty_like(qkv)
         delta = torch.empty(B, num_heads, T, dtype=torch.float32, device=qkv.device)
         # the fused kernel adds dQ tiles into an fp32 buffer (sum order varies between runs); the
@@ -415,6 +442,9 @@ class _RopeAttentionFn(torch.autograd.Function):
         native.call("ajb_flash_bwd", qkv.data_ptr(), out.data_ptr(), grad_out.data_ptr(), lse.data_ptr(),
                     delta.data_ptr(), dqkv.data_ptr(), dq_acc.data_ptr() if dq_acc is not None else None,
                     B, T, num_heads, num_kv_heads, head_dim, width, int(causal), scale, stream)
+        if head_dim != true_head_dim:
+            dqkv = repack_heads(dqkv, num_heads + 2 * num_kv_heads, head_dim, true_head_dim)
+            head_dim, width = true_head_dim, dqkv.shape[-1]
         if use_rope:
             native.call("ajb_rope_qk", dqkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), None, B * T, T,
                         num_heads, num_kv_heads, head_dim, width, 1, stream)

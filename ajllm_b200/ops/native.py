@@ -46,6 +46,7 @@ _SIGNATURES: dict[str, list] = {
     "ajb_rope_qk": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_void],
     "ajb_swiglu_fwd": [c_void, c_void, c_long, c_int, c_void],
     "ajb_swiglu_bwd": [c_void, c_void, c_void, c_long, c_int, c_void],
+    "ajb_repack_heads": [c_void, c_void, c_long, c_int, c_int, c_int, c_long, c_long, c_void],
     "ajb_silu": [c_void, c_void, c_void, c_long, c_void],
     "ajb_ce_fwd_bwd": [c_void, c_void, c_void, c_int, c_int, c_long, c_float, c_int, c_void],
     "ajb_embedding_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],
@@ -59,9 +60,9 @@ _SIGNATURES: dict[str, list] = {
     "ajb_fp8_block_gemm": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_void],
     "ajb_moe_route_fwd": [c_void, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void],
     "ajb_moe_assign_slots": [c_void, c_long, c_int, c_int, c_int, c_void, c_void, c_void],
-    "ajb_sample_rows": [c_void, c_long, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void],
+    "ajb_sample_rows": [c_void, c_long, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void],
     "ajb_spec_verify": [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void],
-    "ajb_paged_attention": [c_void] * 7 + [c_int] * 8 + [c_float, c_void],
+    "ajb_paged_attention": [c_void] * 7 + [c_int] * 8 + [c_float, c_int, c_void, c_void, c_void],
     "ajb_flash_bwd": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
                       c_long, c_int, c_float, c_void],
 }

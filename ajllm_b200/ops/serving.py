@@ -37,6 +37,7 @@ class PagedPlan:
                 classes.setdefault(b - a, []).append((i, cursor + a, ctx - (n - b)))
             cursor += n
         self.total_rows = cursor
+        self.max_context = max(context_lens_host) if context_lens_host else 0
         device = block_tables.device
         self.launches = []
         identity = list(range(block_tables.shape[0]))
@@ -48,17 +49,40 @@ class PagedPlan:
             self.launches.append((q_len, len(items), tables, packed[0], packed[1]))
 
 
-def paged_attention_planned(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, plan: PagedPlan) -> torch.Tensor:
+def paged_attention_planned(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, plan: PagedPlan,
+                            scale: float | None = None) -> torch.Tensor:
+    """``scale`` defaults to ``1 / sqrt(head width of q)``; callers whose heads are zero-padded pass the true one."""
     total, heads, head_dim = q.shape
     kv_heads = key_cache.shape[2]
     out = torch.empty_like(q)
-    scale = 1.0 / math.sqrt(head_dim)
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     num_blocks, block_size = key_cache.shape[0], key_cache.shape[1]
     for q_len, count, tables, starts, ctxs in plan.launches:
+        # few (sequence, KV head) pairs cannot fill the device: cut every sequence's keys over several CTAs, up to
+        # about two CTAs per SM and never more parts than the longest context has 128-key tiles
+        max_context = getattr(plan, "max_context", None) or tables.shape[1] * block_size
+        splits = paged_splits(count * kv_heads, max_context)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty(total, heads, splits, head_dim, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(total, heads, splits, 2, dtype=torch.float32, device=q.device)
         native.call("ajb_paged_attention", q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), tables.data_ptr(),
                     ctxs.data_ptr(), starts.data_ptr(), out.data_ptr(), count, num_blocks, block_size,
-                    tables.shape[1], heads, kv_heads, head_dim, q_len, scale, native.stream_ptr())
+                    tables.shape[1], heads, kv_heads, head_dim, q_len, scale, splits, native.ptr(part_o),
+                    native.ptr(part_ml), native.stream_ptr())
     return out
+
+
+_SM_COUNT: list[int] = []
+
+
+def paged_splits(ctas: int, max_context: int) -> int:
+    """Parts per sequence for the paged-attention kernel given the (sequence, KV head) pairs of a launch."""
+    if not _SM_COUNT:
+        _SM_COUNT.append(int(native.lib().ajb_sm_count()))
+    want = (2 * _SM_COUNT[0]) // max(1, ctas)
+    tiles = max(1, (max_context + 127) // 128)
+    return max(1, min(want, tiles, 16))
 
 
 def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, block_tables: torch.Tensor,
@@ -69,14 +93,16 @@ def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch
     return paged_attention_planned(q, key_cache, value_cache, plan)
 
 
-def prompt_attention(qkv_rows: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int) -> torch.Tensor:
+def prompt_attention(qkv_rows: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                     scale: float | None = None) -> torch.Tensor:
     """Causal attention of one prompt that starts from an empty cache, read in place from its packed
     (already rotated) ``[T, (Hq + 2 Hkv) * hd]`` rows. Returns ``[T, Hq * hd]``."""
     T, width = qkv_rows.shape
     out = torch.empty(T, num_heads * head_dim, dtype=torch.bfloat16, device=qkv_rows.device)
     lse = torch.empty(num_heads, T, dtype=torch.float32, device=qkv_rows.device)
     native.call("ajb_flash_fwd", qkv_rows.data_ptr(), out.data_ptr(), lse.data_ptr(), 1, T, num_heads, num_kv_heads,
-                head_dim, qkv_rows.stride(0), 1, 1.0 / math.sqrt(head_dim), native.stream_ptr())
+                head_dim, qkv_rows.stride(0), 1, 1.0 / math.sqrt(head_dim) if scale is None else scale,
+                native.stream_ptr())
     return out
 
 
@@ -85,10 +111,16 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
     """One token per row of fp32 ``logits`` ``[rows, vocab]``; per-row temperature (``<= 0`` = greedy),
     top-p, and a counter-based random stream ``(seed, counter)``. Returns int32 ``[rows]`` on the device."""
     logits = logits.contiguous()
-    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-    native.call("ajb_sample_rows", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1],
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    # few rows over a large vocabulary: the row maxima are found by about two CTAs per SM, not one CTA per row
+    if not _SM_COUNT:
+        _SM_COUNT.append(int(native.lib().ajb_sm_count()))
+    chunks = max(1, min(2 * _SM_COUNT[0] // max(1, rows), vocab // 4096, 64))
+    workspace = torch.empty(rows, chunks, 2, dtype=torch.int32, device=logits.device) if chunks > 1 else None
+    native.call("ajb_sample_rows", logits.data_ptr(), logits.stride(0), rows, vocab,
                 temperature.data_ptr(), top_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(), out.data_ptr(),
-                native.stream_ptr())
+                chunks, native.ptr(workspace), native.stream_ptr())
     return out
 
 

@@ -51,7 +51,7 @@ def run(config: LoadedConfig) -> dict[str, Any]:
         from ajllm_b200.parallel.contexts import make_tensor_parallel
         _, _, device = init_distributed(device.type)
         fused = (data.get("acceleration", {}) or {}).get("fused")
-        tp = make_tensor_parallel(ParallelMesh(tp=world).tp, device, None if fused is None else bool(fused))
+        tp = make_tensor_parallel(ParallelMesh(tp=world).tp, device, None if fused is None else bool(fused), interleave=1)
     main = tp is None or tp.rank == 0
     model, train_cfg, _ = load_model_from_run(training_run, checkpoint, device, tp=tp)
     tok_dir, tok_manifest = open_tokenizer_artifact(config.project_root, train_cfg["tokenizer"]["name"])

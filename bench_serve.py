@@ -157,7 +157,7 @@ def run_ours(args):
     from ajllm_b200.parallel.contexts import make_tensor_parallel
 
     rank, world, device = init_distributed("cuda")
-    tp = make_tensor_parallel(ParallelMesh(tp=world).tp, device) if world > 1 else None
+    tp = make_tensor_parallel(ParallelMesh(tp=world).tp, device, interleave=1) if world > 1 else None
     torch.manual_seed(0)
     config = dict(MODEL)
     if args.layers:

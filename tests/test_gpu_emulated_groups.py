@@ -162,7 +162,7 @@ def test_expert_dispatch_and_combine_as_rank_0(ep):
     push.argtypes = [ctypes.POINTER(_Args), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     pull.argtypes = [ctypes.POINTER(_Args), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     push.restype = pull.restype = ctypes.c_int
-    tokens, top_k, dim, local_experts, stride = 300, 3, 264, 2, 192
+    tokens, top_k, dim, local_experts, stride = 300, 3, 264, 2, 256
     experts = ep * local_experts
     # distinct (expert, position) slots per assignment; about a tenth dropped (-1)
     choice = torch.stack([torch.randperm(experts, device=dev)[:top_k] for _ in range(tokens)])

@@ -210,7 +210,8 @@ def test_sumsq_and_adamw_flat():
 
 
 @pytest.mark.parametrize("deterministic", [False, True])
-@pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 256, 4, 2, 128), (1, 200, 2, 2, 128), (2, 384, 8, 2, 64), (1, 1024, 2, 1, 128)])
+@pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 256, 4, 2, 128), (1, 200, 2, 2, 128), (2, 384, 8, 2, 64), (1, 1024, 2, 1, 128),
+                                           (2, 256, 16, 16, 32), (1, 200, 4, 2, 96)])
 def test_flash_attention_forward_backward(B, T, Hq, Hkv, hd, deterministic, monkeypatch):
     """Both backward paths (fused single pass with reduced dQ; two reproducible kernels) against fp32 math."""
     from ajllm_b200.ops import functional

@@ -70,6 +70,29 @@ def test_engine_prefill_logits_match_training_forward(models):
     assert float((step[0] - full).abs().max()) < 0.08 * float(full.abs().max())
 
 
+def test_engine_serves_32_wide_heads_like_the_training_forward():
+    """Head sizes the kernels do not exist for (the reference's flagship has 16 heads of 32) are cached zero-padded."""
+    from ajllm_b200.engine.model_runner import RunItem
+    torch.manual_seed(1)
+    config = {**CFG, "num_heads": 16, "num_kv_heads": 16}
+    model = build_model(config, 1024).to(device=_dev(), dtype=torch.bfloat16)
+    engine = LLMEngine(model, num_blocks=64)
+    assert engine.cache.head_dim == 64 and engine.runner.head_dim == 32
+    prompt = _prompts()[2]
+    got = engine.runner.forward([RunItem(0, prompt, len(prompt))])
+    with torch.no_grad():
+        want = model(torch.tensor([prompt], device=_dev()))[0].float()
+    assert float((got - want).abs().max()) < 0.08 * float(want.abs().max())
+    nxt = int(got[-1].argmax())
+    step = engine.runner.forward([RunItem(0, [nxt], 1)])
+    with torch.no_grad():
+        full = model(torch.tensor([prompt + [nxt]], device=_dev()))[0, -1].float()
+    assert float((step[0] - full).abs().max()) < 0.08 * float(full.abs().max())
+    outs = LLMEngine(model, num_blocks=128).generate(_prompts()[:3], SamplingParams(12, 0.0, None))
+    assert all(len(o.output) == 12 for o in outs)
+    assert native.lib().ajb_check_status() == 0
+
+
 def test_gpu_engine_batched_equals_sequential_and_speculative(models):
     target, draft = models
     prompts = _prompts()
