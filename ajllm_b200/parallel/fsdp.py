@@ -96,6 +96,7 @@ class ShardedOptimizer:
         self.step_count = 0
 
     def zero_grad(self, set_to_none: bool = True) -> None:
+        self.owner.join_reductions()
         self.owner.grad.zero_()
         if self.owner.local_grad is not None:
             self.owner.local_grad.zero_()
@@ -103,6 +104,7 @@ class ShardedOptimizer:
     @torch.no_grad()
     def step(self, max_norm: float = 0.0) -> torch.Tensor:
         o = self.owner
+        o.join_reductions()
         # the fused reduce-scatter left per-CTA sums of squares of every unit's (fully accumulated) shard
         sumsq = o._sumsq_partials.sum().reshape(1) if o.fused_reduce is not None else flat_sumsq(o.grad).clone()
         if o.local_grad is not None:
@@ -196,11 +198,21 @@ class ShardedDataParallel(nn.Module):
         if fused_reduce is None:
             fused_reduce = dev.type == "cuda" and 1 < self.world <= 8 and os.environ.get("AJB_FUSED_FSDP", "1") != "0"
         self.fused_reduce = None
+        # With the fused kernel the reduction of a unit runs on a stream of its own while the next unit already
+        # back-propagates into a second full-gradient buffer (AJB_FSDP_OVERLAP_REDUCE=0: one buffer, in stream order).
+        self._reducers: list = []
+        self._reduce_stream = None
+        self._reduce_events: list = [None, None]
+        self._grad_slot = 0
         if fused_reduce:
             from ajllm_b200.parallel.grad_reduce import FusedGradReduce
-            self.fused_reduce = FusedGradReduce(group, dev, largest)
+            overlap = os.environ.get("AJB_FSDP_OVERLAP_REDUCE", "1") != "0"
+            self._reducers = [FusedGradReduce(group, dev, largest) for _ in range(2 if overlap else 1)]
+            self.fused_reduce = self._reducers[0]
             self._full_grad = self.fused_reduce.buffer
             self._sumsq_partials = torch.zeros(len(self.units), FusedGradReduce.CTAS, dtype=torch.float32, device=dev)
+            if overlap:
+                self._reduce_stream = torch.cuda.Stream(device=dev)
         else:
             self._full_grad = torch.zeros(largest, dtype=torch.float32, device=dev)
         # Parameter all-gather of a block fused into its first GEMM (the QKV projection): opt-in, bf16 on GPUs.
@@ -332,7 +344,20 @@ class ShardedDataParallel(nn.Module):
             p.data = torch.empty(0, dtype=self.dtype, device=self.device)
         self._resident.pop(index, None)
 
+    def join_reductions(self) -> None:
+        """The current stream waits for the gradient reductions still running on their own stream."""
+        if self._reduce_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._reduce_stream)
+
     def _attach_grad_views(self, unit: _Unit) -> None:
+        if self._reduce_stream is not None:
+            # alternate between the two full-gradient buffers; the one taken now was last reduced two units ago
+            self._grad_slot ^= 1
+            self.fused_reduce = self._reducers[self._grad_slot]
+            self._full_grad = self.fused_reduce.buffer
+            pending = self._reduce_events[self._grad_slot]
+            if pending is not None:
+                torch.cuda.current_stream().wait_event(pending)
         self._full_grad[:unit.padded].zero_()
         for p, off in zip(unit.params, unit.offsets):
             p.main_grad = self._full_grad[off:off + p._full_shape.numel()].view(p._full_shape)
@@ -349,7 +374,14 @@ class ShardedDataParallel(nn.Module):
             if p.grad is not None:
                 p.main_grad.add_(p.grad.to(torch.float32))
                 p.grad = None
-        if self.fused_reduce is not None:
+        if self.fused_reduce is not None and self._reduce_stream is not None:
+            side = self._reduce_stream
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.fused_reduce.reduce_into(self.grad[unit.base:unit.base + unit.shard], unit.shard, accumulate=True,
+                                              sumsq_partials=self._sumsq_partials[index])
+                self._reduce_events[self._grad_slot] = side.record_event()
+        elif self.fused_reduce is not None:
             self.fused_reduce.reduce_into(self.grad[unit.base:unit.base + unit.shard], unit.shard, accumulate=True,
                                           sumsq_partials=self._sumsq_partials[index])
         else:

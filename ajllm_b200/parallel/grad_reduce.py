@@ -37,6 +37,7 @@ class FusedGradReduce:
     """Owns the symmetric full-gradient buffer of ``elements`` floats and the handshake words."""
 
     CTAS = 64          # enough 16-byte loads in flight to fill the NVLink ports; leaves SMs to other streams
+    GUARD_FLOATS, GUARD_VALUE = 1024, -6.02e23     # behind the payload: peers address this buffer with raw pointers
 
     def __init__(self, group, device: torch.device, elements: int) -> None:
         import torch.distributed._symmetric_memory as symm_mem
@@ -45,9 +46,11 @@ class FusedGradReduce:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if not 1 <= self.world <= _MAX_RANKS:
             raise ValueError("fused gradient reduce-scatter supports up to 8 ranks")
-        self.buffer = symm_mem.empty(elements, dtype=torch.float32, device=device)
-        self.buffer.zero_()
-        self._buffer_ptrs = list(symm_mem.rendezvous(self.buffer, group).buffer_ptrs)
+        self._whole = symm_mem.empty(elements + self.GUARD_FLOATS, dtype=torch.float32, device=device)
+        self._whole.zero_()
+        self._whole[elements:].fill_(self.GUARD_VALUE)
+        self.buffer = self._whole[:elements]
+        self._buffer_ptrs = list(symm_mem.rendezvous(self._whole, group).buffer_ptrs)
         self._flags = symm_mem.empty(32, dtype=torch.int32, device=device)     # [0:8] ready, [8:16] done
         self._flags.zero_()
         self._flag_ptrs = list(symm_mem.rendezvous(self._flags, group).buffer_ptrs)
@@ -59,6 +62,10 @@ class FusedGradReduce:
         fn.argtypes = [ctypes.POINTER(_Args), ctypes.c_void_p]
         fn.restype = ctypes.c_int
         self._fn = fn
+
+    def guards_intact(self) -> bool:
+        """True while nothing (a weight-gradient epilogue, a peer's kernel) has written behind the end of the buffer."""
+        return bool((self._whole[self.buffer.numel():] == self.GUARD_VALUE).all())
 
     def reduce_into(self, dst: torch.Tensor, shard_elems: int, accumulate: bool = True, scale: float = 1.0,
                     sumsq_partials: torch.Tensor | None = None) -> None:

@@ -31,6 +31,8 @@ class _Args(ctypes.Structure):
 
 
 class FusedExpertExchange:
+    GUARD_ELEMENTS, GUARD_VALUE = 2048, -12345.0      # behind every symmetric row buffer (peers store with raw pointers)
+
     def __init__(self, group, device: torch.device) -> None:
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -61,17 +63,22 @@ class FusedExpertExchange:
         """Symmetric bf16 ``[rows, dim]`` buffer (allocated collectively on first use, zero-filled)."""
         need = rows * dim
         have = self._buffers.get(name)
-        if have is None or have[0].numel() < need:
+        if have is None or have[0].numel() - self.GUARD_ELEMENTS < need:
             torch.cuda.synchronize(self.device)
             dist.barrier(self.group)
-            buf = self._symm.empty(need, dtype=torch.bfloat16, device=self.device)
+            buf = self._symm.empty(need + self.GUARD_ELEMENTS, dtype=torch.bfloat16, device=self.device)
             buf.zero_()
+            buf[need:].fill_(self.GUARD_VALUE)
             ptrs = list(self._symm.rendezvous(buf, self.group).buffer_ptrs)
             torch.cuda.synchronize(self.device)
             dist.barrier(self.group)
             have = (buf, ptrs)
             self._buffers[name] = have
         return have[0][:need].view(rows, dim), have[1]
+
+    def guards_intact(self) -> bool:
+        """True while no peer has stored past the end of a row buffer (checked by the multi-GPU tests)."""
+        return all(bool((buf[-self.GUARD_ELEMENTS:] == self.GUARD_VALUE).all()) for buf, _ in self._buffers.values())
 
     def _args(self, slots: torch.Tensor, dim: int, local_experts: int, stride: int, peer_ptrs: list[int],
               counts: torch.Tensor | None) -> _Args:

@@ -140,12 +140,14 @@ def run_ours(args) -> dict | None:
     if world > 1:
         tp = make_tensor_parallel(ParallelMesh(tp=world).tp, device)
         classes = tp_optimizer_classes(tp)
-    micro = args.micro_batch or {1: 8, 2: 8, 4: 16, 8: 32}.get(world, 8)
-    micro = min(micro, args.global_batch)
-    accumulation = args.global_batch // micro
     with torch.device(device):
         model = build_model(config, VOCAB, tp=tp)
     model = model.to(device=device, dtype=torch.bfloat16)
+    # sequences per micro-batch: as many as fit; with two micro-batches in flight (model.interleave) the batch of 32
+    # is cut into at least two
+    micro = args.micro_batch or {1: 8, 2: 8, 4: 16, 8: 32 if model.interleave == 1 else 16}.get(world, 8)
+    micro = min(micro, args.global_batch)
+    accumulation = args.global_batch // micro
     optimizer = FlatAdamW(model, learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1, classes=classes)
     params = sum(p.numel() for p in model.parameters())
 

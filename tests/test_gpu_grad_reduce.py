@@ -72,6 +72,8 @@ def _worker(rank: int, world: int, port: int, results):
                     shards[fused] = fsdp.grad.clone()
                 norms.append(float(opt.step(1.0)))
             out[f"norms_{fused}"] = norms
+            # nothing wrote behind the end of a symmetric full-gradient buffer
+            out[f"guards_{fused}"] = all(r.guards_intact() for r in fsdp._reducers)
             del fsdp, model
         ref = shards[False]
         out["fsdp_grad_rel"] = float((shards[True] - ref).norm() / ref.norm())
@@ -149,6 +151,7 @@ def test_fused_gradient_reduce_scatter():
     for rank in range(2):
         out = results[rank]
         assert out["status"] == 0, out
+        assert all(v for k, v in out.items() if k.startswith("guards_")), out
         assert out["kernel_max_abs"] < 1e-5, out
         assert out["sumsq_rel"] < 1e-5, out
         # the paths add the same fp32 partials in a different order; the step-2 gradients compared here also carry

@@ -32,11 +32,15 @@ def _train(model, optimizer, batches, steps):
     return losses
 
 
-def test_interleaved_microbatches_match_sequential_ones_on_one_gpu():
+def test_interleaved_microbatches_match_sequential_ones_on_one_gpu(monkeypatch):
     from ajllm_b200.models import build_model
     from ajllm_b200.ops import functional, native
     from ajllm_b200.training import FlatAdamW
 
+    # reproducible kernels (no K-sliced atomic weight gradients, two-kernel attention backward): what is left to differ
+    # between the two schedules is the order of a few fp32 additions
+    monkeypatch.setattr(functional, "DETERMINISTIC_ATTENTION_BACKWARD", True)
+    monkeypatch.setattr(functional, "DETERMINISTIC_WGRAD", True)
     device = torch.device("cuda", 0)
     gen = torch.Generator().manual_seed(3)
     steps = 3
@@ -48,16 +52,18 @@ def test_interleaved_microbatches_match_sequential_ones_on_one_gpu():
             torch.manual_seed(0)
             model = build_model(CONFIG, VOCAB).to(device=device, dtype=torch.bfloat16)
             model._interleave = 2 if mode == "interleaved" else 1
-            optimizer = FlatAdamW(model, learning_rate=1e-3, weight_decay=0.1)
-            losses = _train(model, optimizer, batches, steps)
-            results[mode] = (losses, optimizer.grad.clone(), optimizer.master.clone())
+            optimizer = FlatAdamW(model, learning_rate=1e-4, weight_decay=0.1)
+            first = _train(model, optimizer, batches[:1], 1)
+            first_grad = optimizer.grad.clone()          # same weights in both modes: only the schedule differs
+            losses = first + _train(model, optimizer, batches[1:], steps - 1)
+            results[mode] = (losses, first_grad, optimizer.master.clone())
             assert (functional.wgrad_stream() is not None) == (mode == "interleaved")
     finally:
         functional.set_wgrad_stream(None)
     (l0, g0, w0), (l1, g1, w1) = results["sequential"], results["interleaved"]
     assert all(abs(a - b) < 2e-3 for a, b in zip(l0, l1)), (l0, l1)
-    assert _rel(g1, g0) < 2e-3, _rel(g1, g0)        # the last step's gradient buffer (fp32 sums in another order)
-    assert _rel(w1, w0) < 5e-4, _rel(w1, w0)
+    assert _rel(g1, g0) < 1e-4, _rel(g1, g0)        # a lost or doubled accumulation would show as percents
+    assert _rel(w1, w0) < 2e-3, _rel(w1, w0)
     assert native.check_status() == 0
 
 

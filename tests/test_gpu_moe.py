@@ -103,6 +103,9 @@ def _worker(rank, world, port, results):
             dist.all_reduce(router)             # the router is replicated: its gradient is the sum over ranks
             report[tag] = {"loss": abs(float(total) / world - float(want_loss)),
                            "w13": rel(ff.experts.w13.grad / world, want_w13), "router": rel(router / world, want_router)}
+            if tag == "fused":
+                torch.cuda.synchronize()
+                report["guards"] = ep.exchange.guards_intact()
         torch.cuda.synchronize()
         results[rank] = {"report": report, "status": native.lib().ajb_check_status()}
     finally:
@@ -128,6 +131,7 @@ def test_fused_expert_exchange_matches_all_to_all_path():
     for rank in range(2):
         out = results[rank]
         assert out["status"] == 0, out
+        assert out["report"]["guards"], out
         fused, nccl = out["report"]["fused"], out["report"]["nccl"]
         assert fused["loss"] < 3e-2 and nccl["loss"] < 3e-2, out
         for key in ("w13", "router"):
