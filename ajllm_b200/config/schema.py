@@ -50,16 +50,20 @@ def check_model(model: dict[str, Any]) -> None:
 
 
 def check_parallel(parallel: dict[str, Any], world_size: int) -> dict[str, int]:
-    """Return the mesh extents ``{tp, ep, fsdp, pp}``; their product (EP shares FSDP's ranks) must fill
-    the world."""
+    """Return the mesh extents ``{tp, ep, fsdp, pp, cp}``; their product (EP shares FSDP's ranks) must fill
+    the world. Context parallelism (``cp``) takes the innermost axis in place of ``tp`` and combines with
+    replicated data parallelism only."""
     tp = int(parallel.get("tp", 1))
     pp = int(parallel.get("pp", 1))
     ep = int(parallel.get("ep", 1))
-    fsdp = int(parallel.get("fsdp", max(1, world_size // (tp * pp))))
-    if min(tp, pp, ep, fsdp) < 1:
+    cp = int(parallel.get("cp", 1))
+    fsdp = int(parallel.get("fsdp", max(1, world_size // (tp * pp * cp))))
+    if min(tp, pp, ep, fsdp, cp) < 1:
         raise ConfigError("parallel extents must be positive")
-    if tp * pp * fsdp != world_size:
-        raise ConfigError(f"parallel.tp*pp*fsdp = {tp * pp * fsdp} does not match world size {world_size}")
+    if cp > 1 and (tp > 1 or pp > 1 or ep > 1):
+        raise ConfigError("parallel.cp combines with data parallelism only (tp = pp = ep = 1)")
+    if tp * pp * fsdp * cp != world_size:
+        raise ConfigError(f"parallel.tp*pp*fsdp*cp = {tp * pp * fsdp * cp} does not match world size {world_size}")
     if fsdp % ep != 0 and ep % fsdp != 0:
         raise ConfigError("parallel.ep must divide, or be a multiple of, parallel.fsdp")
-    return {"tp": tp, "ep": ep, "fsdp": fsdp, "pp": pp}
+    return {"tp": tp, "ep": ep, "fsdp": fsdp, "pp": pp, "cp": cp}

@@ -10,6 +10,11 @@
 // epilogue warps fold it into per-thread fp32 running sums with the product of the two scales while the
 // tensor core already works on the next K block (two partial accumulators in tensor memory).
 // One CTA computes a 128 x 128 tile: one weight scale per K block, one activation scale per row.
+//
+// Decoding has few rows and therefore few tiles; a tile that walks the whole K on its own is a long serial chain
+// on a mostly idle device. With `splits` > 1 the K blocks of a tile are divided over that many CTAs (grid z), each
+// writes its fp32 partial tile to a workspace, and a second small kernel sums the parts in a fixed order and rounds
+// to bf16.
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -30,6 +35,8 @@ struct Params {
   const float* b_scale;   // [ceil(N / 128), kblocks]
   int m, n, k;
   long long ldc;
+  int splits;        // CTAs per tile along K
+  float* partial;    // splits > 1: [splits, m, n] fp32
   DeviceStatus* status;
 };
 
@@ -48,7 +55,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tn = blockIdx.x, tm = blockIdx.y;
-  const int num_kb = (p.k + BK - 1) / BK;
+  const int num_kb = (p.k + BK - 1) / BK;          // K blocks of the whole problem (scale tables are indexed by these)
+  const int per_split = (num_kb + p.splits - 1) / p.splits;
+  const int kb_begin = min(num_kb, (int)blockIdx.z * per_split);
+  const int kb_count = min(num_kb - kb_begin, per_split);      // this CTA's blocks: [kb_begin, kb_begin + kb_count)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -75,9 +85,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % kStages;
-        if (!mbar_wait(&empty[s], ((kb / kStages) & 1) ^ 1, abort_flag, p.status, kFp8KernelId, 1)) break;
+      for (int i = 0; i < kb_count; ++i) {
+        const int s = i % kStages, kb = kb_begin + i;
+        if (!mbar_wait(&empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kFp8KernelId, 1)) break;
         uint8_t* sa = smem + s * kStageBytes;
         mbar_arrive_expect_tx(&full[s], kStageBytes);
         tma_load_2d(sa, &map_a, &full[s], kb * BK, tm * BM);
@@ -86,7 +96,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else if (warp == 1) {
     constexpr uint32_t idesc = make_idesc(BM, BN, /*e4m3*/ 0, false, false);
-    for (int kb = 0; kb < num_kb; ++kb) {
+    for (int kb = 0; kb < kb_count; ++kb) {          // local block index
       const int s = kb % kStages, buf = kb & 1;
       if (!mbar_wait(&part_empty[buf], (((uint32_t)kb >> 1) & 1) ^ 1, abort_flag, p.status, kFp8KernelId, 2)) break;
       if (!mbar_wait(&full[s], (kb / kStages) & 1, abort_flag, p.status, kFp8KernelId, 3)) break;
@@ -110,10 +120,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
     for (int i = 0; i < BN; ++i) acc[i] = 0.0f;
     bool ok = true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int buf = kb & 1;
+    for (int i = 0; i < kb_count && ok; ++i) {
+      const int buf = i & 1, kb = kb_begin + i;
       const float scale = (row_ok ? p.a_scale[(size_t)row * num_kb + kb] : 0.0f) * p.b_scale[(size_t)tn * num_kb + kb];
-      if (!mbar_wait(&part_full[buf], ((uint32_t)kb >> 1) & 1, abort_flag, p.status, kFp8KernelId, 4)) { ok = false; break; }
+      if (!mbar_wait(&part_full[buf], ((uint32_t)i >> 1) & 1, abort_flag, p.status, kFp8KernelId, 4)) { ok = false; break; }
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
@@ -127,7 +137,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&part_empty[buf]);
     }
-    if (ok && row_ok) {
+    if (ok && row_ok && p.splits > 1) {
+      // this part's fp32 sums (zeros when it had no K block); n is a multiple of 4 on this path
+      const int col0 = tn * BN;
+      float* dst = p.partial + ((size_t)blockIdx.z * p.m + row) * p.n + col0;
+      const int valid = min(BN, p.n - col0);
+#pragma unroll
+      for (int j = 0; j < BN / 4; ++j)
+        if (4 * j < valid) reinterpret_cast<float4*>(dst)[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    } else if (ok && row_ok) {
       const int col0 = tn * BN;
       __nv_bfloat16* dst = p.c + (long long)row * p.ldc + col0;
       const int valid = min(BN, p.n - col0);
@@ -154,6 +172,25 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// c[r, :] = bf16(sum over the parts of partial[part, r, :]), four columns per thread, parts in index order.
+__global__ void sum_parts_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ c, int m, int n, long long ldc,
+                                 int splits) {
+  const long long vecs = (long long)m * (n >> 2);
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < vecs; idx += (long long)gridDim.x * blockDim.x) {
+    const long long row = idx / (n >> 2);
+    const int col = (int)(idx - row * (n >> 2)) * 4;
+    float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int z = 0; z < splits; ++z) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + ((size_t)z * m + row) * n + col);
+      total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+    }
+    uint2 packed;
+    packed.x = pack_bf16x2(total.x, total.y);
+    packed.y = pack_bf16x2(total.z, total.w);
+    *reinterpret_cast<uint2*>(c + row * ldc + col) = packed;
   }
 }
 
@@ -202,12 +239,28 @@ extern "C" int ajb_fp8_quantize_rows(const void* x, void* q, void* scales, int r
   return 0;
 }
 
+// How many K parts ajb_fp8_block_gemm would like for this problem (1 = none): enough CTAs to cover the device when
+// the tiles alone do not, each part at least four K blocks long.
+extern "C" int ajb_fp8_block_gemm_splits(int m, int n, int k) {
+  using namespace ajb;
+  const int tiles = ((n + fp8::BN - 1) / fp8::BN) * ((m + fp8::BM - 1) / fp8::BM);
+  const int num_kb = (k + fp8::BK - 1) / fp8::BK;
+  if (n % 4 != 0 || tiles >= sm_count()) return 1;
+  int want = (sm_count() + tiles - 1) / tiles;
+  if (want > num_kb / 4) want = num_kb / 4;
+  return want < 1 ? 1 : want;
+}
+
 // a [m, k] e4m3 (row pitch lda bytes), b [n, k] e4m3 (row pitch ldb bytes), scales as described above.
+// splits > 1 (see ajb_fp8_block_gemm_splits) needs `workspace` of splits * m * n floats.
 extern "C" int ajb_fp8_block_gemm(const void* a, const void* b, const void* a_scale, const void* b_scale, void* c, int m,
-                                  int n, int k, long long lda, long long ldb, long long ldc, void* stream) {
+                                  int n, int k, long long lda, long long ldb, long long ldc, int splits, void* workspace,
+                                  void* stream) {
   using namespace ajb;
   AJB_REQUIRE(m > 0 && n > 0 && k > 0, "fp8 gemm: empty problem");
   AJB_REQUIRE(k % 16 == 0, "fp8 gemm: k must be a multiple of 16");
+  AJB_REQUIRE(splits >= 1 && (splits == 1 || (workspace != nullptr && n % 4 == 0 && ldc % 4 == 0)),
+              "fp8 gemm: K parts need a workspace and n, ldc multiples of 4");
   CUtensorMap map_a, map_b;
   int rc = make_tensor_map_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m, k, lda, fp8::BM, fp8::BK);
   if (rc) return rc;
@@ -221,8 +274,17 @@ extern "C" int ajb_fp8_block_gemm(const void* a, const void* b, const void* a_sc
   fp8::Params p;
   p.c = (__nv_bfloat16*)c; p.a_scale = (const float*)a_scale; p.b_scale = (const float*)b_scale;
   p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.status = device_status_buffer();
-  dim3 grid((n + fp8::BN - 1) / fp8::BN, (m + fp8::BM - 1) / fp8::BM);
-  fp8::fp8_gemm_kernel<<<grid, fp8::kThreads, fp8::kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+  p.splits = splits; p.partial = (float*)workspace;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid((n + fp8::BN - 1) / fp8::BN, (m + fp8::BM - 1) / fp8::BM, splits);
+  fp8::fp8_gemm_kernel<<<grid, fp8::kThreads, fp8::kSmem, s>>>(map_a, map_b, p);
   AJB_CUDA_OK(cudaGetLastError());
+  if (splits > 1) {
+    const long long vecs = (long long)m * (n / 4);
+    const long long blocks = (vecs + 255) / 256;
+    fp8::sum_parts_kernel<<<(unsigned)(blocks < (long long)sm_count() * 8 ? blocks : (long long)sm_count() * 8), 256, 0, s>>>(
+        (const float*)workspace, (__nv_bfloat16*)c, m, n, ldc, splits);
+    AJB_CUDA_OK(cudaGetLastError());
+  }
   return 0;
 }

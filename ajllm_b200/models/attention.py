@@ -21,7 +21,7 @@ from ajllm_b200.ops import reference
 
 class SelfAttention(nn.Module):
     def __init__(self, d_model: int, num_heads: int, num_kv_heads: int | None, context_length: int,
-                 position_encoding: str, rope_theta: float, init: InitSpec = InitSpec(), tp=None) -> None:
+                 position_encoding: str, rope_theta: float, init: InitSpec = InitSpec(), tp=None, cp=None) -> None:
         super().__init__()
         if d_model % num_heads:
             raise ValueError("d_model must be divisible by num_heads")
@@ -32,6 +32,11 @@ class SelfAttention(nn.Module):
         self.total_heads, self.total_kv_heads = num_heads, num_kv_heads
         self.head_dim = d_model // num_heads
         self.tp = tp
+        self.cp = cp if (cp is not None and cp.size > 1) else None      # context parallelism: sequence split <-> head split
+        if self.cp is not None:
+            if tp is not None and tp.size > 1:
+                raise ValueError("context parallelism and tensor parallelism are not combined")
+            self.cp.check_heads(num_heads, num_kv_heads)
         self.qkv_override = None
         tp_size = tp.size if tp is not None else 1
         if num_heads % tp_size or num_kv_heads % tp_size:
@@ -140,6 +145,15 @@ class SelfAttention(nn.Module):
         """``x`` is ``[local_tokens, d_model]`` (or ``[B, T, d_model]`` without TP); ``batch_shape`` is
         the global ``(B, T)`` the tokens were flattened from."""
         B, T = batch_shape
+        if self.cp is not None:
+            cp = self.cp
+            # x holds T / cp tokens of every sequence: trade the sequence split for a head split around the kernel
+            qkv = cp.to_heads(self.project_qkv(x).reshape(B, T // cp.size, -1), self.num_heads, self.num_kv_heads,
+                              self.head_dim)
+            attended = ops.rope_attention(qkv, self.rope_cos, self.rope_sin, self.num_heads // cp.size,
+                                          self.num_kv_heads // cp.size, self.head_dim, causal=True)
+            attended = cp.to_sequence(attended, self.num_heads, self.head_dim)
+            return self.project_out(attended.reshape(B * (T // cp.size), -1)).reshape(x.shape)
         qkv = self.project_qkv(x).reshape(B, T, -1)
         attended = ops.rope_attention(qkv, self.rope_cos, self.rope_sin, self.num_heads, self.num_kv_heads,
                                       self.head_dim, causal=True)

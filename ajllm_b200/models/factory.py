@@ -21,7 +21,7 @@ def default_d_ff(d_model: int, feed_forward: str) -> int:
 
 
 def build_model(config: dict[str, Any], vocab_size: int, use_flash_attention: bool = False, *,
-                tp=None, ep=None, activation_checkpointing: str = "none") -> TransformerLM:
+                tp=None, ep=None, activation_checkpointing: str = "none", cp=None) -> TransformerLM:
     """``use_flash_attention`` is accepted for config compatibility; attention is always the tiled
     kernel on a GPU and the exact softmax on the CPU."""
     check_model(config)
@@ -52,6 +52,7 @@ def build_model(config: dict[str, Any], vocab_size: int, use_flash_attention: bo
         init=InitSpec.from_config(config.get("init")),
         tp=tp,
         ep=ep,
+        cp=cp,
         norm_epsilon=float(config.get("norm_epsilon", 1e-5)),
         activation_checkpointing=activation_checkpointing,
     )

@@ -26,7 +26,7 @@ class TransformerBlock(nn.Module):
     def __init__(self, d_model: int, num_heads: int, num_kv_heads: int | None, d_ff: int, context_length: int,
                  position_encoding: str, rope_theta: float, normalization: str, norm_placement: str,
                  feed_forward: str, moe: dict | None = None, init: InitSpec = InitSpec(),
-                 tp=None, ep=None, norm_epsilon: float = 1e-5) -> None:
+                 tp=None, ep=None, norm_epsilon: float = 1e-5, cp=None) -> None:
         super().__init__()
         if norm_placement not in {"pre", "post"}:
             raise ValueError("normalization.placement must be 'pre' or 'post'")
@@ -34,7 +34,7 @@ class TransformerBlock(nn.Module):
         self.norm1 = make_norm(normalization, d_model, norm_epsilon)
         self.norm2 = make_norm(normalization, d_model, norm_epsilon)
         self.attention = SelfAttention(d_model, num_heads, num_kv_heads, context_length, position_encoding,
-                                       rope_theta, init, tp)
+                                       rope_theta, init, tp, cp)
         if moe:
             self.feed_forward = MoEFeedForward(d_model, moe, init, ep)
         else:
@@ -59,7 +59,7 @@ class TransformerLM(nn.Module):
                  rope_theta: float = 10_000.0, normalization: str = "rmsnorm", norm_placement: str = "pre",
                  feed_forward: str = "swiglu", tie_embeddings: bool = False, moe: dict | None = None,
                  init: InitSpec = InitSpec(), tp=None, ep=None, norm_epsilon: float = 1e-5,
-                 activation_checkpointing: str = "none") -> None:
+                 activation_checkpointing: str = "none", cp=None) -> None:
         super().__init__()
         if position_encoding not in {"rope", "none", "learned"}:
             raise ValueError("position encoding must be rope, none, or learned")
@@ -71,13 +71,14 @@ class TransformerLM(nn.Module):
         self.tie_embeddings, self.moe = tie_embeddings, moe
         self.rope_theta = rope_theta
         self.tp, self.ep = tp, ep
+        self.cp = cp if (cp is not None and cp.size > 1) else None
         self.activation_checkpointing = activation_checkpointing
 
         self.token_embeddings = Embedding(vocab_size, d_model, init)
         self.position_embeddings = Embedding(context_length, d_model, init) if position_encoding == "learned" else None
         self.layers = nn.ModuleList([
             TransformerBlock(d_model, num_heads, num_kv_heads, d_ff, context_length, position_encoding, rope_theta,
-                             normalization, norm_placement, feed_forward, moe, init, tp, ep, norm_epsilon)
+                             normalization, norm_placement, feed_forward, moe, init, tp, ep, norm_epsilon, cp)
             for _ in range(num_layers)
         ])
         self.final_norm = make_norm(normalization if norm_placement == "pre" else "none", d_model, norm_epsilon)
@@ -93,16 +94,23 @@ class TransformerLM(nn.Module):
             return self.tp.local_rows(flat)
         return flat
 
+    def _local_ids(self, per_token: torch.Tensor) -> torch.Tensor:
+        """This rank's tokens of a ``[B, T]`` tensor, flattened: a slice of every sequence under context parallelism,
+        a slice of the flattened rows under tensor parallelism."""
+        if self.cp is not None:
+            return self.cp.local_sequence(per_token, 1).reshape(-1)
+        return self._local_tokens(per_token.reshape(-1))
+
     def hidden_states(self, token_ids: torch.Tensor) -> torch.Tensor:
         """Final-norm output for this rank's tokens, ``[local_tokens, d_model]``."""
         B, T = token_ids.shape
         if T > self.context_length:
             raise ValueError(f"Input length {T} exceeds context length {self.context_length}")
-        ids = self._local_tokens(token_ids.reshape(-1))
+        ids = self._local_ids(token_ids)
         stream = self.token_embeddings(ids)
         if self.position_embeddings is not None:
-            positions = torch.arange(T, device=token_ids.device).repeat(B)
-            stream = stream + self.position_embeddings(self._local_tokens(positions))
+            positions = torch.arange(T, device=token_ids.device).repeat(B, 1)
+            stream = stream + self.position_embeddings(self._local_ids(positions))
         shape = (B, T)
         if self.norm_placement == "pre":
             pending = None
@@ -121,7 +129,7 @@ class TransformerLM(nn.Module):
     @property
     def interleave(self) -> int:
         """Micro-batches that :meth:`loss_interleaved` runs side by side (1: the feature is off)."""
-        if self.moe or self.norm_placement != "pre" or self.activation_checkpointing != "none":
+        if self.moe or self.norm_placement != "pre" or self.activation_checkpointing != "none" or self.cp is not None:
             return 1
         return int(getattr(self.tp, "interleave", 1)) if self.tp is not None else int(getattr(self, "_interleave", 1))
 
@@ -215,6 +223,9 @@ class TransformerLM(nn.Module):
         logits = ops.linear(self.hidden_states(token_ids), self.head_weight)
         if self.tp is not None and self.tp.size > 1:
             logits = self.tp.all_gather_cat(logits, 0, differentiable=True)
+        if self.cp is not None:
+            local = logits.reshape(B, T // self.cp.size, self.vocab_size)
+            return self.cp.all_gather_cat(local, 1, differentiable=True)
         return logits.reshape(B, T, self.vocab_size)
 
     def loss(self, token_ids: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0) -> torch.Tensor:
@@ -225,12 +236,14 @@ class TransformerLM(nn.Module):
         gradient the sharded backward needs.
         """
         hidden = self.hidden_states(token_ids)
-        local_targets = self._local_tokens(targets.reshape(-1))
+        local_targets = self._local_ids(targets)
         # replicated data parallelism sets `data_parallel_share = 1 / dp` so that gradients and losses of the
         # replicas add up to those of the global batch with plain sums
         share = float(getattr(self, "data_parallel_share", 1.0))
         if self.tp is not None and self.tp.size > 1:
             share = share / self.tp.size
+        if self.cp is not None:
+            share = share / self.cp.size
         loss = ops.linear_cross_entropy(hidden, self.head_weight, local_targets, loss_scale) * share
         aux = self.aux_loss()
         if aux is not None:

@@ -23,8 +23,12 @@ def fp8_block_gemm(x: torch.Tensor, weight) -> torch.Tensor:
     """``x @ W.T`` with ``x`` quantised on the fly; ``weight`` is an ``engine.quant.Fp8Weight``."""
     xq, sx = quantize_rows(x.to(torch.bfloat16))
     rows, k = xq.shape
-    out = torch.empty(rows, weight.out_features, dtype=torch.bfloat16, device=x.device)
+    n = weight.out_features
+    out = torch.empty(rows, n, dtype=torch.bfloat16, device=x.device)
+    # few rows = few tiles: the K blocks of a tile are then divided over several CTAs whose fp32 parts a second kernel sums
+    splits = int(native.lib().ajb_fp8_block_gemm_splits(rows, n, k))
+    workspace = torch.empty(splits, rows, n, dtype=torch.float32, device=x.device) if splits > 1 else None
     native.call("ajb_fp8_block_gemm", xq.data_ptr(), weight.q.data_ptr(), sx.data_ptr(), weight.scale.data_ptr(),
-                out.data_ptr(), rows, weight.out_features, k, xq.stride(0), weight.q.stride(0), out.stride(0),
-                native.stream_ptr())
+                out.data_ptr(), rows, n, k, xq.stride(0), weight.q.stride(0), out.stride(0), splits,
+                native.ptr(workspace), native.stream_ptr())
     return out.to(x.dtype)

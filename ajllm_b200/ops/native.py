@@ -57,7 +57,9 @@ _SIGNATURES: dict[str, list] = {
     "ajb_add_bf16": [c_void, c_void, c_void, c_long, c_void],
     "ajb_flash_fwd": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_float, c_void],
     "ajb_fp8_quantize_rows": [c_void, c_void, c_void, c_int, c_int, c_void],
-    "ajb_fp8_block_gemm": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_void],
+    "ajb_fp8_block_gemm": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_int,
+                           c_void, c_void],
+    "ajb_fp8_block_gemm_splits": [c_int, c_int, c_int],
     "ajb_moe_route_fwd": [c_void, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void],
     "ajb_moe_assign_slots": [c_void, c_long, c_int, c_int, c_int, c_void, c_void, c_void],
     "ajb_sample_rows": [c_void, c_long, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void],

@@ -10,9 +10,14 @@ is a plain sum.
 from __future__ import annotations
 
 
-def optimizer_classes(mesh, tp=None) -> list[dict]:
-    """Parameter classes for the flat optimizer under (tensor x data) parallelism."""
+def optimizer_classes(mesh, tp=None, cp=None) -> list[dict]:
+    """Parameter classes for the flat optimizer under (tensor x data) parallelism. With context parallelism (``cp``,
+    which then occupies the mesh's innermost axis instead of ``tp``) every parameter is replicated over the group and
+    its gradient, computed from that rank's tokens only, is summed over it."""
     dp_group = mesh.dp.group if mesh.dp_size > 1 else None
+    if cp is not None and cp.size > 1:
+        return [{"name": "replicated", "match": lambda n, p: True,
+                 "reduce_groups": [g for g in (cp.group, dp_group) if g is not None], "norm_groups": []}]
 
     def tp_sharded(name: str, p) -> bool:
         return tp is not None and tp.size > 1 and any(

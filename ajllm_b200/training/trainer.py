@@ -121,10 +121,10 @@ class Trainer:
     def _global_loss(self, local: torch.Tensor) -> float:
         """Device scalar -> host float of the global mean loss (ranks hold shares or replicas)."""
         value = local.detach().float().reshape(1)
-        tp = getattr(self.base_model, "tp", None)
-        if tp is not None and tp.size > 1:
-            value = value.clone()
-            dist.all_reduce(value, op=dist.ReduceOp.SUM, group=tp.group)   # shares add up to the mean
+        for axis in (getattr(self.base_model, "tp", None), getattr(self.base_model, "cp", None)):
+            if axis is not None and axis.size > 1:
+                value = value.clone()
+                dist.all_reduce(value, op=dist.ReduceOp.SUM, group=axis.group)   # shares add up to the mean
         if self.loss_reduce_group is not None:
             if float(getattr(self.base_model, "data_parallel_share", 1.0)) != 1.0:
                 value = value.clone()           # replicas report local_mean / dp: the shares add up to the mean

@@ -107,26 +107,33 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
                           if val_name and val_name in enc_manifest["splits"] else None)
 
     # ---- mesh and model
-    tp = ep = None
+    tp = ep = cp = None
     mesh = None
-    sizes = {"tp": 1, "ep": 1, "fsdp": 1, "pp": 1}
+    sizes = {"tp": 1, "ep": 1, "fsdp": 1, "pp": 1, "cp": 1}
     if world > 1:
         from ajllm_b200.parallel import ParallelMesh
         from ajllm_b200.parallel.contexts import make_expert_parallel, make_tensor_parallel
         defaults = dict(parallel_cfg)
-        if "fsdp" not in defaults and "tp" not in defaults:
+        if "fsdp" not in defaults and "tp" not in defaults and "cp" not in defaults:
             defaults["fsdp"] = world
         sizes = check_parallel(defaults, world)
         if sizes["pp"] != 1 and (sizes["tp"] != 1 or sizes["fsdp"] != 1 or sizes["ep"] != 1):
             raise ValueError("pipeline parallelism runs on its own here: set tp = fsdp = ep = 1 (pp = world size)")
-        mesh = ParallelMesh(tp=sizes["tp"], fsdp=sizes["fsdp"], ep=sizes["ep"], pp=sizes["pp"])
+        # context-parallel peers take the innermost (adjacent-rank) axis, the one tensor parallelism would use
+        mesh = ParallelMesh(tp=sizes["tp"] * sizes["cp"], fsdp=sizes["fsdp"], ep=sizes["ep"], pp=sizes["pp"])
+        if sizes["cp"] > 1:
+            if use_fsdp:
+                raise ValueError("context parallelism runs with replicated data parallelism (acceleration.use_fsdp: false)")
+            from ajllm_b200.parallel.context_parallel import ContextParallel
+            cp = ContextParallel(mesh.tp.group, mesh.tp.rank, mesh.tp.size)
         fused = acceleration.get("fused")
-        tp = make_tensor_parallel(mesh.tp, device, None if fused is None else bool(fused))
+        if cp is None:
+            tp = make_tensor_parallel(mesh.tp, device, None if fused is None else bool(fused))
         ep = make_expert_parallel(mesh.ep, device, None if fused is None else bool(fused))
     from ajllm_b200.parallel.contexts import expert_exchange_backend, tp_backend
     checkpointing = str(acceleration.get("activation_checkpointing", "layer" if use_fsdp else "none"))
     dtype = compute_dtype
-    model = build_model(model_cfg, vocab_size, bool(acceleration.get("use_flash_attention", False)), tp=tp, ep=ep,
+    model = build_model(model_cfg, vocab_size, bool(acceleration.get("use_flash_attention", False)), tp=tp, ep=ep, cp=cp,
                         activation_checkpointing="none" if use_fsdp else checkpointing)
     model = model.to(device=device, dtype=dtype)
     parameter_count = sum(p.numel() for p in model.parameters())
@@ -157,7 +164,7 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
         loss_group = mesh.dp.group
     elif mesh is not None:
         from ajllm_b200.parallel.data_parallel import optimizer_classes
-        optimizer = FlatAdamW(model, classes=optimizer_classes(mesh, tp), **_optimizer_kwargs(data))
+        optimizer = FlatAdamW(model, classes=optimizer_classes(mesh, tp, cp), **_optimizer_kwargs(data))
         loss_group = mesh.dp.group if dp_size > 1 else None
         if dp_size > 1:
             model.data_parallel_share = 1.0 / dp_size
@@ -171,7 +178,7 @@ def run(config: LoadedConfig, run_directory: Path | None = None) -> dict[str, An
         note = describe_device_choice(requested, device)
         if note:
             print(f"  device note: {note}")
-        print(f"  world size: {world}  mesh: tp={sizes['tp']} fsdp={sizes['fsdp']} ep={sizes['ep']}")
+        print(f"  world size: {world}  mesh: tp={sizes['tp']} cp={sizes['cp']} fsdp={sizes['fsdp']} ep={sizes['ep']}")
         print(f"  train tokens: {len(train_dataset):,}")
         if validation_dataset is not None:
             print(f"  validation tokens: {len(validation_dataset):,}")

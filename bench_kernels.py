@@ -1,5 +1,6 @@
 """Kernel microbenchmarks on one B200: the tcgen05 GEMM against cuBLAS on the layer shapes of the flagship
-model, the attention kernels, the fused norm kernels, and the tensor-pipe probe.
+model, the attention kernels, the fused norm kernels, paged decode attention with and without the split over the keys,
+the sampler, the block-scaled fp8 GEMM, and the gradient reduce-scatter kernel emulated on one GPU.
 
     python bench_kernels.py                      # everything, full-size shapes
     python bench_kernels.py --case flash --small # a small case (for a profiler capture)
@@ -129,9 +130,114 @@ def run_decode_gemm(dev, small: bool) -> None:
                 del w
 
 
+def run_paged(dev, small: bool) -> None:
+    """Decode attention over a paged cache: bytes = K and V of every cached token, once. Few sequences with long contexts
+    are where cutting a sequence over several CTAs matters; many sequences fill the device on their own."""
+    from ajllm_b200.engine.kv_cache import PagedKVCache
+    from ajllm_b200.ops import serving
+
+    heads, kv_heads, hd = 32, 8, 128
+    cases = ((16, 2048),) if small else ((16, 1024), (16, 4096), (64, 2048), (256, 1280))
+    for seqs, ctx in cases:
+        blocks_per = (ctx + 15) // 16
+        cache = PagedKVCache(1, seqs * blocks_per + 1, 16, kv_heads, hd, torch.bfloat16, dev)
+        cache.keys[0].normal_(0, 0.5)
+        cache.values[0].normal_(0, 0.5)
+        tables = torch.arange(seqs * blocks_per, dtype=torch.int32, device=dev).view(seqs, blocks_per)
+        q = (torch.randn(seqs, heads, hd, device=dev) * 0.5).to(torch.bfloat16)
+        plan = serving.PagedPlan(tables, [1] * seqs, [ctx] * seqs, heads, kv_heads)
+        nbytes = 2 * seqs * ctx * kv_heads * hd * 2
+        line = f"paged decode {seqs:3d} seqs x {ctx:4d} keys:"
+        for label, forced in (("one CTA per (seq, kv head)", 1), ("split", None)):
+            original = serving.paged_splits
+            if forced is not None:
+                serving.paged_splits = lambda ctas, max_context: 1
+            try:
+                t = timeit(lambda: serving.paged_attention_planned(q, cache.keys[0], cache.values[0], plan), iters=20)
+                parts = serving.paged_splits(seqs * kv_heads, ctx)
+            finally:
+                serving.paged_splits = original
+            line += f"  {label} ({parts} part{'s' if parts > 1 else ''}) {t * 1e3:6.1f} us {nbytes / t / 1e6:6.0f} GB/s |"
+        print(line, flush=True)
+
+
+def run_sampler(dev, small: bool) -> None:
+    from ajllm_b200.ops import serving
+
+    vocab = 128256
+    for rows in ((16,) if small else (16, 64, 256)):
+        logits = torch.randn(rows, vocab, device=dev)
+        zeros = torch.zeros(rows, device=dev)
+        ones = torch.ones(rows, device=dev)
+        seeds = torch.arange(rows, dtype=torch.int64, device=dev)
+        counters = torch.zeros(rows, dtype=torch.int64, device=dev)
+        greedy = timeit(lambda: serving.sample_rows(logits, zeros, ones, seeds, counters), iters=20)
+        sampled = timeit(lambda: serving.sample_rows(logits, ones, ones, seeds, counters), iters=20)
+        nbytes = rows * vocab * 4
+        print(f"sampler {rows:3d} rows x {vocab}: greedy {greedy * 1e3:6.1f} us ({nbytes / greedy / 1e6:5.0f} GB/s) | "
+              f"temperature 1 {sampled * 1e3:6.1f} us", flush=True)
+
+
+def run_fp8(dev, small: bool) -> None:
+    """Block-scaled fp8 GEMM (128 x 128 weight blocks, per-token activation scales) against the bf16 GEMM of the same shape."""
+    from ajllm_b200.engine.quant import Fp8Weight, fp8_linear
+
+    shapes = ((4096, 4096, 4096),) if small else ((64, 6144, 4096), (64, 28672, 4096), (4096, 6144, 4096), (8192, 28672, 4096))
+    with torch.no_grad():
+        for m, n, k in shapes:
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            w = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+            q = Fp8Weight.from_dense(w)
+            t8 = timeit(lambda: fp8_linear(x, q))
+            t16 = timeit(lambda: ops.linear(x, w))
+            flops = 2 * m * n * k
+            print(f"fp8 block-scaled m{m} n{n} k{k}: fp8 {t8 * 1e3:8.1f} us {flops / t8 / 1e9:7.1f} TF | bf16 {t16 * 1e3:8.1f} us "
+                  f"{flops / t16 / 1e9:7.1f} TF", flush=True)
+
+
+def run_grad_reduce(dev, small: bool) -> None:
+    """The gradient reduce-scatter kernel as rank 0 of a group whose peers' buffers are tensors on this device and whose
+    handshake words are preset (nothing crosses NVLink: this is the kernel's own cost at HBM speed)."""
+    import ctypes
+
+    from ajllm_b200.parallel.grad_reduce import FusedGradReduce, _Args
+    fn = native.lib().ajb_grad_reduce_scatter
+    fn.argtypes = [ctypes.POINTER(_Args), ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    for world in ((2,) if small else (2, 8)):
+        shard = (8 if small else 32) * 1024 * 1024
+        buffers = [torch.randn(world * shard, device=dev) for _ in range(world)]
+        flags = torch.zeros(32, dtype=torch.int32, device=dev)
+        counter = torch.zeros(4, dtype=torch.int32, device=dev)
+        dst = torch.zeros(shard, device=dev)
+        partials = torch.zeros(FusedGradReduce.CTAS, device=dev)
+        epoch = [0]
+
+        def launch():
+            epoch[0] += 1
+            flags[:16] = epoch[0]          # every peer's "ready" and "done" word for this call
+            a = _Args()
+            a.world, a.rank, a.shard_elems = world, 0, shard
+            for r in range(world):
+                a.full_ptrs[r] = buffers[r].data_ptr()
+                a.ready_ptrs[r] = flags.data_ptr()
+                a.done_ptrs[r] = flags.data_ptr() + 8 * 4
+            a.dst, a.accumulate, a.scale = dst.data_ptr(), 1, 1.0
+            a.sumsq_partials, a.ctas = partials.data_ptr(), FusedGradReduce.CTAS
+            a.epoch, a.local_counter = epoch[0], counter.data_ptr()
+            assert fn(ctypes.byref(a), native.stream_ptr()) == 0
+
+        t = timeit(launch, iters=10)
+        nbytes = (world + 2) * shard * 4        # world slices read, the shard read and written
+        print(f"grad reduce-scatter as rank 0 of {world}: shard {shard * 4 / 2**20:.0f} MiB, {t * 1e3:7.1f} us "
+              f"{nbytes / t / 1e6:6.0f} GB/s", flush=True)
+    print("kernel status", native.check_status(False))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--case", default="all", choices=["all", "gemm", "decode", "flash", "flash64", "norm"])
+    ap.add_argument("--case", default="all", choices=["all", "gemm", "decode", "flash", "flash64", "norm", "paged", "sampler",
+                                                      "fp8", "grad_reduce"])
     ap.add_argument("--small", action="store_true", help="one small shape per case (a few hundred MB on the device)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -148,6 +254,14 @@ def main() -> None:
         run_flash(dev, args.small, head_dim=64)
     if args.case in ("all", "norm"):
         run_norm(dev, args.small)
+    if args.case in ("all", "paged"):
+        run_paged(dev, args.small)
+    if args.case in ("all", "sampler"):
+        run_sampler(dev, args.small)
+    if args.case in ("all", "fp8"):
+        run_fp8(dev, args.small)
+    if args.case in ("all", "grad_reduce"):
+        run_grad_reduce(dev, args.small)
     print("kernel status", native.lib().ajb_check_status())
 
 
