@@ -51,7 +51,7 @@ def test_dotted_override_and_validators():
         check_model({"name": "m", "context_length": 8, "d_model": 32, "num_layers": 1, "num_heads": 4, "num_kv_heads": 3})
     with pytest.raises(ConfigError):
         check_tokenizer({"name": "t", "vocab_size": 256, "special_tokens": ["<s>"]})
-    assert check_parallel({"tp": 2}, 8) == {"tp": 2, "ep": 1, "fsdp": 4, "pp": 1}
+    assert check_parallel({"tp": 2}, 8) == {"tp": 2, "ep": 1, "fsdp": 4, "pp": 1, "cp": 1}
     with pytest.raises(ConfigError):
         check_parallel({"tp": 3}, 8)
 
