@@ -3,16 +3,22 @@
 // One CTA serves one (sequence, KV head): the `group * q_len` query rows that share this KV head
 // (group = Hq / Hkv query heads, q_len new tokens: 1 for plain decoding, k + 1 when verifying k draft
 // tokens) form the top rows of a 128-row tcgen05 tile, so every K/V byte of the sequence is read once
-// for all of them. K/V tiles of 128 tokens are assembled from the sequence's 16-token cache blocks by
+// for all of them. K/V tiles of 64 tokens are assembled from the sequence's 16-token cache blocks by
 // TMA (one box per block, addressed through the block table); S = Q K^T and O += P V run on the tensor
 // cores with accumulators in tensor memory, exactly as in the training forward kernel, but only the
 // softmax warps whose 32-row quarter holds real rows do any work. Row (head h, new token i) may see
 // keys 0 .. context_len - q_len + i.
 //
+// The kernel streams the cache once and does little arithmetic per byte, so what matters is how many bytes are in
+// flight per SM. A step (wait for the tile, one product, a softmax over it, a second product) is a dependent chain
+// of a couple of microseconds; one CTA per SM with two 128-key stages kept about one tile in flight and reached 0.4
+// of the copy bandwidth. Tiles of 64 keys halve the shared memory of a CTA (113 KB) and its tensor memory (256
+// columns), so two CTAs share an SM and each one's chain hides behind the other's loads.
+//
 // Plain decoding has 4 to 8 real rows, all in the first quarter, and one warp would do the softmax of
-// 128 columns per tile while three idle. With at most 32 rows (REPL) the query rows are therefore staged
+// all key columns of a tile while three idle. With at most 32 rows (REPL) the query rows are therefore staged
 // four times, once per 32-lane quarter: the score tile then holds four identical copies, and warp q
-// works on key columns [32 q, 32 q + 32) of its own copy. The four partial row maxima (and at the end the
+// works on key columns [16 q, 16 q + 16) of its own copy. The four partial row maxima (and at the end the
 // partial row sums) are exchanged through shared memory; P is assembled in rows 0..31 of the operand
 // tile, so only the first quarter of O is meaningful and the first warp alone rescales and stores it.
 //
@@ -29,7 +35,8 @@
 namespace ajb {
 namespace paged {
 
-constexpr int TILE = 128;          // keys per step
+constexpr int TILE = 64;           // keys per step
+constexpr int QROWS = 128;         // rows of the query / probability operand tiles (the MMA's M)
 constexpr int BLOCK_TOKENS = 16;   // tokens per cache block
 constexpr int kThreads = 192;
 constexpr int kMaxRows = 64;       // group * q_len
@@ -38,11 +45,15 @@ constexpr int kPagedKernelId = 5;
 
 template <int HD>
 struct Cfg {
-  static constexpr int kTile = TILE * HD * 2;
-  static constexpr int kP = TILE * TILE * 2;
-  static constexpr int kExchange = 2 * 4 * 32 * 4;   // [parity][quarter][row] partial maxima / sums (REPL)
-  static constexpr int kSmem = kTile /*Q*/ + 4 * kTile /*2 x (K,V)*/ + kP + kExchange + 256;
-  static constexpr int kOCol = 256;
+  static constexpr int kQ = QROWS * HD * 2;          // the query rows, staged once
+  static constexpr int kTile = TILE * HD * 2;        // one K or V tile
+  static constexpr int kP = QROWS * TILE * 2;        // probabilities of one step (A operand of P V)
+  // [parity][quarter][row] partial maxima / sums of the REPL variant live in rows 64.. of the P tile: with at most 32
+  // real rows those operand rows only feed accumulator rows that nobody reads
+  static constexpr int kExchangeOffset = 64 * 128;
+  static constexpr int kSmem = kQ + 4 * kTile /*2 x (K,V)*/ + kP + 256;
+  static constexpr int kOCol = 2 * TILE;             // S0 at 0, S1 at TILE, O behind them
+  static constexpr int kTmemCols = 256;              // 2 * 64 + HD <= 256: two CTAs fit the SM's 512 columns
 };
 
 struct Params {
@@ -60,23 +71,24 @@ struct Params {
   DeviceStatus* status;
 };
 
+// 16-byte chunk `ch` of row `row` of a K-major operand tile of QROWS rows (128-byte swizzle, 64-element boxes).
 __device__ __forceinline__ void store_chunk(uint8_t* tile, int row, int ch, uint4 val) {
-  uint8_t* dst = tile + (ch >> 3) * (TILE * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+  uint8_t* dst = tile + (ch >> 3) * (QROWS * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
   *reinterpret_cast<uint4*>(dst) = val;
 }
 
 template <int HD, bool REPL>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const Params p) {
   using C = Cfg<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + C::kTile;
+  uint8_t* sKV = sQ + C::kQ;
   uint8_t* sP = sKV + 4 * C::kTile;
-  float* sExchange = reinterpret_cast<float*>(sP + C::kP);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kP + C::kExchange);
+  float* sExchange = reinterpret_cast<float*>(sP + C::kExchangeOffset);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kP);
   if (smem_misaligned(smem, p.status, kPagedKernelId, reinterpret_cast<uint32_t*>(bars) + 60)) return;
   uint64_t* kv_full = bars;        // 2
   uint64_t* kv_empty = bars + 2;   // 2
@@ -117,7 +129,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     prefetch_tensor_map(&map_v);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
   // stage Q: rows beyond `rows` are zero (their scores are never used)
@@ -162,8 +174,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       }
     }
   } else if (warp == 1) {
-    constexpr uint32_t idesc_s = make_idesc(TILE, TILE, 1, false, false);
-    constexpr uint32_t idesc_o = make_idesc(TILE, HD, 1, false, true);
+    constexpr uint32_t idesc_s = make_idesc(QROWS, TILE, 1, false, false);
+    constexpr uint32_t idesc_o = make_idesc(QROWS, HD, 1, false, true);
     // descriptor low words; a k-step is a compile-time offset added to one of these (see common.cuh)
     const uint32_t q_km = desc_lo_k_major(smem_u32(sQ)), p_km = desc_lo_k_major(smem_u32(sP));
     const uint32_t k_km0 = desc_lo_k_major(smem_u32(sKV));
@@ -182,7 +194,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         umma_f16_c<false>(d, desc_at(q_km, 0), desc_at(k_km, 0), idesc_s);
 #pragma unroll
         for (int k = 1; k < HD / 16; ++k)
-          umma_f16_c<true>(d, desc_at(q_km, k_major_step(k, TILE * 128)), desc_at(k_km, k_major_step(k, TILE * 128)), idesc_s);
+          umma_f16_c<true>(d, desc_at(q_km, k_major_step(k, QROWS * 128)), desc_at(k_km, k_major_step(k, TILE * 128)), idesc_s);
         tc_commit(&s_full[s]);
       }
       __syncwarp();
@@ -201,21 +213,21 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         umma_f16(tmem_base + C::kOCol, desc_at(p_km, 0), desc_at(v_mn, 0), idesc_o, j != 0);
 #pragma unroll
         for (int k = 1; k < TILE / 16; ++k)
-          umma_f16_c<true>(tmem_base + C::kOCol, desc_at(p_km, k_major_step(k, TILE * 128)), desc_at(v_mn, mn_major_step(k)), idesc_o);
+          umma_f16_c<true>(tmem_base + C::kOCol, desc_at(p_km, k_major_step(k, QROWS * 128)), desc_at(v_mn, mn_major_step(k)), idesc_o);
         tc_commit(pv_done);
         tc_commit(&kv_empty[j & 1]);
       }
       __syncwarp();
     }
   } else if (REPL) {
-    // ---- at most 32 query rows, copied into every quarter: warp q handles key columns [32 q, 32 q + 32)
+    // ---- at most 32 query rows, copied into every quarter: warp q handles key columns [16 q, 16 q + 16)
     const int quarter = warp & 3;
     const bool real = lane < rows;
     const int h = real ? lane / p.q_len : 0, qi = real ? lane % p.q_len : 0;
     const int k_max = real ? ctx - p.q_len + qi : -1;   // last visible key
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float sl = p.scale * kLog2e;
-    float m_run = -INFINITY, l_run = 0.0f;              // l_run: this warp's 32 columns of every tile only
+    float m_run = -INFINITY, l_run = 0.0f;              // l_run: this warp's 16 columns of every tile only
     bool ok = true;
     // publishes `mine`, waits (bounded) for the other three warps, returns all four values of this row
     auto exchange = [&](uint32_t phase, float mine, float (&all)[4]) -> bool {
@@ -232,16 +244,16 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int s = j & 1;
       if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kPagedKernelId, 6)) { ok = false; break; }
       tc_fence_after_sync();
-      const int k0 = (t0 + j) * TILE + quarter * 32;
-      uint32_t sv[32];
-      tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * TILE + quarter * 32), sv);
+      const int k0 = (t0 + j) * TILE + quarter * 16;
+      uint32_t sv[16];
+      tmem_ld_32x16(tmem_base + lane_addr + (uint32_t)(s * TILE + quarter * 16), sv);
       tc_wait_ld();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[s]);
       float m_loc = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < 16; ++i) {
         float x = __uint_as_float(sv[i]);
         if (k0 + i > k_max) x = -INFINITY;
         sv[i] = __float_as_uint(x);
@@ -257,9 +269,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const float alpha = moved ? exp2f((m_run - m_safe) * sl) : 1.0f;
       const float neg = -m_safe * sl;
       float l_tile = 0.0f;
-      uint32_t pk[16];
+      uint32_t pk[8];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
+      for (int i = 0; i < 16; i += 2) {
         const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sl, neg));
         const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl, neg));
         l_tile += p0 + p1;
@@ -271,8 +283,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       tc_fence_after_sync();
       // P row `lane`, key columns of this warp: rows 32..127 of the operand tile are never read back
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch)
-        store_chunk(sP, lane, quarter * 4 + ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
+      for (int ch = 0; ch < 2; ++ch)
+        store_chunk(sP, lane, quarter * 2 + ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
       if (quarter == 0 && j > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
@@ -349,17 +361,17 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       if (!mbar_wait(&s_full[s], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kPagedKernelId, 6)) { ok = false; break; }
       tc_fence_after_sync();
       const int k0 = (t0 + j) * TILE;
-      uint32_t pk[64];
+      uint32_t pk[TILE / 2];
       float alpha = 1.0f;
       bool moved = false;
       if (active) {
-        uint32_t sv[4][32];
+        uint32_t sv[TILE / 32][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * TILE + c * 32), sv[c]);
+        for (int c = 0; c < TILE / 32; ++c) tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(s * TILE + c * 32), sv[c]);
         tc_wait_ld();
         float m_tile = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < TILE / 32; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float x = __uint_as_float(sv[c][i]);
@@ -376,7 +388,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const float neg = -m_safe * sl;
         float l_tile = 0.0f;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < TILE / 32; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const float p0 = exp2f(fmaf(__uint_as_float(sv[c][i]), sl, neg));
@@ -389,7 +401,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         m_run = m_new;
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) pk[i] = 0u;
+        for (int i = 0; i < TILE / 2; ++i) pk[i] = 0u;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -399,7 +411,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       // inactive quarters write their (zero) rows only once: they never change
       if (active || j == 0) {
 #pragma unroll
-        for (int ch = 0; ch < 16; ++ch) store_chunk(sP, row, ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
+        for (int ch = 0; ch < TILE / 8; ++ch) store_chunk(sP, row, ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
       }
       if (active && j > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
@@ -465,7 +477,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -523,6 +535,11 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, const
   if (!configured) {
     AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    // two CTAs per SM need the whole shared-memory carve-out
+    AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD, false>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared));
+    AJB_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<HD, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared));
     configured = true;
   }
   Params p;

@@ -59,8 +59,8 @@ def paged_attention_planned(q: torch.Tensor, key_cache: torch.Tensor, value_cach
     num_blocks, block_size = key_cache.shape[0], key_cache.shape[1]
     for q_len, count, tables, starts, ctxs in plan.launches:
         # few (sequence, KV head) pairs cannot fill the device: cut every sequence's keys over several CTAs, up to
-        # one CTA per SM (the kernel's shared memory admits one) and never more parts than the longest context has
-        # 128-key tiles
+        # two CTAs per SM (what the kernel's shared memory admits) and never more parts than the longest context has
+        # 64-key tiles
         max_context = getattr(plan, "max_context", None) or tables.shape[1] * block_size
         splits = paged_splits(count * kv_heads, max_context)
         part_o = part_ml = None
@@ -81,8 +81,8 @@ def paged_splits(ctas: int, max_context: int) -> int:
     """Parts per sequence for the paged-attention kernel given the (sequence, KV head) pairs of a launch."""
     if not _SM_COUNT:
         _SM_COUNT.append(int(native.lib().ajb_sm_count()))
-    want = _SM_COUNT[0] // max(1, ctas)
-    tiles = max(1, (max_context + 127) // 128)
+    want = (2 * _SM_COUNT[0]) // max(1, ctas)
+    tiles = max(1, (max_context + 63) // 64)
     return max(1, min(want, tiles, 16))
 
 

@@ -17,8 +17,11 @@ import torch
 import torch.distributed as dist
 
 
-def init_distributed(device_type: str = "auto", timeout_s: float = 1800.0) -> tuple[int, int, torch.device]:
-    """Join the env:// rendezvous when launched by torchrun; returns ``(rank, world, device)``."""
+def init_distributed(device_type: str = "auto", timeout_s: float | None = None) -> tuple[int, int, torch.device]:
+    """Join the env:// rendezvous when launched by torchrun; returns ``(rank, world, device)``. The process-group
+    timeout is ``timeout_s``, else ``AJB_DIST_TIMEOUT_S``, else 30 minutes."""
+    if timeout_s is None:
+        timeout_s = float(os.environ.get("AJB_DIST_TIMEOUT_S", "1800"))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

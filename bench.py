@@ -528,8 +528,10 @@ def _child(script: str, extra: list[str], port_offset: int, limit_s: float) -> d
     if "MASTER_PORT" in env:
         env["MASTER_PORT"] = str(int(env["MASTER_PORT"]) + port_offset)
     env.setdefault("MASTER_ADDR", "127.0.0.1")
-    # the child hosts its own rendezvous store instead of joining the launcher's
+    # the child hosts its own rendezvous store instead of joining the launcher's, and gives up quickly on a peer
+    # that never arrives
     env.pop("TORCHELASTIC_USE_AGENT_STORE", None)
+    env.setdefault("AJB_DIST_TIMEOUT_S", "180")
     rank = int(env.get("RANK", "0"))
     with tempfile.NamedTemporaryFile("w+", suffix=f".rank{rank}.log", delete=False) as log:
         proc = subprocess.Popen([sys.executable, str(ROOT / script), *extra], stdout=log, stderr=subprocess.STDOUT,
@@ -553,24 +555,61 @@ def _child(script: str, extra: list[str], port_offset: int, limit_s: float) -> d
     return {"error": f"no result (exit {code}): " + text[-400:].replace("\n", " | ")}
 
 
+SECONDARY_BUDGET_S = 480.0       # no further secondary workload starts once this much time has gone into them
+
+
 def run_secondary(args, impl: str) -> dict:
     world = args.gpus
     common = ["--gpus", str(world), "--child", "--no-secondary", "--impl", impl]
     out: dict = {}
+    started = time.perf_counter()
+
+    rank = int(os.environ.get("RANK", "0"))
+    tag = f'{os.environ.get("TORCHELASTIC_RUN_ID", "single")}_{os.environ.get("MASTER_PORT", "0")}'
+
+    def child(name: str, script: str, extra: list[str], port_offset: int, limit_s: float) -> None:
+        # rank 0 decides whether there is time left and tells the other ranks of the node through a file, so that
+        # either every rank starts its child or none does
+        note = Path(tempfile.gettempdir()) / f"ajb_bench_{tag}_{impl}_{name}.go"
+        if rank == 0:
+            left = SECONDARY_BUDGET_S - (time.perf_counter() - started)
+            go = left >= 45.0
+            note.write_text(f"{int(go)} {max(60.0, min(limit_s, left + 60.0)):.0f}")
+        else:
+            waited = 0.0
+            while not note.exists() and waited < 90.0:
+                time.sleep(0.2)
+                waited += 0.2
+        try:
+            flag, limit = note.read_text().split()
+            go, limit_s = flag == "1", float(limit)
+        except (OSError, ValueError):
+            go = False
+        if not go:
+            out[name] = {"skipped": "the time set aside for the secondary workloads of this run was used up"}
+        else:
+            out[name] = _child(script, extra, port_offset, limit_s)
+        if rank == 0:
+            time.sleep(1.0)                 # the other ranks have read the note by now
+            note.unlink(missing_ok=True)
+
     if impl == "ours":
-        out["dense1p3b_mha16"] = _child("bench.py", [*common, "--workload", "dense1p3b_tp", "--kv-heads", "16",
-                                                     "--steps", "3", "--warmup", "3"], 11, 240)
+        child("serve_8b", "bench_serve.py", ["--gpus", str(world), "--suite"], 17, 300)
         skip = _fits(8.03e9, world, "the 8B decoder")
-        out["dense8b_fsdp"] = {"skipped": skip} if skip else _child(
-            "bench.py", [*common, "--workload", "dense8b_fsdp", "--steps", "2", "--warmup", "3"], 13, 420)
+        if skip:
+            out["dense8b_fsdp"] = {"skipped": skip}
+        else:
+            child("dense8b_fsdp", "bench.py", [*common, "--workload", "dense8b_fsdp", "--steps", "2", "--warmup", "3"], 13, 300)
         skip = _fits(13.9e9, world, "the 64-expert model")
-        out["moe64e_ep"] = {"skipped": skip} if skip else _child(
-            "bench.py", [*common, "--workload", "moe64e_ep", "--steps", "3", "--warmup", "3"], 15, 300)
-        out["serve_8b"] = _child("bench_serve.py", ["--gpus", str(world), "--suite"], 17, 480)
+        if skip:
+            out["moe64e_ep"] = {"skipped": skip}
+        else:
+            child("moe64e_ep", "bench.py", [*common, "--workload", "moe64e_ep", "--steps", "3", "--warmup", "3"], 15, 240)
+        child("dense1p3b_mha16", "bench.py", [*common, "--workload", "dense1p3b_tp", "--kv-heads", "16", "--steps", "3",
+                                             "--warmup", "3"], 11, 200)
     else:
-        out["dense8b_fsdp"] = _child("bench.py", [*common, "--workload", "dense8b_fsdp", "--steps", "2", "--warmup", "3"],
-                                     13, 420)
-        out["serve_8b"] = _child("bench_serve.py", ["--gpus", str(world), "--impl", "reference", "--requests", "3"], 17, 420)
+        child("serve_8b", "bench_serve.py", ["--gpus", str(world), "--impl", "reference", "--requests", "3"], 17, 300)
+        child("dense8b_fsdp", "bench.py", [*common, "--workload", "dense8b_fsdp", "--steps", "2", "--warmup", "3"], 13, 300)
         out["moe64e_ep"] = {"impl": "reference", "unavailable": "the reference has no mixture-of-experts layer and no expert parallelism"}
     return out
 

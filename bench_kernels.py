@@ -234,10 +234,76 @@ def run_grad_reduce(dev, small: bool) -> None:
     print("kernel status", native.check_status(False))
 
 
+def run_moe_exchange(dev, small: bool) -> None:
+    """Expert dispatch (push) and combine (pull) as rank 0 of an 8-rank group whose peers' buffers are tensors on this
+    device and whose handshake words are preset: the kernels' own cost at HBM speed, nothing crosses NVLink."""
+    import ctypes
+
+    from ajllm_b200.parallel.moe_exchange import _Args
+    lib = native.lib()
+    push, pull = lib.ajb_moe_push_rows, lib.ajb_moe_pull_rows
+    push.argtypes = [ctypes.POINTER(_Args), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    pull.argtypes = [ctypes.POINTER(_Args), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    push.restype = pull.restype = ctypes.c_int
+    ep, local_experts, top_k, dim = 8, 8, 6, 2048
+    tokens = 4096 if small else 16384
+    experts = ep * local_experts
+    capacity = int(1.25 * tokens * top_k / experts)
+    stride = (capacity + 127) // 128 * 128
+    choice = torch.rand(tokens, experts, device=dev).topk(top_k, dim=1).indices
+    # position of each assignment inside its expert = its rank among the assignments to that expert
+    flat = choice.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    ranks = torch.empty_like(order)
+    counts = torch.bincount(flat, minlength=experts)
+    starts = torch.cumsum(counts, 0) - counts
+    ranks[order] = torch.arange(flat.numel(), device=dev) - starts[flat[order]]
+    slots = torch.where(ranks < capacity, flat * stride + ranks, torch.full_like(flat, -1)).view(tokens, top_k).to(torch.int32)
+    rows = torch.randn(tokens, dim, device=dev).to(torch.bfloat16)
+    gates = torch.rand(tokens, top_k, device=dev)
+    buffers = [torch.zeros(local_experts * ep * stride, dim, device=dev, dtype=torch.bfloat16) for _ in range(ep)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(ep)]
+    counts_sym = [torch.zeros(4096, dtype=torch.int32, device=dev) for _ in range(ep)]
+    kept = counts.clamp(max=capacity).to(torch.int32)
+    local = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = torch.empty(tokens, dim, device=dev, dtype=torch.bfloat16)
+    epoch = [0]
+
+    def args():
+        epoch[0] += 1
+        flags[0][:24] = epoch[0]            # arrival, release and ready words of every peer for this call
+        a = _Args()
+        a.tokens, a.top_k, a.dim, a.ep, a.rank = tokens, top_k, dim, ep, 0
+        a.local_experts, a.stride = local_experts, stride
+        a.slots = slots.data_ptr()
+        for r in range(ep):
+            a.peer_buffers[r] = buffers[r].data_ptr()
+            a.flag_ptrs[r] = flags[r].data_ptr()
+            a.peer_counts[r] = counts_sym[r].data_ptr()
+        a.counts = kept.data_ptr()
+        a.epoch, a.local_counter = epoch[0], local.data_ptr()
+        return a
+
+    def do_push():
+        a = args()
+        assert push(ctypes.byref(a), rows.data_ptr(), None, native.stream_ptr()) == 0
+
+    def do_pull():
+        a = args()
+        assert pull(ctypes.byref(a), out.data_ptr(), gates.data_ptr(), None, None, native.stream_ptr()) == 0
+
+    moved = int((slots >= 0).sum()) * dim * 2
+    t_push, t_pull = timeit(do_push), timeit(do_pull)
+    print(f"expert dispatch as rank 0 of {ep}: {tokens} tokens x top-{top_k}, {moved / 1e6:.0f} MB of rows: push {t_push * 1e3:7.1f} us "
+          f"({2 * moved / t_push / 1e6:5.0f} GB/s read + written) | pull + weighted sum {t_pull * 1e3:7.1f} us "
+          f"({moved / t_pull / 1e6:5.0f} GB/s read)", flush=True)
+    print("kernel status", native.check_status(False))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--case", default="all", choices=["all", "gemm", "decode", "flash", "flash64", "norm", "paged", "sampler",
-                                                      "fp8", "grad_reduce"])
+                                                      "fp8", "grad_reduce", "moe_exchange"])
     ap.add_argument("--small", action="store_true", help="one small shape per case (a few hundred MB on the device)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -262,6 +328,8 @@ def main() -> None:
         run_fp8(dev, args.small)
     if args.case in ("all", "grad_reduce"):
         run_grad_reduce(dev, args.small)
+    if args.case in ("all", "moe_exchange"):
+        run_moe_exchange(dev, args.small)
     print("kernel status", native.lib().ajb_check_status())
 
 
