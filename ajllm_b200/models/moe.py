@@ -40,7 +40,8 @@ def route_tokens(logits: torch.Tensor, top_k: int, capacity: int, normalize_gate
     Returns ``(gates [N,k] fp32, experts [N,k], slots [N,k], aux_terms)`` where ``slots`` is the row of
     the ``[E * stride]`` dispatch buffer an assignment lands in (``stride`` defaults to ``capacity``; a
     larger stride pads every expert's region), or ``-1`` when it was dropped, and
-    ``aux_terms = (f [E], P [E])``. On a GPU the slot assignment is one kernel (one CTA per expert scans
+    ``aux_terms = (f [E], P [E], kept [E])`` with ``kept`` the int32 number of assignments every expert accepted
+    (``min(count, capacity)``). On a GPU the slot assignment is one kernel (one CTA per expert scans
     the assignments in order); gates and probabilities stay in autograd.
     """
     tokens, num_experts = logits.shape
@@ -59,6 +60,7 @@ def route_tokens(logits: torch.Tensor, top_k: int, capacity: int, normalize_gate
         counts = torch.bincount(flat_expert, minlength=num_experts)
         slots = slots.long()
     else:
+        kept = None
         order = torch.argsort(flat_expert, stable=True)
         counts = torch.bincount(flat_expert, minlength=num_experts)
         starts = torch.cumsum(counts, 0) - counts
@@ -67,7 +69,9 @@ def route_tokens(logits: torch.Tensor, top_k: int, capacity: int, normalize_gate
         slots = torch.where(position < capacity, flat_expert * stride + position, torch.full_like(position, -1))
     fraction = counts.float() / float(tokens * top_k)
     mean_prob = probs.mean(dim=0)
-    return gates, experts, slots.reshape(tokens, top_k), (fraction, mean_prob)
+    if kept is None:
+        kept = counts.clamp(max=capacity).to(torch.int32)
+    return gates, experts, slots.reshape(tokens, top_k), (fraction, mean_prob, kept)
 
 
 def capacity_for(tokens: int, top_k: int, num_experts: int, capacity_factor: float) -> int:
@@ -170,12 +174,12 @@ class MoEFeedForward(nn.Module):
         if k2 in state:
             state[prefix + "experts.w2"] = state.pop(k2)[mine].contiguous()
 
-    def _forward_fused(self, flat, gates, experts, slots, kept, capacity, stride, exchange) -> torch.Tensor:
+    def _forward_fused(self, flat, gates, slots, counts, stride, exchange) -> torch.Tensor:
         """Expert-parallel path over symmetric memory: rows go straight to the owning rank's expert-major buffer,
-        experts run as batched GEMMs that skip padding, outputs are read back and gate-weighted in one kernel."""
+        experts run as batched GEMMs that skip padding, outputs are read back and gate-weighted in one kernel.
+        ``counts`` (int32 ``[E]``) are the rows every expert accepted from this rank; nothing here waits for the host."""
         from ajllm_b200.parallel import moe_exchange
 
-        counts = torch.bincount(experts[kept], minlength=self.num_experts).to(torch.int32)
         slots32 = slots.to(torch.int32).contiguous()
         grouped = moe_exchange.dispatch(flat, slots32, counts, exchange, self.num_local, stride)
         valid = exchange.received_counts(self.num_local)
@@ -194,14 +198,14 @@ class MoEFeedForward(nn.Module):
         # on a GPU every expert's region is padded to whole 128-row tiles so the batched GEMM can skip padding
         stride = (capacity + 127) // 128 * 128 if on_gpu else capacity
         logits = ops.reference.linear(flat.float(), self.router.float())
-        gates, experts, slots, (fraction, mean_prob) = route_tokens(logits, self.top_k, capacity,
-                                                                  self.normalize_gates, stride)
+        gates, experts, slots, (fraction, mean_prob, kept_counts) = route_tokens(logits, self.top_k, capacity,
+                                                                               self.normalize_gates, stride)
         self.last_aux_loss = self.aux_loss_coef * self.num_experts * torch.sum(fraction.detach() * mean_prob)
         kept = slots >= 0
         self.last_dropped_fraction = float(1.0 - kept.float().mean()) if not x.requires_grad else None
         exchange = getattr(self.ep, "exchange", None) if self.ep is not None else None
         if exchange is not None and on_gpu:
-            return self._forward_fused(flat, gates, experts, slots, kept, capacity, stride, exchange).reshape(shape)
+            return self._forward_fused(flat, gates, slots, kept_counts, stride, exchange).reshape(shape)
         capacity = stride          # buffer rows per expert from here on
 
         # dispatch: row s of the buffer holds the token assigned to slot s (zeros where unused)

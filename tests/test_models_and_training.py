@@ -137,7 +137,7 @@ def test_moe_routing_capacity_and_aux_terms():
     torch.manual_seed(0)
     logits = torch.randn(64, 8)
     cap = capacity_for(64, 2, 8, 1.0)
-    gates, experts, slots, (fraction, mean_prob) = route_tokens(logits, 2, cap)
+    gates, experts, slots, (fraction, mean_prob, kept_counts) = route_tokens(logits, 2, cap)
     assert torch.allclose(gates.sum(-1), torch.ones(64))
     assert fraction.sum() == pytest.approx(1.0) and mean_prob.sum() == pytest.approx(1.0, rel=1e-5)
     kept = slots[slots >= 0]
