@@ -45,17 +45,19 @@ def _matmul(x: torch.Tensor, weight) -> torch.Tensor:
 
 
 class _DecodeGraph:
-    """Static buffers and the captured graph of one batch-size bucket."""
+    """Static buffers and the captured graph of one (batch-size bucket, new tokens per sequence) pair: one new token
+    for plain decoding, ``k + 1`` for the verification pass of speculative decoding."""
 
-    def __init__(self, bucket: int, max_blocks: int, device: torch.device) -> None:
-        self.bucket = bucket
-        self.ids = torch.zeros(bucket, dtype=torch.long, device=device)
-        self.pos = torch.zeros(bucket, dtype=torch.long, device=device)
-        self.pos32 = torch.zeros(bucket, dtype=torch.int32, device=device)
-        self.slots = torch.zeros(bucket, dtype=torch.long, device=device)
+    def __init__(self, bucket: int, q_len: int, max_blocks: int, device: torch.device) -> None:
+        self.bucket, self.q_len = bucket, q_len
+        rows = bucket * q_len
+        self.ids = torch.zeros(rows, dtype=torch.long, device=device)
+        self.pos = torch.zeros(rows, dtype=torch.long, device=device)
+        self.pos32 = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.slots = torch.zeros(rows, dtype=torch.long, device=device)
         self.tables = torch.zeros(bucket, max_blocks, dtype=torch.int32, device=device)
-        self.ctx = torch.ones(bucket, dtype=torch.int32, device=device)
-        self.starts = torch.arange(bucket, dtype=torch.int32, device=device)
+        self.ctx = torch.full((bucket,), q_len, dtype=torch.int32, device=device)
+        self.starts = torch.arange(bucket, dtype=torch.int32, device=device) * q_len
         self.logits: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
 
@@ -97,7 +99,7 @@ class ModelRunner:
             self.weights.append(entry)
         # decoding graphs: dense feed-forward blocks (expert routing has data-dependent shapes); with several ranks only
         # when every row-parallel projection runs as the fused kernel (bf16 weights)
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self._scratch_block: int | None = None
         single = self.tp is None or self.tp.size == 1
         fused_everywhere = (not single and getattr(self.tp, "fused", None) is not None
@@ -109,13 +111,13 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ graph-replayed decoding
     def _decode_static(self, g: _DecodeGraph) -> torch.Tensor:
-        """One decoding step over the static buffers of ``g`` (every row: one new token, everything else cached)."""
+        """One decoding step over the static buffers of ``g`` (every sequence: ``q_len`` new tokens, the rest cached)."""
         from ajllm_b200.ops import serving
         model, cache = self.model, self.cache
-        n = g.bucket
+        n = g.bucket * g.q_len
         plan = object.__new__(serving.PagedPlan)
         plan.total_rows = n
-        plan.launches = [(1, n, g.tables, g.starts, g.ctx)]
+        plan.launches = [(g.q_len, g.bucket, g.tables, g.starts, g.ctx)]
         stream = model.token_embeddings(g.ids)
         if model.position_embeddings is not None:
             stream = stream + model.position_embeddings(g.pos)
@@ -140,17 +142,19 @@ class ModelRunner:
         hidden = model.final_norm.add_and_norm(stream, pending)[1]
         return ops.linear(hidden, model.head_weight).float()
 
-    def _graph_for(self, bucket: int) -> _DecodeGraph:
-        g = self._graphs.get(bucket)
+    def _graph_for(self, bucket: int, q_len: int) -> _DecodeGraph:
+        g = self._graphs.get((bucket, q_len))
         if g is not None:
             return g
         cache = self.cache
         if self._scratch_block is None:
             self._scratch_block = cache.allocator.allocate()       # padding rows read and write this block only
         max_blocks = (self.model.context_length + cache.block_size - 1) // cache.block_size
-        g = _DecodeGraph(bucket, max_blocks, self.device)
+        g = _DecodeGraph(bucket, q_len, max_blocks, self.device)
         g.tables.fill_(self._scratch_block)
-        g.slots.fill_(self._scratch_block * cache.block_size)
+        g.slots.copy_(self._scratch_block * cache.block_size + (torch.arange(bucket * q_len, device=self.device) % q_len))
+        g.pos.copy_(torch.arange(bucket * q_len, device=self.device) % q_len)
+        g.pos32.copy_(g.pos)
         # one eager run on a side stream first (lazy kernel attributes, allocator warm-up), then the capture
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -159,47 +163,58 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
         g.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g.graph):
+        # thread-local error mode: with a process group alive, its watchdog thread polls CUDA events while this thread
+        # captures, which the default (global) mode treats as a capture violation
+        with torch.cuda.graph(g.graph, capture_error_mode="thread_local"):
             g.logits = self._decode_static(g)
-        self._graphs[bucket] = g
+        self._graphs[(bucket, q_len)] = g
         return g
 
     def _forward_decode_graph(self, items: list[RunItem]) -> torch.Tensor | None:
-        """Replay path for a pure decoding step; ``None`` when the step does not qualify."""
+        """Replay path for a step in which every sequence feeds the same number of new tokens on top of a non-empty
+        cache and wants logits for all of them (plain decoding: one; speculative verification: ``k + 1``); ``None``
+        when the step does not qualify."""
         n = len(items)
         if n == 0 or n > self.GRAPH_BUCKETS[-1]:
             return None
         cache, model = self.cache, self.model
+        q_len = len(items[0].token_ids)
+        attn0 = model.layers[0].attention
+        # a sequence's rows share one attention CTA (64 rows at most) and padding rows live in one scratch block
+        if q_len < 1 or q_len > cache.block_size or (attn0.num_heads // attn0.num_kv_heads) * q_len > 64:
+            return None
         for item in items:
-            if len(item.token_ids) != 1 or item.num_logits != 1 or cache.length(item.seq_id) == 0:
+            if len(item.token_ids) != q_len or item.num_logits != q_len or cache.length(item.seq_id) == 0:
                 return None
-            if cache.length(item.seq_id) + 1 > model.context_length:
+            if cache.length(item.seq_id) + q_len > model.context_length:
                 raise ValueError(f"sequence {item.seq_id} would exceed the context length {model.context_length}")
         bucket = next(b for b in self.GRAPH_BUCKETS if b >= n)
-        g = self._graph_for(bucket)
+        g = self._graph_for(bucket, q_len)
         tokens, positions, slots, ctx = [], [], [], []
         for item in items:
             start = cache.length(item.seq_id)
-            slots.extend(cache.append_slots(item.seq_id, 1))
-            tokens.append(item.token_ids[0])
-            positions.append(start)
-            ctx.append(start + 1)
+            slots.extend(cache.append_slots(item.seq_id, q_len))
+            tokens.extend(item.token_ids)
+            positions.extend(range(start, start + q_len))
+            ctx.append(start + q_len)
         pad = bucket - n
         scratch_slot = self._scratch_block * cache.block_size
-        host = torch.tensor([tokens + [0] * pad, positions + [0] * pad, slots + [scratch_slot] * pad, ctx + [1] * pad],
+        pad_rows = list(range(q_len)) * pad
+        rows = torch.tensor([tokens + [0] * (pad * q_len), positions + pad_rows, slots + [scratch_slot + r for r in pad_rows]],
                             dtype=torch.long).pin_memory()
-        staged = host.to(self.device, non_blocking=True)
+        per_seq = torch.tensor(ctx + [q_len] * pad, dtype=torch.int32).pin_memory()
+        staged = rows.to(self.device, non_blocking=True)
         g.ids.copy_(staged[0])
         g.pos.copy_(staged[1])
         g.pos32.copy_(staged[1])
         g.slots.copy_(staged[2])
-        g.ctx.copy_(staged[3])
+        g.ctx.copy_(per_seq.to(self.device, non_blocking=True))
         tables = cache.block_table_tensor([item.seq_id for item in items], self.device)
         g.tables[:n, :tables.shape[1]].copy_(tables)
         if pad:
             g.tables[n:, 0].fill_(self._scratch_block)
         g.graph.replay()
-        return g.logits[:n]
+        return g.logits[:n * q_len]
 
     def _padded_heads(self, qkv: torch.Tensor, attn) -> torch.Tensor:
         if self.kernel_head_dim == self.head_dim:

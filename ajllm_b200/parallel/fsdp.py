@@ -603,6 +603,9 @@ class ShardedDataParallel(nn.Module):
             m.token_embeddings.weight.main_grad.add_(tied_grad)
         self._reduce_unit_grads(0)
         self._release(0)
+        # work queued on the current stream after this call sees complete gradient shards: the reductions that ran
+        # beside the backward pass are joined here (a stream dependency, no host wait)
+        self.join_reductions()
         # a leaf that accepts .backward(): the gradients above are already in place
         return loss_value.detach().clone().requires_grad_(True)
 

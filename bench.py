@@ -145,7 +145,7 @@ def run_ours(args) -> dict | None:
     model = model.to(device=device, dtype=torch.bfloat16)
     # sequences per micro-batch: as many as fit; with two micro-batches in flight (model.interleave) the batch of 32
     # is cut into at least two
-    micro = args.micro_batch or {1: 8, 2: 8, 4: 16, 8: 32 if model.interleave == 1 else 16}.get(world, 8)
+    micro = args.micro_batch or {1: 8, 2: 16, 4: 16, 8: 32 if model.interleave == 1 else 16}.get(world, 8)
     micro = min(micro, args.global_batch)
     accumulation = args.global_batch // micro
     optimizer = FlatAdamW(model, learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1, classes=classes)
@@ -552,7 +552,8 @@ def _child(script: str, extra: list[str], port_offset: int, limit_s: float) -> d
                 return json.loads(line)
             except ValueError:
                 continue
-    return {"error": f"no result (exit {code}): " + text[-400:].replace("\n", " | ")}
+    first = next((line.strip() for line in text.splitlines() if "Error" in line or "error:" in line), "")
+    return {"error": f"no result (exit {code}): {first[:300]} ... " + text[-300:].replace("\n", " | ")}
 
 
 SECONDARY_BUDGET_S = 480.0       # no further secondary workload starts once this much time has gone into them
