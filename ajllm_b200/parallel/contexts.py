@@ -28,15 +28,16 @@ def _wants_fused(fused: bool | None, device: torch.device, size: int, switch: st
 
 
 def interleaved_microbatches(tp_size: int, device: torch.device) -> int:
-    """How many micro-batches a tensor-parallel training step keeps in flight on streams of their own. From four
-    ranks on, most fused projections wait on NVLink longer than they compute (the bytes per rank stay the same while
-    the products shrink with 1 / tp), so a second micro-batch fills the idle SMs; ``AJB_TP_INTERLEAVE`` overrides."""
+    """How many micro-batches a tensor-parallel training step keeps in flight on streams of their own
+    (``AJB_TP_INTERLEAVE=2`` switches it on). Off by default: measured on two and four GPUs the two streams run in
+    step with each other (both in a link-bound projection, then both in attention), so the step time did not change
+    (within 1 %), and an unchanged time does not pay for the second set of symmetric buffers."""
     if device.type != "cuda":
         return 1
     forced = os.environ.get("AJB_TP_INTERLEAVE")
     if forced is not None:
         return max(1, int(forced))
-    return 2 if tp_size >= 4 else 1
+    return 1
 
 
 def make_tensor_parallel(axis: AxisGroup, device: torch.device, fused: bool | None = None,

@@ -55,7 +55,10 @@ class FusedTensorParallel:
         self.rank = dist.get_rank(group)
         if not 2 <= self.size <= _MAX_RANKS:
             raise ValueError("fused tensor parallelism supports 2..8 ranks")
-        self.copy_ctas = int(copy_ctas or os.environ.get("AJB_COPY_CTAS", "20"))
+        # CTAs that pull the peers' shards before they join the products. Two ranks hide their one transfer behind the
+        # products with 20; from four ranks on the transfer is the longer part and more pulling SMs shorten it
+        # (measured on four GPUs: 588 / 485 / 472 / 444 us for the QKV gather with 20 / 32 / 48 / 64)
+        self.copy_ctas = int(copy_ctas or os.environ.get("AJB_COPY_CTAS", "20" if self.size <= 2 else "48"))
         # Buffers that peers read (staging) or write (receive) exist twice and alternate with the call number, so a
         # call never waits for its peers to finish the same call (csrc/comm_gemm.cu explains the protocol). Gathering
         # calls are counted here; reducing calls are counted on the device so that CUDA graphs can replay them.

@@ -143,9 +143,10 @@ def run_ours(args) -> dict | None:
     with torch.device(device):
         model = build_model(config, VOCAB, tp=tp)
     model = model.to(device=device, dtype=torch.bfloat16)
-    # sequences per micro-batch: as many as fit; with two micro-batches in flight (model.interleave) the batch of 32
-    # is cut into at least two
-    micro = args.micro_batch or {1: 8, 2: 16, 4: 16, 8: 32 if model.interleave == 1 else 16}.get(world, 8)
+    # sequences per micro-batch: activations per GPU stay about what 8 sequences cost on one GPU; with two
+    # micro-batches in flight (model.interleave, opt-in) the batch of 32 is cut into at least two
+    micro = args.micro_batch or {1: 8, 2: 16, 4: 32 if model.interleave == 1 else 16,
+                                 8: 32 if model.interleave == 1 else 16}.get(world, 8)
     micro = min(micro, args.global_batch)
     accumulation = args.global_batch // micro
     optimizer = FlatAdamW(model, learning_rate=3e-4, betas=(0.9, 0.95), epsilon=1e-8, weight_decay=0.1, classes=classes)
