@@ -2,11 +2,14 @@
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ajllm_b200.ops import native
 
 BLOCK = 128
+_K_PARTS = os.environ.get("AJB_FP8_K_PARTS", "1") != "0"      # 0: every tile walks the whole K on its own
 
 
 def quantize_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -26,7 +29,7 @@ def fp8_block_gemm(x: torch.Tensor, weight) -> torch.Tensor:
     n = weight.out_features
     out = torch.empty(rows, n, dtype=torch.bfloat16, device=x.device)
     # few rows = few tiles: the K blocks of a tile are then divided over several CTAs whose fp32 parts a second kernel sums
-    splits = int(native.lib().ajb_fp8_block_gemm_splits(rows, n, k))
+    splits = int(native.lib().ajb_fp8_block_gemm_splits(rows, n, k)) if _K_PARTS else 1
     workspace = torch.empty(splits, rows, n, dtype=torch.float32, device=x.device) if splits > 1 else None
     native.call("ajb_fp8_block_gemm", xq.data_ptr(), weight.q.data_ptr(), sx.data_ptr(), weight.scale.data_ptr(),
                 out.data_ptr(), rows, n, k, xq.stride(0), weight.q.stride(0), out.stride(0), splits,

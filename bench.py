@@ -145,7 +145,7 @@ def run_ours(args) -> dict | None:
     model = model.to(device=device, dtype=torch.bfloat16)
     # sequences per micro-batch: activations per GPU stay about what 8 sequences cost on one GPU; with two
     # micro-batches in flight (model.interleave, opt-in) the batch of 32 is cut into at least two
-    micro = args.micro_batch or {1: 8, 2: 16, 4: 32 if model.interleave == 1 else 16,
+    micro = args.micro_batch or {1: 8, 2: 16, 4: 16,
                                  8: 32 if model.interleave == 1 else 16}.get(world, 8)
     micro = min(micro, args.global_batch)
     accumulation = args.global_batch // micro
