@@ -84,6 +84,7 @@ constexpr int kGroupM = 16;
 constexpr int kCopyPiece = 32768;                       // bytes per bulk copy
 constexpr int kCopyBufs = 6;                            // pieces in flight per copy CTA (ring = pipeline + epilogue space)
 static_assert((Cfg<false>::kRingBytes + kEpiBytes) / kCopyPiece >= kCopyBufs, "copy ring does not fit");
+static_assert(kSwigluWarpBytes <= 32 * kEpiRowPitch, "the SwiGLU row buffers of a warp must fit its part of the staging tile");
 static_assert((Cfg<true>::kRingBytes + kEpiBytes) / kCopyPiece >= kCopyBufs, "copy ring does not fit");
 constexpr int kQueue = 4;                               // depth of the per-CTA tile queue
 constexpr int kMaxGroups = 32;                          // arrival groups per shard (all-gather)
@@ -123,6 +124,12 @@ struct Params {
   unsigned int epoch;                    // gathering modes: number of this call (host-counted)
   unsigned int* local_cta_counter;       // local, zeroed by the host before launch
   unsigned int* tile_counter;            // local, zeroed by the host before launch
+  // all-gather mode only. 1: the output holds (gate, up) pairs in neighbouring columns and the epilogue also writes
+  // aux[m, n / 2] = silu(gate) * up. 2: the accumulators are d_act[m, n], aux is the saved gate_up[m, 2 n] and the
+  // epilogue writes d_gate_up[m, 2 n] to the output instead of the accumulators.
+  int swiglu;
+  void* aux;
+  long long ld_aux;
   DeviceStatus* status;
 };
 
@@ -188,22 +195,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m_local, int til
   tn = within / rows;
 }
 
-// ---- bulk copies (async proxy, no multicast)
-__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all_but_two() { asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); }
 
 // One copy CTA's share of the all-gather: thread 0 streams 32 KB pieces through a shared-memory ring.
 __device__ void copy_cta_all_gather(const Params& p, uint8_t* ring, uint64_t* bars, volatile uint32_t* abort_flag) {
@@ -659,20 +650,39 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
       tc_fence_after_sync();
       bulk_wait_read_all();          // the previous tile's store has read this lane's staging row
       const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
+      const int row = tm * C::kTileRows + (int)pair_rank * BM + quarter * 32 + lane;
+      const int col0 = tn * BN;
+      if (p.swiglu == 2) {
+        // SwiGLU backward: the accumulators are d_act; they meet the saved (gate, up) words of the same positions
+        // and leave as the gradient of the pairs (n is a multiple of 32: a chunk is whole or absent). The warp's
+        // part of the staging tile is its row block.
+        const int row0 = row - lane;
+        const long long at = 2 * col0;
+        swiglu_backward_rows(taddr, reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row0 * p.ld_aux + at, p.ld_aux,
+                             reinterpret_cast<__nv_bfloat16*>(p.out_local) + (long long)row0 * p.ldc + at, p.ldc, 32,
+                             min(BN, p.n - col0), epi_base + quarter * 32 * kEpiRowPitch, lane);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(acc_empty_leader + (uint32_t)buf * 8u);
+          else mbar_arrive(&acc_empty[buf]);
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + (uint32_t)c, v);
         tc_wait_ld();
+        uint32_t w[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 q;
-          q.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-          q.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-          q.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-          q.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-          *reinterpret_cast<uint4*>(my_row + c * 2 + j * 16) = q;
-        }
+        for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(my_row + c * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        if (p.swiglu == 1 && col0 + c < p.n)
+          swiglu_store_activation(w, reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.aux) +
+                                                             (long long)row * p.ld_aux + ((col0 + c) >> 1)));
       }
       // the accumulator is in shared memory now: hand the TMEM buffer back before the stores
       tc_fence_before_sync();
@@ -683,8 +693,6 @@ __device__ __forceinline__ void comm_gemm_body(const CUtensorMap& map_a, const C
         else mbar_arrive(&acc_empty[buf]);
       }
       // one bulk store per row: up to 512 contiguous bytes leave the SM without passing through registers
-      const int row = tm * C::kTileRows + (int)pair_rank * BM + quarter * 32 + lane;
-      const int col0 = tn * BN;
       const int bytes = min(BN, p.n - col0) * 2;
       if (p.mode == kAllReduce) {
         // the partial tile goes to every rank's receive buffer (own included), slot = this rank
@@ -794,6 +802,9 @@ struct AjbCommArgs {
   int a_rows;                    // all-reduce: rows of `a` that exist (<= m; the tiles above them read zeros); 0 means m
   long long shard_elems;         // gather-weight: bf16 elements per rank slice of the flat buffer (multiple of 8)
   long long b_offset_elems;      // gather-weight: first element of W inside the gathered buffer (multiple of 8)
+  int swiglu;                    // all-gather: 0 plain, 1 also write aux = silu(gate) * up, 2 out = SwiGLU gradient of aux
+  void* aux;                     // swiglu 1: act [m, n / 2] (written); swiglu 2: saved gate_up [m, 2 n] (read)
+  long long ld_aux;              // row stride of aux in elements (multiple of 8)
 };
 
 extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
@@ -859,6 +870,15 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   AJB_REQUIRE(gathers || a.reduce_state != nullptr, "comm_gemm: reducing modes need the two state words");
   p.out_local = a.out;
   p.ldc = a.ldc;
+  p.swiglu = a.swiglu;
+  p.aux = a.aux;
+  p.ld_aux = a.ld_aux;
+  if (a.swiglu != 0) {
+    AJB_REQUIRE(a.mode == kAllGather && (a.swiglu == 1 || a.swiglu == 2), "comm_gemm: SwiGLU epilogues belong to the all-gather mode");
+    AJB_REQUIRE(a.n % 32 == 0 && a.aux != nullptr && a.ld_aux % 8 == 0 && a.ldc % 8 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(a.aux) | reinterpret_cast<uintptr_t>(a.out)) & 15) == 0,
+                "comm_gemm: SwiGLU epilogues need n %% 32 == 0, 16-byte aligned buffers and row strides that are multiples of 8");
+  }
   p.epoch = a.epoch;
   p.status = device_status_buffer();
   AJB_CUDA_OK(cudaMemsetAsync(a.shard_flags, 0, kScratchWords * sizeof(unsigned int), s));

@@ -461,6 +461,109 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+
+// 16 bytes of read-only global memory (written by an earlier launch) through the non-coherent path.
+__device__ __forceinline__ uint4 ld_nc_v4(const uint4* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
+
+// ---- bulk copies (async proxy, no multicast)
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all_but_two() { asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+
+// SwiGLU in a GEMM epilogue. A thread holds 32 consecutive accumulator columns of one row.
+// Forward: the columns are 16 (gate, up) pairs, already packed to bf16 in w[16]; 16 activations silu(gate) * up leave
+// as two 16-byte stores to act (32-byte aligned row position).
+__device__ __forceinline__ void swiglu_store_activation(const uint32_t (&w)[16], uint4* act) {
+  float a[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float2 pair = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+    a[j] = pair.x / (1.0f + __expf(-pair.x)) * pair.y;
+  }
+  act[0] = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+  act[1] = make_uint4(pack_bf16x2(a[8], a[9]), pack_bf16x2(a[10], a[11]), pack_bf16x2(a[12], a[13]), pack_bf16x2(a[14], a[15]));
+}
+// Backward: the columns are 32 values of d_act (fp32 bits in v); g holds the 32 saved (gate, up) words of the same
+// positions; 32 (d_gate, d_up) words leave as eight 16-byte stores.
+__device__ __forceinline__ void swiglu_store_gradient(const uint32_t (&v)[32], const uint4 (&g)[8], uint4* out) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t w[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 pair = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      const float d = __uint_as_float(v[4 * j + i]);
+      const float sig = 1.0f / (1.0f + __expf(-pair.x));
+      o[i] = pack_bf16x2(d * pair.y * sig * (1.0f + pair.x * (1.0f - sig)), d * pair.x * sig);
+    }
+    out[j] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// SwiGLU backward for one warp of an epilogue: 32 rows x `cols` columns of d_act in tensor memory (lane l owns row l)
+// meet the saved (gate, up) words of the same positions, 32 columns = 128 bytes per row at a time. Global memory is
+// read and written with whole 128-byte row segments (8 lanes per row, 4 rows per instruction); a padded block of
+// shared memory turns them into the row-per-lane layout of the accumulators and back. `in` / `out` point at the
+// first of the warp's rows, at the tile's first pair; rows at or past `rows_valid` are neither read nor written.
+constexpr int kSwigluRowPitch = 144;                         // 128 bytes + 16: 16-byte accesses of 8 lanes cover all banks
+constexpr int kSwigluWarpBytes = 32 * kSwigluRowPitch;
+__device__ __forceinline__ void swiglu_backward_rows(uint32_t taddr, const __nv_bfloat16* in, long long ld_in,
+                                                     __nv_bfloat16* out, long long ld_out, int rows_valid, int cols,
+                                                     uint8_t* stage, int lane) {
+  const int chunks = cols >> 5;
+  const int sub = lane >> 3, piece = lane & 7;
+  uint4 g[8];
+  auto fetch = [&](int c) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = 4 * i + sub;
+      if (r < rows_valid) g[i] = ld_nc_v4(reinterpret_cast<const uint4*>(in + (long long)r * ld_in + c * 64) + piece);
+    }
+  };
+  if (chunks > 0) fetch(0);
+  uint4* mine = reinterpret_cast<uint4*>(stage + lane * kSwigluRowPitch);
+#pragma unroll 1
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(stage + (4 * i + sub) * kSwigluRowPitch + piece * 16) = g[i];
+    __syncwarp();
+    if (c + 1 < chunks) fetch(c + 1);
+    uint4 row[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) row[j] = mine[j];
+    tc_wait_ld();
+    swiglu_store_gradient(v, row, mine);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = 4 * i + sub;
+      const uint4 q = *reinterpret_cast<const uint4*>(stage + r * kSwigluRowPitch + piece * 16);
+      if (r < rows_valid) reinterpret_cast<uint4*>(out + (long long)r * ld_out + c * 64)[piece] = q;
+    }
+    __syncwarp();
+  }
+}
 #endif  // __CUDACC__
 
 }  // namespace ajb

@@ -37,12 +37,20 @@ constexpr int kBBytes = BNH * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * BN;
 constexpr int kSmemBytes = kStages * kStageBytes + 256;
+constexpr int kSmemBytesSwigluBackward = kSmemBytes + 4 * kSwigluWarpBytes;   // plus the epilogue warps' row blocks
 constexpr int kKernelId = 10;
 
-enum Epilogue : int { kStoreBf16 = 0, kAccumF32 = 1, kStoreF32 = 2, kAtomicAddF32 = 3 };
+// kStoreBf16Swiglu: C holds (gate, up) pairs in neighbouring columns; besides C (skipped when c is null) the epilogue
+//   writes act[m, n / 2] = silu(gate) * up to c2, computed from the bf16-rounded pair.
+// kSwigluBackward: the accumulators are d_act[m, n]; c2 is the saved gate_up[m, 2 n] and the epilogue writes
+//   d_gate_up[m, 2 n] to c. d_act itself never reaches memory.
+enum Epilogue : int { kStoreBf16 = 0, kAccumF32 = 1, kStoreF32 = 2, kAtomicAddF32 = 3, kStoreBf16Swiglu = 4,
+                      kSwigluBackward = 5 };
 
 struct Params {
   void* c;
+  void* c2;
+  long long ldc2;
   int m, n, k;
   long long ldc;
   int epilogue;
@@ -61,7 +69,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = within / rows;
 }
 
-template <bool A_MN, bool B_MN>
+// SWIGLU_BWD: the kernel of the kSwigluBackward epilogue (a row block per epilogue warp behind the barriers).
+template <bool A_MN, bool B_MN, bool SWIGLU_BWD = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -73,6 +82,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint8_t* row_stage = smem_raw + kStages * kStageBytes + 256;          // SWIGLU_BWD: 4 warps x kSwigluWarpBytes
   // both CTAs of a pair take the same branch here (same dynamic shared memory offset in both)
   const bool misaligned = smem_misaligned(smem_raw, p.status, kKernelId, reinterpret_cast<uint32_t*>(bars) + 60);
 
@@ -216,6 +226,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int col0 = tn * BN;
       const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.m;
+      if (SWIGLU_BWD) {
+        // the accumulators are d_act: turned into the gradient of the saved (gate, up) pairs, 32 columns at a time
+        // (n is a multiple of 32: a chunk is whole or absent)
+        const int row0 = row - lane;
+        const long long at = 2 * col0;
+        swiglu_backward_rows(taddr, reinterpret_cast<const __nv_bfloat16*>(p.c2) + (long long)row0 * p.ldc2 + at, p.ldc2,
+                             reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row0 * p.ldc + at, p.ldc,
+                             min(32, p.m - row0), min(BN, p.n - col0), row_stage + quarter * kSwigluWarpBytes, lane);
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
@@ -224,7 +243,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int col = col0 + c;
         if (!row_ok || col >= p.n) continue;
         const int valid = min(32, p.n - col);
-        if (p.epilogue == kStoreBf16) {
+        if (p.epilogue == kStoreBf16Swiglu) {
+          // n is a multiple of 32 here
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+          if (p.c != nullptr) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row * p.ldc + col);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          }
+          swiglu_store_activation(w, reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.c2) +
+                                                             (long long)row * p.ldc2 + (col >> 1)));
+        } else if (p.epilogue == kStoreBf16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row * p.ldc + col;
           if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -313,9 +344,10 @@ static int resident_pairs(Kernel kernel) {
   return clusters < sm_count_physical() / 2 ? clusters : sm_count_physical() / 2;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool SWIGLU_BWD = false>
 static int launch(const void* a, const void* b, void* c, int m, int n, int k, long long lda, long long ldb, long long ldc,
-                  int epilogue, int split_k, cudaStream_t stream) {
+                  int epilogue, int split_k, cudaStream_t stream, void* c2 = nullptr, long long ldc2 = 0) {
+  constexpr int kSmemBytes = SWIGLU_BWD ? kSmemBytesSwigluBackward : gemm_pair::kSmemBytes;
   CUtensorMap map_a, map_b;
   int rc;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -327,14 +359,14 @@ static int launch(const void* a, const void* b, void* c, int m, int n, int k, lo
   if (rc) return rc;
 
   static bool configured = false;
-  auto kernel = gemm_pair_kernel<A_MN, B_MN>;
+  auto kernel = gemm_pair_kernel<A_MN, B_MN, SWIGLU_BWD>;
   if (!configured) {
     AJB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     configured = true;
   }
   const int pairs = capacity();
   Params p;
-  p.c = c; p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.epilogue = epilogue;
+  p.c = c; p.c2 = c2; p.ldc2 = ldc2; p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.epilogue = epilogue;
   p.tiles_m = (m + 2 * BM - 1) / (2 * BM);
   p.tiles_n = (n + BN - 1) / BN;
   p.split_k = split_k;
@@ -371,8 +403,38 @@ int run(const void* a, const void* b, void* c, int m, int n, int k, long long ld
   }
 }
 
+int run_swiglu(const void* a, const void* b, void* c, void* c2, int m, int n, int k, long long lda, long long ldb,
+               long long ldc, long long ldc2, int backward, cudaStream_t s) {
+  if (backward) return launch<false, true, true>(a, b, c, m, n, k, lda, ldb, ldc, kSwigluBackward, 1, s, c2, ldc2);
+  return launch<false, false>(a, b, c, m, n, k, lda, ldb, ldc, kStoreBf16Swiglu, 1, s, c2, ldc2);
+}
+
 }  // namespace gemm_pair
 }  // namespace ajb
+
+// SwiGLU inside the projections around it, on CTA pairs (the reference applies it as three eager ops between the
+// matmuls, ajllm/modeling/activations.py:25).
+//   forward  (backward = 0): gate_up[m, n] = x[m, k] w13[n, k]^T with (gate, up) pairs in neighbouring columns, and
+//            act[m, n / 2] = silu(gate) * up from the same accumulators. gate_up may be null (inference): only act is
+//            written.
+//   backward (backward = 1): d_act[m, n] = d_out[m, k] w2[k, n] stays in tensor memory; the epilogue reads the saved
+//            gate_up[m, 2 n] and writes d_gate_up[m, 2 n].
+// n must be a multiple of 32, all row strides multiples of 8 elements, all bases 16-byte aligned.
+extern "C" int ajb_gemm_bf16_swiglu(const void* a, const void* b, void* gate_up, void* other, int m, int n, int k,
+                                    long long lda, long long ldb, long long ld_gate_up, long long ld_other, int backward,
+                                    void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm_swiglu: empty problem %dx%dx%d", m, n, k);
+  AJB_REQUIRE(n % 32 == 0, "gemm_swiglu: n = %d must be a multiple of 32", n);
+  AJB_REQUIRE(ld_gate_up % 8 == 0 && ld_other % 8 == 0, "gemm_swiglu: row strides must be multiples of 8 elements");
+  AJB_REQUIRE(other != nullptr && (backward == 0 || gate_up != nullptr), "gemm_swiglu: missing operand");
+  AJB_REQUIRE(((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(other)) & 15) == 0,
+              "gemm_swiglu: outputs must be 16-byte aligned");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // forward: C = gate_up, c2 = act; backward: C = d_gate_up (`other`), c2 = the saved gate_up
+  if (backward) return gemm_pair::run_swiglu(a, b, other, gate_up, m, n, k, lda, ldb, ld_other, ld_gate_up, 1, s);
+  return gemm_pair::run_swiglu(a, b, gate_up, other, m, n, k, lda, ldb, ld_gate_up, ld_other, 0, s);
+}
 
 // The pair kernel on its own (tests and benchmarks; ajb_gemm_bf16 chooses between the two kernels itself).
 // Epilogues 0 (bf16 store), 1 (fp32 accumulate), 2 (fp32 store); 3 (fp32 add with reductions) takes `split_k` K slices.

@@ -341,7 +341,9 @@ class ModelRunner:
             if "moe" in w:
                 pending = w["moe"](normed)
             elif "w13" in w:
-                pending = self._row_parallel(ops.swiglu_interleaved(_matmul(normed, w["w13"])), w["w2"])
+                hidden_ff = (ops.swiglu_interleaved(_matmul(normed, w["w13"])) if isinstance(w["w13"], Fp8Weight)
+                             else ops.linear_swiglu(normed, w["w13"]))
+                pending = self._row_parallel(hidden_ff, w["w2"])
             else:
                 pending = self._row_parallel(ops.silu(_matmul(normed, w["w1"])), w["w2"])
         hidden = model.final_norm.add_and_norm(stream, pending)[1]

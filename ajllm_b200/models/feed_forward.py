@@ -68,9 +68,8 @@ class SwiGLU(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp is not None and self.tp.size > 1:
-            gate_up = self.tp.gather_linear(x, self.w13)
-            return self.tp.linear_scatter(ops.swiglu_interleaved(gate_up), self.w2)
-        return ops.linear(ops.swiglu_interleaved(ops.linear(x, self.w13)), self.w2)
+            return self.tp.swiglu_ffn(x, self.w13, self.w2)
+        return ops.swiglu_ffn(x, self.w13, self.w2)
 
 
 class SiLUFeedForward(nn.Module):

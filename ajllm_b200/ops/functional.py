@@ -516,6 +516,112 @@ def swiglu_interleaved(gate_up: torch.Tensor) -> torch.Tensor:
     return reference.swiglu_interleaved(gate_up)
 
 
+# SwiGLU computed by the epilogues of the projections around it (csrc/gemm_bf16_pair.cu); AJB_FUSED_SWIGLU=0 keeps the
+# three separate steps.
+FUSED_SWIGLU = os.environ.get("AJB_FUSED_SWIGLU", "1") != "0"
+
+
+def _gemm_swiglu(a, b, gate_up, other, m, n, k, backward: bool) -> None:
+    native.call("ajb_gemm_bf16_swiglu", a.data_ptr(), b.data_ptr(), native.ptr(gate_up), other.data_ptr(), m, n, k,
+                a.stride(0), b.stride(0), gate_up.stride(0) if gate_up is not None else 0, other.stride(0),
+                int(backward), native.stream_ptr())
+
+
+class _SwigluFfnFn(torch.autograd.Function):
+    """``(silu(x W1^T) * x W3^T) W2^T`` with W1 / W3 rows interleaved in ``w13``: the activation leaves the first
+    projection's epilogue, and in the backward pass the gradient of ``gate_up`` leaves the epilogue of
+    ``d_out @ W2`` without ``d_act`` ever being stored."""
+
+    @staticmethod
+    def run_forward(x, w13, w2, keep: bool):
+        """Returns ``(out, x2, gate_up, act)``; without ``keep`` the pre-activation is never written."""
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        m, k = x2.shape
+        f2 = w13.shape[0]
+        d_out = w2.shape[0]
+        gate_up = torch.empty(m, f2, dtype=torch.bfloat16, device=x.device) if keep else None
+        act = torch.empty(m, f2 // 2, dtype=torch.bfloat16, device=x.device)
+        _gemm_swiglu(x2, w13, gate_up, act, m, f2, k, backward=False)
+        out = torch.empty(m, d_out, dtype=torch.bfloat16, device=x.device)
+        gemm(act, w2, out, m, d_out, f2 // 2)
+        return out.view(*x.shape[:-1], d_out), x2, gate_up, act
+
+    @staticmethod
+    def forward(ctx, x, w13, w2):
+        out, x2, gate_up, act = _SwigluFfnFn.run_forward(x, w13, w2, keep=True)
+        ctx.save_for_backward(x2, w13, w2, gate_up, act)
+        ctx.lead = x.shape[:-1]
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x2, w13, w2, gate_up, act = ctx.saved_tensors
+        m, k = x2.shape
+        f2 = w13.shape[0]
+        f = f2 // 2
+        d_out = w2.shape[0]
+        g2 = grad_out.reshape(-1, d_out)
+        if g2.stride(-1) != 1 or g2.dtype != torch.bfloat16:
+            g2 = g2.to(torch.bfloat16).contiguous()
+        d_gate_up = torch.empty(m, f2, dtype=torch.bfloat16, device=g2.device)
+        _gemm_swiglu(g2, w2, gate_up, d_gate_up, m, f, d_out, backward=True)
+        grad_x = grad_w13 = grad_w2 = None
+        if ctx.needs_input_grad[2]:
+            main = getattr(w2, "main_grad", None)
+            if main is not None:
+                wgrad_accumulate(g2, act, main, d_out, f, m)
+                w2.main_grad_written = True
+            else:
+                grad_w2 = torch.empty(d_out, f, dtype=torch.bfloat16, device=g2.device)
+                gemm(g2, act, grad_w2, d_out, f, m, a_mn_major=True, b_mn_major=True)
+        if ctx.needs_input_grad[0]:
+            grad_x = torch.empty(m, k, dtype=torch.bfloat16, device=g2.device)
+            gemm(d_gate_up, w13, grad_x, m, k, f2, b_mn_major=True)
+            grad_x = grad_x.view(*ctx.lead, k)
+        if ctx.needs_input_grad[1]:
+            main = getattr(w13, "main_grad", None)
+            if main is not None:
+                wgrad_accumulate(d_gate_up, x2, main, f2, k, m)
+                w13.main_grad_written = True
+            else:
+                grad_w13 = torch.empty(f2, k, dtype=torch.bfloat16, device=g2.device)
+                gemm(d_gate_up, x2, grad_w13, f2, k, m, a_mn_major=True, b_mn_major=True)
+        return grad_x, grad_w13, grad_w2
+
+
+def swiglu_ffn(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """The SwiGLU feed-forward block ``W2(silu(W1 x) * W3 x)`` (``ajllm/modeling/activations.py:15-27``) for an
+    interleaved ``w13``. On the GPU the activation and its gradient are computed inside the GEMM epilogues when the
+    shapes allow (more than 128 rows, hidden width a multiple of 32); otherwise as three steps."""
+    if _native(x, "swiglu_ffn"):
+        rows = x.numel() // x.shape[-1]
+        f = w13.shape[0] // 2
+        fused = (FUSED_SWIGLU and rows > _SKINNY_ROWS and f % 32 == 0 and x.shape[-1] % 8 == 0 and w2.shape[0] % 8 == 0
+                 and w13.stride(-1) == 1 and w2.stride(-1) == 1 and w2.stride(0) % 8 == 0 and w13.stride(0) % 8 == 0)
+        if fused:
+            if torch.is_grad_enabled() and (x.requires_grad or w13.requires_grad or w2.requires_grad):
+                return _SwigluFfnFn.apply(x, w13, w2)
+            return _SwigluFfnFn.run_forward(x, w13, w2, keep=False)[0]
+    return linear(swiglu_interleaved(linear(x, w13)), w2)
+
+
+def linear_swiglu(x: torch.Tensor, w13: torch.Tensor) -> torch.Tensor:
+    """``silu(x W1^T) * x W3^T`` for an interleaved ``w13``. Without autograd, on more than a few hundred rows, the
+    activation leaves the projection's epilogue and the pre-activation is never written."""
+    if (_native(x, "linear_swiglu") and FUSED_SWIGLU and not (torch.is_grad_enabled() and (x.requires_grad or w13.requires_grad))
+            and x.numel() // x.shape[-1] > _SKINNY_ROWS and (w13.shape[0] // 2) % 32 == 0 and x.shape[-1] % 8 == 0
+            and w13.stride(-1) == 1 and w13.stride(0) % 8 == 0):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        act = torch.empty(x2.shape[0], w13.shape[0] // 2, dtype=torch.bfloat16, device=x.device)
+        _gemm_swiglu(x2, w13, None, act, x2.shape[0], w13.shape[0], x2.shape[1], backward=False)
+        return act.view(*x.shape[:-1], act.shape[-1])
+    return swiglu_interleaved(linear(x, w13))
+
+
 class _SiluFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):

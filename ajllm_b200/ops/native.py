@@ -31,6 +31,8 @@ _SIGNATURES: dict[str, list] = {
                       c_int, c_int, c_int, c_void],
     "ajb_gemm_bf16_pair": [c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long,
                            c_int, c_int, c_int, c_int, c_void],
+    "ajb_gemm_bf16_swiglu": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_long,
+                             c_int, c_void],
     "ajb_gemm_pair_capacity": [],
     "ajb_set_sm_budget": [c_int],
     "ajb_sm_count": [],

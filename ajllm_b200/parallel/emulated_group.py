@@ -43,7 +43,7 @@ class EmulatedGroup:
         return (self.reduce_calls + 1) & 1
 
     def launch(self, mode, m, n, k, out, b=None, b_mn=False, a=None, gathered=None, stage=None, recv=None,
-               recv_even=None, tiles_for_count=0, a_rows=0, shard_elems=0, b_offset=0, sm_budget=None):
+               recv_even=None, tiles_for_count=0, a_rows=0, shard_elems=0, b_offset=0, sm_budget=None, swiglu=0, aux=None):
         tp = self.tp
         gathers = mode in (MODE_ALL_GATHER, MODE_GATHER_WEIGHT)
         if gathers:
@@ -76,6 +76,9 @@ class EmulatedGroup:
         args.reduce_state = self.reduce_state.data_ptr()
         args.epoch = self.gather_calls & 0xFFFFFFFF
         args.a_rows, args.shard_elems, args.b_offset_elems = a_rows, shard_elems, b_offset
+        args.swiglu = swiglu
+        args.aux = aux.data_ptr() if aux is not None else None
+        args.ld_aux = aux.stride(0) if aux is not None else 0
         native.launch_count += 1
         with native.sm_budget(sm_budget):
             status = self.fn(ctypes.byref(args), native.stream_ptr())

@@ -38,6 +38,7 @@ class _CommArgs(ctypes.Structure):
         ("done_ptrs", ctypes.c_void_p * _MAX_RANKS),
         ("shard_flags", ctypes.c_void_p), ("reduce_state", ctypes.c_void_p), ("epoch", ctypes.c_uint),
         ("a_rows", ctypes.c_int), ("shard_elems", ctypes.c_longlong), ("b_offset_elems", ctypes.c_longlong),
+        ("swiglu", ctypes.c_int), ("aux", ctypes.c_void_p), ("ld_aux", ctypes.c_longlong),
     ]
 
 
@@ -121,7 +122,7 @@ class FusedTensorParallel:
 
     def _launch(self, mode: int, m: int, n: int, k: int, b: torch.Tensor, b_mn: bool, out: torch.Tensor,
                 a: torch.Tensor | None = None, gathered: torch.Tensor | None = None, a_rows: int = 0,
-                shard_elems: int = 0, b_offset_elems: int = 0) -> None:
+                shard_elems: int = 0, b_offset_elems: int = 0, swiglu: int = 0, aux: torch.Tensor | None = None) -> None:
         gathers = mode in (MODE_ALL_GATHER, MODE_GATHER_WEIGHT)
         parity = self.gather_calls & 1          # gathering: _next_stage() advanced the count and filled this parity
         args = _CommArgs()
@@ -133,6 +134,9 @@ class FusedTensorParallel:
         args.b, args.out = b.data_ptr(), out.data_ptr()
         args.gathered = gathered.data_ptr() if gathered is not None else None
         args.a_rows = a_rows
+        args.swiglu = swiglu
+        args.aux = aux.data_ptr() if aux is not None else None
+        args.ld_aux = aux.stride(0) if aux is not None else 0
         for r in range(self.size):
             args.stage_ptrs[r] = self._stage_ptrs[parity][r] if (gathers and self._stage_ptrs[parity]) else None
             args.recv_ptrs[r] = self._recv_ptrs[1][r] if self._recv_ptrs[1] else None
@@ -179,16 +183,21 @@ class FusedTensorParallel:
         return self._stage[self.gather_calls & 1][:nbytes]
 
     # ------------------------------------------------------------------ raw fused ops
-    def all_gather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, b_mn: bool, n: int, k: int):
-        """Returns ``(gathered [M, k], out [M, n])`` with ``out = gathered @ op(weight)``."""
+    def all_gather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, b_mn: bool, n: int, k: int,
+                        swiglu: int = 0, aux: torch.Tensor | None = None):
+        """Returns ``(gathered [M, k], out [M, n])`` with ``out = gathered @ op(weight)``.
+
+        ``swiglu = 1``: ``out`` holds (gate, up) pairs and the epilogue also writes ``aux [M, n / 2] = silu(gate) * up``.
+        ``swiglu = 2``: the product is ``d_act``, ``aux`` is the saved ``gate_up [M, 2 n]`` and ``out [M, 2 n]`` is the
+        gradient of the pairs; ``d_act`` is never stored."""
         m_local = x_local.shape[0]
         m = m_local * self.size
         stage = self._next_stage(m_local * k * 2).view(torch.bfloat16).view(m_local, k)
         stage.copy_(x_local)
         gathered = torch.empty(m, k, dtype=torch.bfloat16, device=self.device)
         gathered[self.rank * m_local:(self.rank + 1) * m_local].copy_(x_local)   # the kernel moves only remote shards
-        out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
-        self._launch(MODE_ALL_GATHER, m, n, k, weight, b_mn, out, gathered=gathered)
+        out = torch.empty(m, 2 * n if swiglu == 2 else n, dtype=torch.bfloat16, device=self.device)
+        self._launch(MODE_ALL_GATHER, m, n, k, weight, b_mn, out, gathered=gathered, swiglu=swiglu, aux=aux)
         return gathered, out
 
     def gemm_reduce_scatter(self, x: torch.Tensor, weight: torch.Tensor, b_mn: bool, n: int, k: int) -> torch.Tensor:
@@ -251,6 +260,20 @@ class FusedTensorParallel:
         return _LinearScatterFn.apply(x, weight, self)
 
 
+    def swiglu_ffn(self, x_local: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+        """Sequence-parallel SwiGLU block: all-gather -> W13 GEMM with the activation in its epilogue, then W2 GEMM ->
+        reduce-scatter; the backward pass computes the activation gradient in the epilogue of the gathered
+        ``d_out @ W2``. ``w13 [2 F_local, D]`` interleaved, ``w2 [D, F_local]``."""
+        from ajllm_b200.ops import functional
+
+        f = w13.shape[0] // 2
+        if (not functional.FUSED_SWIGLU or x_local.dtype != torch.bfloat16 or f % 32 != 0
+                or not self.supports(x_local.shape[0] * self.size)):
+            from ajllm_b200 import ops
+            return self.linear_scatter(ops.swiglu_interleaved(self.gather_linear(x_local, w13)), w2)
+        return _SwigluFfnFn.apply(x_local, w13, w2, self)
+
+
 def _wgrad(grad_out: torch.Tensor, activations: torch.Tensor, weight: torch.Tensor):
     """``dW[n, k] = grad_out[M, n]^T @ activations[M, k]`` into ``weight.main_grad`` or a new tensor."""
     n, k = weight.shape
@@ -282,6 +305,32 @@ class _GatherLinearFn(torch.autograd.Function):
         grad_x = ctx.fused.gemm_reduce_scatter(grad_out, weight, True, k, n)
         grad_w = _wgrad(grad_out, gathered, weight) if ctx.needs_input_grad[1] else None
         return grad_x, grad_w, None
+
+
+class _SwigluFfnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local, w13, w2, fused: FusedTensorParallel):
+        f2, k = w13.shape
+        d_out = w2.shape[0]
+        m = x_local.shape[0] * fused.size
+        act = torch.empty(m, f2 // 2, dtype=torch.bfloat16, device=x_local.device)
+        gathered, gate_up = fused.all_gather_gemm(x_local.contiguous(), w13, False, f2, k, swiglu=1, aux=act)
+        out = fused.gemm_reduce_scatter(act, w2, False, d_out, f2 // 2)
+        ctx.save_for_backward(gathered, w13, w2, gate_up, act)
+        ctx.fused = fused
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_local):
+        gathered, w13, w2, gate_up, act = ctx.saved_tensors
+        f2, k = w13.shape
+        d_out = w2.shape[0]
+        # d_out is gathered over ranks while d_act = d_out @ W2 runs; its epilogue turns d_act into d_gate_up
+        grad_full, d_gate_up = ctx.fused.all_gather_gemm(grad_local.contiguous(), w2, True, f2 // 2, d_out, swiglu=2, aux=gate_up)
+        grad_w2 = _wgrad(grad_full, act, w2) if ctx.needs_input_grad[2] else None
+        grad_x = ctx.fused.gemm_reduce_scatter(d_gate_up, w13, True, k, f2)
+        grad_w13 = _wgrad(d_gate_up, gathered, w13) if ctx.needs_input_grad[1] else None
+        return grad_x, grad_w13, grad_w2, None
 
 
 class _LinearScatterFn(torch.autograd.Function):

@@ -112,6 +112,13 @@ class TensorParallel:
             return self.fused.linear_scatter(x, weight)
         return _ScatterRows.apply(ops.linear(x, weight), self.group)
 
+    def swiglu_ffn(self, x_local: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+        """Sequence-parallel SwiGLU block ``reduce_scatter_rows((silu(g) * u) @ w2.T)`` with ``(g, u)`` the interleaved
+        columns of ``all_gather_rows(x_local) @ w13.T``."""
+        if self.fused is not None and x_local.is_cuda:
+            return self.fused.swiglu_ffn(x_local, w13, w2)
+        return _ScatterRows.apply(ops.swiglu_ffn(_GatherRows.apply(x_local, self.group), w13, w2), self.group)
+
     def all_reduce_sum_(self, tensor: torch.Tensor) -> torch.Tensor:
         if self.size > 1:
             dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)

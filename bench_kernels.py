@@ -300,10 +300,58 @@ def run_moe_exchange(dev, small: bool) -> None:
     print("kernel status", native.check_status(False))
 
 
+def run_swiglu(dev, small: bool) -> None:
+    """The SwiGLU block's first projection with the activation in its epilogue, and the gradient of the pairs from the
+    epilogue of d_out @ W2, each against the plain GEMM followed by the pointwise kernel."""
+    from ajllm_b200.ops import functional
+    rows, d_model, d_ff = (8192, 2048, 2816) if small else (32768, 2048, 5632)
+    bf = torch.bfloat16
+    x = torch.randn(rows, d_model, device=dev, dtype=bf)
+    w13 = (torch.randn(2 * d_ff, d_model, device=dev) * d_model ** -0.5).to(bf)
+    w2 = (torch.randn(d_model, d_ff, device=dev) * d_ff ** -0.5).to(bf)
+    d_out = torch.randn(rows, d_model, device=dev, dtype=bf)
+    gate_up = torch.empty(rows, 2 * d_ff, device=dev, dtype=bf)
+    act = torch.empty(rows, d_ff, device=dev, dtype=bf)
+    d_act = torch.empty(rows, d_ff, device=dev, dtype=bf)
+    d_gate_up = torch.empty(rows, 2 * d_ff, device=dev, dtype=bf)
+    stream = native.stream_ptr
+
+    def fwd_fused():
+        functional._gemm_swiglu(x, w13, gate_up, act, rows, 2 * d_ff, d_model, backward=False)
+
+    def fwd_fused_act_only():
+        functional._gemm_swiglu(x, w13, None, act, rows, 2 * d_ff, d_model, backward=False)
+
+    def fwd_gemm():
+        ops.gemm(x, w13, gate_up, rows, 2 * d_ff, d_model)
+
+    def fwd_pointwise():
+        native.call("ajb_swiglu_fwd", gate_up.data_ptr(), act.data_ptr(), rows, d_ff, stream())
+
+    def bwd_fused():
+        functional._gemm_swiglu(d_out, w2, gate_up, d_gate_up, rows, d_ff, d_model, backward=True)
+
+    def bwd_gemm():
+        ops.gemm(d_out, w2, d_act, rows, d_ff, d_model, b_mn_major=True)
+
+    def bwd_pointwise():
+        native.call("ajb_swiglu_bwd", gate_up.data_ptr(), d_act.data_ptr(), d_gate_up.data_ptr(), rows, d_ff, stream())
+
+    fwd_gemm()
+    t = {name: timeit(fn) * 1e3 for name, fn in [("fwd_fused", fwd_fused), ("fwd_act_only", fwd_fused_act_only),
+                                                 ("fwd_gemm", fwd_gemm), ("fwd_pointwise", fwd_pointwise),
+                                                 ("bwd_fused", bwd_fused), ("bwd_gemm", bwd_gemm), ("bwd_pointwise", bwd_pointwise)]}
+    print(f"SwiGLU block, {rows} rows, d_model {d_model}, d_ff {d_ff}:", flush=True)
+    print(f"  forward  x W13^T + activation: one kernel {t['fwd_fused']:7.1f} us (activation only, inference: {t['fwd_act_only']:7.1f} us) | "
+          f"GEMM {t['fwd_gemm']:7.1f} + pointwise {t['fwd_pointwise']:6.1f} = {t['fwd_gemm'] + t['fwd_pointwise']:7.1f} us", flush=True)
+    print(f"  backward d_out W2 -> d(gate, up): one kernel {t['bwd_fused']:7.1f} us | "
+          f"GEMM {t['bwd_gemm']:7.1f} + pointwise {t['bwd_pointwise']:6.1f} = {t['bwd_gemm'] + t['bwd_pointwise']:7.1f} us", flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--case", default="all", choices=["all", "gemm", "decode", "flash", "flash64", "norm", "paged", "sampler",
-                                                      "fp8", "grad_reduce", "moe_exchange"])
+                                                      "fp8", "grad_reduce", "moe_exchange", "swiglu"])
     ap.add_argument("--small", action="store_true", help="one small shape per case (a few hundred MB on the device)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -330,6 +378,8 @@ def main() -> None:
         run_grad_reduce(dev, args.small)
     if args.case in ("all", "moe_exchange"):
         run_moe_exchange(dev, args.small)
+    if args.case in ("all", "swiglu"):
+        run_swiglu(dev, args.small)
     print("kernel status", native.lib().ajb_check_status())
 
 

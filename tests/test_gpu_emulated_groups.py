@@ -51,6 +51,45 @@ def test_all_gather_gemm_as_rank_0(tp, m_local, n, k, b_mn):
     assert native.check_status() == 0
 
 
+@pytest.mark.parametrize("tp,m_local,d_model,d_ff", [(2, 512, 512, 704), (4, 256, 256, 352), (8, 128, 256, 1408), (2, 384, 384, 96)])
+def test_swiglu_epilogues_of_the_all_gather_gemm_as_rank_0(tp, m_local, d_model, d_ff):
+    """Forward: gathered x @ w13^T leaves (gate, up) pairs and the activation from one kernel. Backward: gathered
+    d_out @ w2 leaves the gradient of the pairs; d_act is never stored."""
+    from ajllm_b200.ops import reference
+    from ajllm_b200.parallel.emulated_group import MODE_ALL_GATHER
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(tp * 31 + d_ff)
+    group = _group(tp)
+    m = tp * m_local
+    x = (torch.randn(m, d_model, device=dev) * 0.5).to(BF)
+    w13 = (torch.randn(2 * d_ff, d_model, device=dev) * d_model ** -0.5).to(BF)
+    w2 = (torch.randn(d_model, d_ff, device=dev) * d_ff ** -0.5).to(BF)
+    # forward
+    stage = [x[r * m_local:(r + 1) * m_local].contiguous() for r in range(tp)]
+    gathered = torch.zeros(m, d_model, device=dev, dtype=BF)
+    gathered[:m_local].copy_(stage[0])
+    gate_up = torch.zeros(m, 2 * d_ff, device=dev, dtype=BF)
+    act = torch.zeros(m, d_ff, device=dev, dtype=BF)
+    group.launch(MODE_ALL_GATHER, m, 2 * d_ff, d_model, gate_up, b=w13, gathered=gathered, stage=stage, swiglu=1, aux=act)
+    torch.cuda.synchronize()
+    assert _rel(gate_up, x.float() @ w13.float().t()) < 5e-3
+    assert _rel(act, reference.swiglu_interleaved(gate_up.float())) < 4e-3        # from the bf16-rounded pairs
+    # backward
+    d_out = (torch.randn(m, d_model, device=dev)).to(BF)
+    stage = [d_out[r * m_local:(r + 1) * m_local].contiguous() for r in range(tp)]
+    gathered = torch.zeros(m, d_model, device=dev, dtype=BF)
+    gathered[:m_local].copy_(stage[0])
+    d_gate_up = torch.zeros(m, 2 * d_ff, device=dev, dtype=BF)
+    group.launch(MODE_ALL_GATHER, m, d_ff, d_model, d_gate_up, b=w2, b_mn=True, gathered=gathered, stage=stage,
+                 swiglu=2, aux=gate_up)
+    torch.cuda.synchronize()
+    pairs = gate_up.float().requires_grad_()
+    reference.swiglu_interleaved(pairs).backward(d_out.float() @ w2.float())
+    assert torch.equal(gathered, d_out)
+    assert _rel(d_gate_up, pairs.grad) < 6e-3
+    assert native.check_status() == 0
+
+
 @pytest.mark.parametrize("tp,m_local,n,k,b_mn", [(2, 512, 1024, 512, False), (2, 128, 1000, 256, True),
                                                  (4, 256, 512, 256, False), (8, 256, 768, 128, False),
                                                  (8, 384, 256, 256, True)])

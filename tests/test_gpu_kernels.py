@@ -156,6 +156,38 @@ def test_swiglu_interleaved():
     assert _rel_err(act, actr) < 5e-3 and _rel_err(gu.grad, gur.grad) < 8e-3
 
 
+@pytest.mark.parametrize("rows,d_model,d_ff", [(1024, 512, 1408), (777, 256, 352), (4096, 2048, 5632)])
+def test_swiglu_inside_the_projection_epilogues(rows, d_model, d_ff):
+    """The feed-forward block whose activation and activation gradient are computed by GEMM epilogues, against
+    the fp32 statement and against the three-step path."""
+    from ajllm_b200.ops import functional
+
+    torch.manual_seed(60)
+    dev = _dev()
+    x = torch.randn(rows, d_model, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    w13 = (torch.randn(2 * d_ff, d_model, device=dev) * d_model ** -0.5).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(d_model, d_ff, device=dev) * d_ff ** -0.5).to(torch.bfloat16).requires_grad_()
+    assert functional.FUSED_SWIGLU
+    before = native.launch_count
+    y = ops.swiglu_ffn(x, w13, w2)
+    assert native.launch_count - before == 2        # two GEMMs, no separate activation kernel
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, w13r, w2r = (t.detach().float().requires_grad_() for t in (x, w13, w2))
+    yr = reference.linear(reference.swiglu_interleaved(reference.linear(xr, w13r)), w2r)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 8e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(w13.grad, w13r.grad) < 1e-2 and _rel_err(w2.grad, w2r.grad) < 1e-2
+    # the same block as three steps (both round the pair to bf16 before the activation)
+    x3, w133, w23 = (t.detach().clone().requires_grad_() for t in (x, w13, w2))
+    y3 = ops.linear(ops.swiglu_interleaved(ops.linear(x3, w133)), w23)
+    y3.backward(g)
+    assert _rel_err(y3, y) < 1e-3
+    assert _rel_err(x.grad, x3.grad) < 4e-3 and _rel_err(w13.grad, w133.grad) < 4e-3
+    with torch.no_grad():
+        assert _rel_err(ops.swiglu_ffn(x, w13, w2), y) < 1e-6     # inference form: the pre-activation is never written
+
+
 def test_embedding_and_scatter_add():
     torch.manual_seed(7)
     table = torch.randn(1000, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
