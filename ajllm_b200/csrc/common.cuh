@@ -564,6 +564,40 @@ __device__ __forceinline__ void swiglu_backward_rows(uint32_t taddr, const __nv_
     __syncwarp();
   }
 }
+
+// Row-per-lane registers to whole row segments in memory, for one warp of an epilogue (same padded block of shared
+// memory as above). w: 64 bf16 columns of lane l's row; they leave as 128 contiguous bytes per row, 8 lanes per row.
+__device__ __forceinline__ void store_rows_128(const uint32_t (&w)[32], __nv_bfloat16* out, long long ld, int rows_valid,
+                                               uint8_t* stage, int lane) {
+  uint4* mine = reinterpret_cast<uint4*>(stage + lane * kSwigluRowPitch);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) mine[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  __syncwarp();
+  const int sub = lane >> 3, piece = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = 4 * i + sub;
+    const uint4 q = *reinterpret_cast<const uint4*>(stage + r * kSwigluRowPitch + piece * 16);
+    if (r < rows_valid) reinterpret_cast<uint4*>(out + (long long)r * ld)[piece] = q;
+  }
+  __syncwarp();
+}
+// The same for 32 bf16 columns (64 bytes per row, 4 lanes per row).
+__device__ __forceinline__ void store_rows_64(const uint32_t (&w)[16], __nv_bfloat16* out, long long ld, int rows_valid,
+                                              uint8_t* stage, int lane) {
+  uint4* mine = reinterpret_cast<uint4*>(stage + lane * kSwigluRowPitch);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) mine[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  __syncwarp();
+  const int sub = lane >> 2, piece = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + sub;
+    const uint4 q = *reinterpret_cast<const uint4*>(stage + r * kSwigluRowPitch + piece * 16);
+    if (r < rows_valid) reinterpret_cast<uint4*>(out + (long long)r * ld)[piece] = q;
+  }
+  __syncwarp();
+}
 #endif  // __CUDACC__
 
 }  // namespace ajb

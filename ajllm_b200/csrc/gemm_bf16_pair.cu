@@ -18,6 +18,8 @@
 //   acc_full[b]  one per CTA, same mechanism.
 //   acc_empty[b] leader only, 8 arrivals: the four epilogue warps of each CTA (the peer's arrive remotely).
 // Every CTA fetches its own bytes with its own TMA loads.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_pair.h"
 
@@ -36,8 +38,7 @@ constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BNH * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * BN;
-constexpr int kSmemBytes = kStages * kStageBytes + 256;
-constexpr int kSmemBytesSwigluBackward = kSmemBytes + 4 * kSwigluWarpBytes;   // plus the epilogue warps' row blocks
+constexpr int kSmemBytes = kStages * kStageBytes + 256 + 4 * kSwigluWarpBytes;   // ring, barriers, a row block per epilogue warp
 constexpr int kKernelId = 10;
 
 // kStoreBf16Swiglu: C holds (gate, up) pairs in neighbouring columns; besides C (skipped when c is null) the epilogue
@@ -51,6 +52,7 @@ struct Params {
   void* c;
   void* c2;
   long long ldc2;
+  int row_stores;           // bf16 outputs leave as whole row segments through shared memory (AJB_GEMM_ROW_STORES=0: 16-byte pieces)
   int m, n, k;
   long long ldc;
   int epilogue;
@@ -82,7 +84,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  uint8_t* row_stage = smem_raw + kStages * kStageBytes + 256;          // SWIGLU_BWD: 4 warps x kSwigluWarpBytes
+  uint8_t* row_stage = smem_raw + kStages * kStageBytes + 256;          // 4 epilogue warps x kSwigluWarpBytes
   // both CTAs of a pair take the same branch here (same dynamic shared memory offset in both)
   const bool misaligned = smem_misaligned(smem_raw, p.status, kKernelId, reinterpret_cast<uint32_t*>(bars) + 60);
 
@@ -226,6 +228,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int col0 = tn * BN;
       const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.m;
+      // bf16 outputs whose rows start on 16-byte boundaries go out as whole row segments
+      const bool bf16_rows = p.row_stores && (p.epilogue == kStoreBf16 || p.epilogue == kStoreBf16Swiglu) && (p.ldc & 7) == 0 &&
+                             (reinterpret_cast<uintptr_t>(p.c) & 15) == 0;
       if (SWIGLU_BWD) {
         // the accumulators are d_act: turned into the gradient of the saved (gate, up) pairs, 32 columns at a time
         // (n is a multiple of 32: a chunk is whole or absent)
@@ -237,10 +242,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       } else
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
+        const int col = col0 + c;
+        if (bf16_rows && (c & 63) == 0 && col + 64 <= p.n) {
+          // 64 whole columns: bf16 rows leave as 128-byte segments through the warp's row block
+          const int row0 = row - lane;
+          uint32_t w[32];
+          {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + (uint32_t)c, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+            tmem_ld_32x32(taddr + (uint32_t)(c + 32), v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) w[16 + j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+          }
+          uint8_t* stage = row_stage + quarter * kSwigluWarpBytes;
+          if (p.c != nullptr)
+            store_rows_128(w, reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row0 * p.ldc + col, p.ldc, p.m - row0, stage, lane);
+          if (p.epilogue == kStoreBf16Swiglu) {
+            uint32_t a[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[2 * j]));
+              const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[2 * j + 1]));
+              a[j] = pack_bf16x2(p0.x / (1.0f + __expf(-p0.x)) * p0.y, p1.x / (1.0f + __expf(-p1.x)) * p1.y);
+            }
+            store_rows_64(a, reinterpret_cast<__nv_bfloat16*>(p.c2) + (long long)row0 * p.ldc2 + (col >> 1), p.ldc2,
+                          p.m - row0, stage, lane);
+          }
+          c += 32;
+          continue;
+        }
         uint32_t v[32];
         tmem_ld_32x32(taddr + (uint32_t)c, v);
         tc_wait_ld();
-        const int col = col0 + c;
         if (!row_ok || col >= p.n) continue;
         const int valid = min(32, p.n - col);
         if (p.epilogue == kStoreBf16Swiglu) {
@@ -347,7 +384,6 @@ static int resident_pairs(Kernel kernel) {
 template <bool A_MN, bool B_MN, bool SWIGLU_BWD = false>
 static int launch(const void* a, const void* b, void* c, int m, int n, int k, long long lda, long long ldb, long long ldc,
                   int epilogue, int split_k, cudaStream_t stream, void* c2 = nullptr, long long ldc2 = 0) {
-  constexpr int kSmemBytes = SWIGLU_BWD ? kSmemBytesSwigluBackward : gemm_pair::kSmemBytes;
   CUtensorMap map_a, map_b;
   int rc;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -366,6 +402,11 @@ static int launch(const void* a, const void* b, void* c, int m, int n, int k, lo
   }
   const int pairs = capacity();
   Params p;
+  static const bool row_stores = [] {
+    const char* v = std::getenv("AJB_GEMM_ROW_STORES");
+    return v == nullptr || v[0] != '0';
+  }();
+  p.row_stores = row_stores ? 1 : 0;
   p.c = c; p.c2 = c2; p.ldc2 = ldc2; p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.epilogue = epilogue;
   p.tiles_m = (m + 2 * BM - 1) / (2 * BM);
   p.tiles_n = (n + BN - 1) / BN;
