@@ -88,6 +88,7 @@ class LLMEngine:
         self.seed = seed
         self._generators: dict[int, torch.Generator] = {}
         self._draws: dict[int, int] = {}
+        self._sampling_state = None          # (key, temps, top_ps, seeds, counters) of the previous sampling call
         self._finished: list[Sequence] = []
 
     # ---------------------------------------------------------------- requests
@@ -121,7 +122,17 @@ class LLMEngine:
         return serving.sample_rows(logits.float(), temps, top_ps, seeds, counters).tolist()
 
     def _device_sampling_state(self, seqs: list[Sequence], device, draws: int):
-        """Per-row temperature / top-p / (seed, counter) tensors; advances each request's draw counter."""
+        """Per-row temperature / top-p / (seed, counter) tensors; advances each request's draw counter. While the batch
+        keeps its composition (the usual case between two arrivals or departures) the tensors of the previous step are
+        reused and the counters advance on the device."""
+        key = (draws, tuple(s.request_id for s in seqs))
+        cached = self._sampling_state
+        if cached is not None and cached[0] == key and cached[1].device == device:
+            _, temps, top_ps, seeds, counters = cached
+            counters.add_(draws)
+            for s in seqs:
+                self._draws[s.request_id] += draws
+            return temps, top_ps, seeds, counters
         temps = torch.tensor([s.params.temperature for s in seqs], dtype=torch.float32, device=device)
         top_ps = torch.tensor([(s.params.top_p if s.params.top_p is not None else 1.0) for s in seqs],
                               dtype=torch.float32, device=device)
@@ -131,8 +142,10 @@ class LLMEngine:
             seeds.append(seed & 0x7FFFFFFFFFFFFFFF)
             counters.append(self._draws.get(s.request_id, 0))
             self._draws[s.request_id] = counters[-1] + draws
-        return (temps, top_ps, torch.tensor(seeds, dtype=torch.int64, device=device),
-                torch.tensor(counters, dtype=torch.int64, device=device))
+        state = (temps, top_ps, torch.tensor(seeds, dtype=torch.int64, device=device),
+                 torch.tensor(counters, dtype=torch.int64, device=device))
+        self._sampling_state = (key, *state)
+        return state
 
     def _emit(self, seq: Sequence, token: int, now: float) -> bool:
         """Append a generated token; returns True when the sequence finished."""
@@ -189,7 +202,7 @@ class LLMEngine:
         items, owners = [], []
         for item in prefill + decode:
             seq = item.seq
-            new = seq.tokens[seq.computed:seq.computed + item.num_new_tokens]
+            new = seq.token_slice(seq.computed, seq.computed + item.num_new_tokens)
             items.append(RunItem(seq.request_id, new, 1 if item.samples else 0))
             owners.append(item)
         if items:
@@ -237,15 +250,15 @@ class LLMEngine:
             items = []
             for seq, proposed in zip(seqs, drafts):
                 have = self.draft_cache.length(seq.request_id)
-                items.append(RunItem(seq.request_id, (seq.tokens + proposed)[have:], 1))
+                items.append(RunItem(seq.request_id, seq.token_slice(have, seq.total_len) + proposed[max(0, have - seq.total_len):], 1))
             logits = self.draft_runner.forward(items).float()
             temps, top_ps, seeds, counters = self._device_sampling_state(seqs, device, draws=1)
-            top_ps.fill_(1.0)          # the accept rule below compares plain softmax distributions
+            top_ps = torch.ones_like(top_ps)          # the accept rule below compares plain softmax distributions
             tokens = serving.sample_rows(logits, temps, top_ps, seeds, counters)
             draft_logits.append(logits)
             for row, token in enumerate(tokens.tolist()):
                 drafts[row].append(token)
-        items = [RunItem(seq.request_id, seq.tokens[seq.computed:] + proposed, k + 1) for seq, proposed in zip(seqs, drafts)]
+        items = [RunItem(seq.request_id, seq.token_slice(seq.computed, seq.total_len) + proposed, k + 1) for seq, proposed in zip(seqs, drafts)]
         target = self.runner.forward(items).float().view(len(seqs), k + 1, -1)
         temps, _, seeds, counters = self._device_sampling_state(seqs, device, draws=2 * k + 1)
         verdict = serving.spec_verify(target, torch.stack(draft_logits, dim=1),
@@ -296,7 +309,7 @@ class LLMEngine:
                     draft_probs[row].append(probs)
                 drafts[row].append(token)
         # --- target scores the last accepted token plus the k proposals in one pass
-        items = [RunItem(seq.request_id, seq.tokens[seq.computed:] + proposed, k + 1)
+        items = [RunItem(seq.request_id, seq.token_slice(seq.computed, seq.total_len) + proposed, k + 1)
                  for seq, proposed in zip(seqs, drafts)]
         logits = self.runner.forward(items)
         now = time.perf_counter()

@@ -56,6 +56,7 @@ class BlockTable:
 
     blocks: list[int] = field(default_factory=list)
     length: int = 0
+    shrinks: int = 0          # how often blocks were given back (a mirror of `blocks` elsewhere must then be rebuilt)
 
 
 class PagedKVCache:
@@ -103,6 +104,7 @@ class PagedKVCache:
         keep = (new_length + self.block_size - 1) // self.block_size
         while len(table.blocks) > keep:
             self.allocator.release(table.blocks.pop())
+            table.shrinks += 1
 
     def fork(self, parent_id: int, child_id: int) -> None:
         """``child`` shares every block of ``parent`` (copy-on-write is the caller's duty: a shared last
@@ -125,12 +127,13 @@ class PagedKVCache:
 
     # ---------------------------------------------------------------- device views
     def block_table_tensor(self, seq_ids: list[int], device: torch.device) -> torch.Tensor:
+        import numpy as np
         width = max((len(self.tables[s].blocks) for s in seq_ids), default=1) or 1
-        out = torch.zeros(len(seq_ids), width, dtype=torch.int32)
+        out = np.zeros((len(seq_ids), width), dtype=np.int32)
         for row, s in enumerate(seq_ids):
             blocks = self.tables[s].blocks
-            out[row, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
-        return out.to(device)
+            out[row, :len(blocks)] = blocks
+        return torch.from_numpy(out).to(device)
 
     def write(self, layer: int, slots: torch.Tensor, keys: torch.Tensor, values: torch.Tensor) -> None:
         """``keys`` / ``values`` are ``[tokens, kv_heads, head_dim]``; ``slots`` the flat slot of each token."""

@@ -44,22 +44,87 @@ def _matmul(x: torch.Tensor, weight) -> torch.Tensor:
     return ops.linear(x, weight)
 
 
+class DecodeStaging:
+    """Host side of a replayed decoding step: token ids, positions, cache slots, context lengths and block tables of
+    the step, kept in two host arrays that persist across steps (pinned when a GPU is present) so that a step costs
+    two host-to-device copies and no allocation. Block-table rows are rewritten only for rows whose sequence changed;
+    a row that keeps its sequence only gets the blocks appended since the previous step."""
+
+    def __init__(self, bucket: int, q_len: int, max_blocks: int, scratch_block: int, block_size: int, pinned: bool) -> None:
+        self.bucket, self.q_len, self.max_blocks = bucket, q_len, max_blocks
+        self.scratch_block, self.block_size = scratch_block, block_size
+        rows = bucket * q_len
+        self.rows = torch.zeros(3, rows, dtype=torch.long, pin_memory=pinned)                  # ids, positions, slots
+        self.meta = torch.zeros(bucket * (1 + max_blocks), dtype=torch.int32, pin_memory=pinned)   # ctx, then tables
+        self._rows = self.rows.numpy()
+        self._ctx = self.meta.numpy()[:bucket]
+        self._tables = self.meta.numpy()[bucket:].reshape(bucket, max_blocks)
+        self._tables[:] = scratch_block
+        self._row_table = [None] * bucket        # block table (object) a row mirrors, and how often it had shrunk then
+        self._row_shrinks = [0] * bucket
+        self._row_blocks = [0] * bucket          # how many of its blocks are written
+
+    def fill(self, items, cache) -> None:
+        """Stages one step; reserves the cache slots of the new tokens (``cache.append_slots``)."""
+        q_len, n = self.q_len, len(items)
+        rows, ctx, tables = self._rows, self._ctx, self._tables
+        block_size = self.block_size
+        for i, item in enumerate(items):
+            seq_id = item.seq_id
+            start = cache.length(seq_id)
+            slots = cache.append_slots(seq_id, q_len)
+            lo = i * q_len
+            if q_len == 1:
+                rows[0, lo] = item.token_ids[0]
+                rows[1, lo] = start
+                rows[2, lo] = slots[0]
+            else:
+                rows[0, lo:lo + q_len] = item.token_ids
+                rows[1, lo:lo + q_len] = range(start, start + q_len)
+                rows[2, lo:lo + q_len] = slots
+            ctx[i] = start + q_len
+            table = cache.tables[seq_id]
+            blocks = table.blocks
+            # same table object and no block given back since (rejected draft tokens, preemption): only new blocks
+            same = self._row_table[i] is table and self._row_shrinks[i] == table.shrinks
+            have = self._row_blocks[i] if same else 0
+            if have != len(blocks) or not same:
+                tables[i, have:len(blocks)] = blocks[have:]
+                self._row_table[i], self._row_shrinks[i], self._row_blocks[i] = table, table.shrinks, len(blocks)
+        # padding rows: q_len tokens of nothing in the scratch block
+        for i in range(n, self.bucket):
+            if self._row_table[i] is not None or ctx[i] != q_len:
+                lo = i * q_len
+                rows[0, lo:lo + q_len] = 0
+                rows[1, lo:lo + q_len] = range(q_len)
+                rows[2, lo:lo + q_len] = range(self.scratch_block * block_size, self.scratch_block * block_size + q_len)
+                ctx[i] = q_len
+                tables[i, 0] = self.scratch_block
+                self._row_table[i], self._row_blocks[i] = None, 0
+
+
 class _DecodeGraph:
     """Static buffers and the captured graph of one (batch-size bucket, new tokens per sequence) pair: one new token
     for plain decoding, ``k + 1`` for the verification pass of speculative decoding."""
 
-    def __init__(self, bucket: int, q_len: int, max_blocks: int, device: torch.device) -> None:
+    def __init__(self, bucket: int, q_len: int, max_blocks: int, device: torch.device, scratch_block: int,
+                 block_size: int) -> None:
         self.bucket, self.q_len = bucket, q_len
         rows = bucket * q_len
-        self.ids = torch.zeros(rows, dtype=torch.long, device=device)
-        self.pos = torch.zeros(rows, dtype=torch.long, device=device)
+        self.staging = DecodeStaging(bucket, q_len, max_blocks, scratch_block, block_size, pinned=device.type == "cuda")
+        self.rows = torch.zeros(3, rows, dtype=torch.long, device=device)
+        self.ids, self.pos, self.slots = self.rows[0], self.rows[1], self.rows[2]
         self.pos32 = torch.zeros(rows, dtype=torch.int32, device=device)
-        self.slots = torch.zeros(rows, dtype=torch.long, device=device)
-        self.tables = torch.zeros(bucket, max_blocks, dtype=torch.int32, device=device)
-        self.ctx = torch.full((bucket,), q_len, dtype=torch.int32, device=device)
+        self.meta = torch.zeros(bucket * (1 + max_blocks), dtype=torch.int32, device=device)
+        self.ctx = self.meta[:bucket]
+        self.tables = self.meta[bucket:].view(bucket, max_blocks)
         self.starts = torch.arange(bucket, dtype=torch.int32, device=device) * q_len
         self.logits: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
+
+    def upload(self) -> None:
+        self.rows.copy_(self.staging.rows, non_blocking=True)
+        self.meta.copy_(self.staging.meta, non_blocking=True)
 
 
 class ModelRunner:
@@ -118,6 +183,7 @@ class ModelRunner:
         plan = object.__new__(serving.PagedPlan)
         plan.total_rows = n
         plan.launches = [(g.q_len, g.bucket, g.tables, g.starts, g.ctx)]
+        g.pos32.copy_(g.pos)
         stream = model.token_embeddings(g.ids)
         if model.position_embeddings is not None:
             stream = stream + model.position_embeddings(g.pos)
@@ -150,11 +216,9 @@ class ModelRunner:
         if self._scratch_block is None:
             self._scratch_block = cache.allocator.allocate()       # padding rows read and write this block only
         max_blocks = (self.model.context_length + cache.block_size - 1) // cache.block_size
-        g = _DecodeGraph(bucket, q_len, max_blocks, self.device)
-        g.tables.fill_(self._scratch_block)
-        g.slots.copy_(self._scratch_block * cache.block_size + (torch.arange(bucket * q_len, device=self.device) % q_len))
-        g.pos.copy_(torch.arange(bucket * q_len, device=self.device) % q_len)
-        g.pos32.copy_(g.pos)
+        g = _DecodeGraph(bucket, q_len, max_blocks, self.device, self._scratch_block, cache.block_size)
+        g.staging.fill([], cache)            # every row is a padding row: the capture reads and writes the scratch block only
+        g.upload()
         # one eager run on a side stream first (lazy kernel attributes, allocator warm-up), then the capture
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -190,29 +254,8 @@ class ModelRunner:
                 raise ValueError(f"sequence {item.seq_id} would exceed the context length {model.context_length}")
         bucket = next(b for b in self.GRAPH_BUCKETS if b >= n)
         g = self._graph_for(bucket, q_len)
-        tokens, positions, slots, ctx = [], [], [], []
-        for item in items:
-            start = cache.length(item.seq_id)
-            slots.extend(cache.append_slots(item.seq_id, q_len))
-            tokens.extend(item.token_ids)
-            positions.extend(range(start, start + q_len))
-            ctx.append(start + q_len)
-        pad = bucket - n
-        scratch_slot = self._scratch_block * cache.block_size
-        pad_rows = list(range(q_len)) * pad
-        rows = torch.tensor([tokens + [0] * (pad * q_len), positions + pad_rows, slots + [scratch_slot + r for r in pad_rows]],
-                            dtype=torch.long).pin_memory()
-        per_seq = torch.tensor(ctx + [q_len] * pad, dtype=torch.int32).pin_memory()
-        staged = rows.to(self.device, non_blocking=True)
-        g.ids.copy_(staged[0])
-        g.pos.copy_(staged[1])
-        g.pos32.copy_(staged[1])
-        g.slots.copy_(staged[2])
-        g.ctx.copy_(per_seq.to(self.device, non_blocking=True))
-        tables = cache.block_table_tensor([item.seq_id for item in items], self.device)
-        g.tables[:n, :tables.shape[1]].copy_(tables)
-        if pad:
-            g.tables[n:, 0].fill_(self._scratch_block)
+        g.staging.fill(items, cache)
+        g.upload()
         g.graph.replay()
         return g.logits[:n * q_len]
 

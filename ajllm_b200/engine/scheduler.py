@@ -34,7 +34,7 @@ class SamplingParams:
     seed: int | None = None
 
 
-@dataclass
+@dataclass(eq=False)          # sequences are compared and hashed by identity (a field-wise == would walk the prompts)
 class Sequence:
     request_id: int
     prompt: list[int]
@@ -51,6 +51,15 @@ class Sequence:
     @property
     def tokens(self) -> list[int]:
         return self.prompt + self.output
+
+    def token_slice(self, start: int, stop: int) -> list[int]:
+        """``tokens[start:stop]`` without joining prompt and output."""
+        split = len(self.prompt)
+        if stop <= split:
+            return self.prompt[start:stop]
+        if start >= split:
+            return self.output[start - split:stop - split]
+        return self.prompt[start:] + self.output[:stop - split]
 
     @property
     def total_len(self) -> int:
@@ -114,14 +123,15 @@ class Scheduler:
         """``decode_tokens`` is 1 for plain decoding and ``k + 1`` for a speculative verify step."""
         plan: list[ScheduledSeq] = []
         reserved: dict[int, int] = {}          # request id -> blocks promised to it in this plan
+        promised = 0                           # their sum
         budget = self.max_batched_tokens
 
         def fits(seq: Sequence, new: int) -> bool:
-            return self.cache.blocks_needed(seq.request_id, new) <= self.cache.allocator.free_blocks - sum(reserved.values())
+            return self.cache.blocks_needed(seq.request_id, new) <= self.cache.allocator.free_blocks - promised
 
         # 1. running sequences (decode, or the next chunk of a long prefill)
         for seq in list(self.running):
-            if seq not in self.running:
+            if seq.status is not SeqStatus.RUNNING:
                 continue              # preempted while making room for an earlier sequence
             if seq.remaining_prefill > 1:
                 new = min(seq.remaining_prefill, budget)
@@ -136,14 +146,15 @@ class Scheduler:
                     break
                 assert len(self.running) < victim_count
                 for item in plan:
-                    if item.seq not in self.running:
+                    if item.seq.status is not SeqStatus.RUNNING:
                         budget += item.num_new_tokens
-                        reserved.pop(item.seq.request_id, None)
-                plan = [item for item in plan if item.seq in self.running]
+                        promised -= reserved.pop(item.seq.request_id, 0)
+                plan = [item for item in plan if item.seq.status is SeqStatus.RUNNING]
             if not fits(seq, new):
                 continue
             budget -= new
             reserved[seq.request_id] = self.cache.blocks_needed(seq.request_id, new)
+            promised += reserved[seq.request_id]
             plan.append(ScheduledSeq(seq, new, is_prefill, samples))
         # 2. admit waiting requests
         while self.waiting and len(self.running) < self.max_num_seqs and budget > 0:
@@ -156,6 +167,7 @@ class Scheduler:
             self.running.append(seq)
             budget -= new
             reserved[seq.request_id] = self.cache.blocks_needed(seq.request_id, new)
+            promised += reserved[seq.request_id]
             plan.append(ScheduledSeq(seq, new, True, new == seq.remaining_prefill))
         if not plan and self.running and not self.waiting:
             raise RuntimeError("KV cache is too small to make progress on a single sequence")

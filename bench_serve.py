@@ -44,6 +44,10 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--self-draft", action="store_true", help="with --speculative: the draft is the target's first 2 layers")
+    ap.add_argument("--decode-steps", type=int, default=0,
+                    help="instead of the request mix: fill --max-num-seqs sequences of --context tokens, then time this "
+                         "many pure decoding steps (ms per step on the device and on the host clock)")
+    ap.add_argument("--context", type=int, default=1280, help="with --decode-steps: prompt tokens per sequence")
     ap.add_argument("--suite", action="store_true",
                     help="bf16 greedy on --requests requests, then shorter fp8 / speculative variants, in one JSON line")
     return ap.parse_args()
@@ -72,6 +76,45 @@ def _self_draft(model, config, layers: int = 2):
     draft.final_norm = model.final_norm
     draft.lm_head = model.lm_head
     return draft
+
+
+def _decode_steps(args, model, device, quantization=None):
+    """Pure decoding: every sequence holds ``--context`` tokens, each timed step emits one token per sequence."""
+    import numpy as np
+    import torch
+
+    from ajllm_b200.engine import LLMEngine, SamplingParams
+
+    seqs, steps = args.max_num_seqs, args.decode_steps
+    # sequences admitted first keep decoding while the others are still prefilled: nobody may finish before the end
+    fill_steps = -(-seqs * args.context // args.max_batched_tokens) + 8
+    budget = fill_steps + steps + 16
+    blocks = (seqs * (args.context + budget + 32)) // 16
+    engine = LLMEngine(model, block_size=16, num_blocks=blocks, max_num_seqs=seqs,
+                       max_batched_tokens=args.max_batched_tokens, quantization=quantization, seed=0)
+    rng = np.random.default_rng(0)
+    for _ in range(seqs):
+        engine.add_request(rng.integers(0, VOCAB, size=args.context).tolist(), SamplingParams(budget, 0.0, None, None))
+    for _ in range(fill_steps):
+        engine.step()
+    if len(engine.scheduler.running) != seqs or any(seq.computed < args.context for seq in engine.scheduler.running):
+        raise RuntimeError("the sequences were not all prefilled within the expected number of steps")
+    for _ in range(3):
+        engine.step()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()          # a profiler started with --profile-from-start off sees only the timed steps
+    t0 = time.perf_counter()
+    begin.record()
+    for _ in range(steps):
+        engine.step()
+    end.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    host_ms = (time.perf_counter() - t0) * 1e3 / steps
+    return {"metric": "decode step", "sequences": seqs, "context": args.context, "steps": steps,
+            "dtype": quantization or "bf16", "ms_per_step_device": begin.elapsed_time(end) / steps,
+            "ms_per_step_host": host_ms, "tokens_per_s": seqs / host_ms * 1e3}
 
 
 def _one_run(args, model, config, tp, device, rank, world, *, requests, quantization=None, speculative=0,
@@ -165,7 +208,9 @@ def run_ours(args):
     with torch.device(device):
         model = build_model(config, VOCAB, tp=tp).to(dtype=torch.bfloat16)
     run = lambda **kw: _one_run(args, model, config, tp, device, rank, world, **kw)   # noqa: E731
-    if not args.suite:
+    if args.decode_steps:
+        record = _decode_steps(args, model, device, args.quantization)
+    elif not args.suite:
         record = run(requests=args.requests, quantization=args.quantization, speculative=args.speculative,
                      temperature=args.temperature, self_draft=args.self_draft)
     else:

@@ -170,3 +170,53 @@ def test_scheduler_rejects_impossible_requests(models):
         sched.add([], SamplingParams())
     sched.add(list(range(30)), SamplingParams())
     assert sched.schedule() == []          # the prompt can never fit in two blocks of four tokens
+
+
+def test_decode_staging_mirrors_the_block_tables_under_churn():
+    """The persistent host arrays of a replayed decoding step against the cache's own tables while sequences come,
+    go, change rows and are rolled back (rejected draft tokens give blocks back and take other ones later)."""
+    import random
+
+    from ajllm_b200.engine.kv_cache import PagedKVCache
+    from ajllm_b200.engine.model_runner import DecodeStaging, RunItem
+
+    random.seed(0)
+    for q_len in (1, 5):
+        cache = PagedKVCache(1, 400, 16, 1, 8, torch.float32, torch.device("cpu"))
+        scratch = cache.allocator.allocate()
+        st = DecodeStaging(8, q_len, 16, scratch, 16, pinned=False)
+        live = {}
+        nxt = 0
+        for step in range(300):
+            # random churn: add / remove / rollback sequences
+            while len(live) < 8 and random.random() < 0.5:
+                cache.append_slots(nxt, random.randint(1, 40)); live[nxt] = True; nxt += 1
+            for s in list(live):
+                r = random.random()
+                if r < 0.05 or cache.length(s) + q_len > 250:
+                    cache.free(s); del live[s]
+                elif r < 0.3 and q_len > 1:
+                    cache.truncate(s, max(1, cache.length(s) - random.randint(0, q_len - 1)))
+            ids = list(live)
+            random.shuffle(ids)
+            ids = ids[:random.randint(0, len(ids))]
+            if not ids: continue
+            items = [RunItem(s, [random.randint(0, 99) for _ in range(q_len)], q_len) for s in ids]
+            before = {s: cache.length(s) for s in ids}
+            st.fill(items, cache)
+            rows, meta = st.rows.numpy(), st.meta.numpy()
+            ctx, tables = meta[:8], meta[8:].reshape(8, 16)
+            for i, it in enumerate(items):
+                lo = i * q_len
+                assert list(rows[0, lo:lo+q_len]) == it.token_ids
+                assert list(rows[1, lo:lo+q_len]) == list(range(before[it.seq_id], before[it.seq_id] + q_len))
+                blocks = cache.tables[it.seq_id].blocks
+                assert list(tables[i, :len(blocks)]) == blocks, (step, i)
+                for j, p in enumerate(range(before[it.seq_id], before[it.seq_id] + q_len)):
+                    assert rows[2, lo + j] == blocks[p // 16] * 16 + p % 16
+                assert ctx[i] == before[it.seq_id] + q_len
+            for i in range(len(items), 8):
+                lo = i * q_len
+                assert ctx[i] == q_len and tables[i, 0] == scratch
+                assert list(rows[2, lo:lo+q_len]) == [scratch * 16 + r for r in range(q_len)]
+                assert list(rows[1, lo:lo+q_len]) == list(range(q_len))
