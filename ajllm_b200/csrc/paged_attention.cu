@@ -22,6 +22,13 @@
 // partial row sums) are exchanged through shared memory; P is assembled in rows 0..31 of the operand
 // tile, so only the first quarter of O is meaningful and the first warp alone rescales and stores it.
 //
+// In that variant the probability tile exists twice (only its first 32 rows matter, 4 KB each; the operand rows behind
+// them may hold anything, they feed accumulator rows that nobody reads), so the softmax of tile j + 1 does not wait for
+// the second product of tile j; and the partial maxima of tile j are exchanged while tile j + 1 is being computed:
+// tile j is exponentiated against the reference maximum of the tiles before it (exact for the first tile), which is
+// safe because bf16 and fp32 share the exponent range: the exponent is capped at 120, a cap that only a score jump of
+// more than 80 natural units above everything seen before could reach.
+//
 // Long contexts at small batch: with `splits` > 1 the tiles of a sequence are divided over `splits` CTAs (grid z).
 // Each writes its un-normalised fp32 output rows and (reference maximum, row sum) to a workspace, and a second small
 // kernel merges the parts with the usual log-sum-exp weights. One CTA per (sequence, KV head) walks a 4k context as
@@ -42,6 +49,7 @@ constexpr int kThreads = 192;
 constexpr int kMaxRows = 64;       // group * q_len
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kPagedKernelId = 5;
+constexpr int kReplTileBytes = 32 * 128;   // REPL variant: the 32 meaningful rows of a probability tile (64 keys x 2 bytes per row)
 
 template <int HD>
 struct Cfg {
@@ -84,20 +92,26 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   using C = Cfg<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
+  // Q, P, the K/V ring, barriers. P sits in front of the ring: the second probability tile of the REPL variant starts
+  // 4 KB into P and its (unused) operand rows reach into the ring, never past the end of the allocation
   uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + C::kQ;
-  uint8_t* sP = sKV + 4 * C::kTile;
+  uint8_t* sP = sQ + C::kQ;
+  uint8_t* sKV = sP + C::kP;
   float* sExchange = reinterpret_cast<float*>(sP + C::kExchangeOffset);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kP);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + 4 * C::kTile);
   if (smem_misaligned(smem, p.status, kPagedKernelId, reinterpret_cast<uint32_t*>(bars) + 60)) return;
-  uint64_t* kv_full = bars;        // 2
-  uint64_t* kv_empty = bars + 2;   // 2
-  uint64_t* s_full = bars + 4;     // 2
-  uint64_t* s_free = bars + 6;     // 2
-  uint64_t* p_ready = bars + 8;    // 1
-  uint64_t* pv_done = bars + 9;    // 1
-  uint64_t* xbar = bars + 10;      // 1 (REPL: the four softmax warps exchange partial maxima / sums)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  // K and V tiles have their own barriers: a K tile is free again after the first product of its step, long before
+  // the V tile of the same step, and the issuing warp must never find the next K tile missing when it gets there
+  uint64_t* k_full = bars;         // 2
+  uint64_t* k_empty = bars + 2;    // 2
+  uint64_t* v_full = bars + 4;     // 2
+  uint64_t* v_empty = bars + 6;    // 2
+  uint64_t* s_full = bars + 8;     // 2
+  uint64_t* s_free = bars + 10;    // 2
+  uint64_t* p_ready = bars + 12;   // 2 (REPL: one per probability tile; otherwise only the first)
+  uint64_t* pv_done = bars + 14;   // 2 (likewise)
+  uint64_t* xbar = bars + 16;      // 1 (REPL: the four softmax warps exchange partial maxima / sums)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -115,13 +129,15 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_free[i], 4);
+      mbar_init(&p_ready[i], 4);
+      mbar_init(&pv_done[i], 1);
     }
-    mbar_init(p_ready, 4);
-    mbar_init(pv_done, 1);
     mbar_init(xbar, 4);
     *abort_flag = 0;
     fence_barrier_init();
@@ -152,26 +168,68 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
-      for (int j = 0; j < n_tiles; ++j) {
+    // Producer. The block ids of eight tiles (32 blocks) are fetched by the 32 lanes with one coalesced load, a group
+    // ahead of their use, and handed to the issuing lane by shuffles: a dependent table lookup per block in front of
+    // its copies would cost more than the copies themselves.
+    constexpr int kBlocksPerTile = TILE / BLOCK_TOKENS;
+    constexpr int kTilesPerGroup = 32 / kBlocksPerTile;
+    const int last_block = (ctx + BLOCK_TOKENS - 1) / BLOCK_TOKENS - 1;
+    // blocks past the end of the sequence re-read the last valid block (masked later); keeps the byte count fixed
+    auto fetch_ids = [&](int group) { return table[max(0, min(last_block, (t0 + group * kTilesPerGroup) * kBlocksPerTile + lane))]; };
+    int ids_next = n_tiles > 0 ? fetch_ids(0) : 0;
+    bool ok = true;
+    // K tiles run one step ahead of V tiles: K(j + 1) goes out as soon as the first product of step j - 1 has read
+    // its slot, V(j) when the second product of step j - 2 has
+    int ids_k = ids_next, ids_prev = ids_next;      // block ids of K's group of tiles and of the group before it
+    int k_group = -1;
+    for (int j = 0; j <= n_tiles && ok; ++j) {
+      if (j < n_tiles) {
+        if (j % kTilesPerGroup == 0) {
+          ids_prev = ids_k;
+          ids_k = ids_next;
+          k_group = j / kTilesPerGroup;
+          if (j + kTilesPerGroup < n_tiles) ids_next = fetch_ids(k_group + 1);
+        }
         const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], (((uint32_t)j >> 1) & 1) ^ 1, abort_flag, p.status, kPagedKernelId, 1)) break;
-        uint8_t* sK = sKV + s * 2 * C::kTile;
-        uint8_t* sV = sK + C::kTile;
-        mbar_arrive_expect_tx(&kv_full[s], 2 * C::kTile);
-        const int first_block = (t0 + j) * (TILE / BLOCK_TOKENS);
-        const int blocks_here = min(TILE / BLOCK_TOKENS, (ctx + BLOCK_TOKENS - 1) / BLOCK_TOKENS - first_block);
-#pragma unroll 1
-        for (int b = 0; b < TILE / BLOCK_TOKENS; ++b) {
-          // blocks past the end of the sequence re-read the last valid block (masked later); keeps the byte count fixed
-          const int id = table[first_block + min(b, blocks_here - 1)];
+        int id[kBlocksPerTile];
 #pragma unroll
-          for (int i = 0; i < HD / 64; ++i) {
-            tma_load_3d(sK + i * (TILE * 128) + b * (BLOCK_TOKENS * 128), &map_k, &kv_full[s], kv_head * HD + 64 * i, 0, id);
-            tma_load_3d(sV + i * (TILE * 128) + b * (BLOCK_TOKENS * 128), &map_v, &kv_full[s], kv_head * HD + 64 * i, 0, id);
+        for (int b = 0; b < kBlocksPerTile; ++b) id[b] = __shfl_sync(0xffffffffu, ids_k, (j % kTilesPerGroup) * kBlocksPerTile + b);
+        if (lane == 0) {
+          ok = mbar_wait(&k_empty[s], (((uint32_t)j >> 1) & 1) ^ 1, abort_flag, p.status, kPagedKernelId, 1);
+          if (ok) {
+            uint8_t* sK = sKV + s * 2 * C::kTile;
+            mbar_arrive_expect_tx(&k_full[s], C::kTile);
+#pragma unroll
+            for (int b = 0; b < kBlocksPerTile; ++b) {
+#pragma unroll
+              for (int i = 0; i < HD / 64; ++i)
+                tma_load_3d(sK + i * (TILE * 128) + b * (BLOCK_TOKENS * 128), &map_k, &k_full[s], kv_head * HD + 64 * i, 0, id[b]);
+            }
           }
         }
       }
+      if (j >= 1) {
+        const int jv = j - 1;
+        const int ids_v = (jv / kTilesPerGroup == k_group) ? ids_k : ids_prev;     // V is one step behind K
+        const int s = jv & 1;
+        int id[kBlocksPerTile];
+#pragma unroll
+        for (int b = 0; b < kBlocksPerTile; ++b) id[b] = __shfl_sync(0xffffffffu, ids_v, (jv % kTilesPerGroup) * kBlocksPerTile + b);
+        if (lane == 0 && ok) {
+          ok = mbar_wait(&v_empty[s], (((uint32_t)jv >> 1) & 1) ^ 1, abort_flag, p.status, kPagedKernelId, 2);
+          if (ok) {
+            uint8_t* sV = sKV + s * 2 * C::kTile + C::kTile;
+            mbar_arrive_expect_tx(&v_full[s], C::kTile);
+#pragma unroll
+            for (int b = 0; b < kBlocksPerTile; ++b) {
+#pragma unroll
+              for (int i = 0; i < HD / 64; ++i)
+                tma_load_3d(sV + i * (TILE * 128) + b * (BLOCK_TOKENS * 128), &map_v, &v_full[s], kv_head * HD + 64 * i, 0, id[b]);
+            }
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
   } else if (warp == 1) {
     constexpr uint32_t idesc_s = make_idesc(QROWS, TILE, 1, false, false);
@@ -185,7 +243,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     auto issue_s = [&](int j) -> bool {
       const int s = j & 1;
       const uint32_t use = (uint32_t)j >> 1;
-      if (!mbar_wait(&kv_full[s], use & 1, abort_flag, p.status, kPagedKernelId, 3)) return false;
+      if (!mbar_wait(&k_full[s], use & 1, abort_flag, p.status, kPagedKernelId, 3)) return false;
       if (!mbar_wait(&s_free[s], (use & 1) ^ 1, abort_flag, p.status, kPagedKernelId, 4)) return false;
       tc_fence_after_sync();
       if (lane == 0) {
@@ -196,6 +254,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int k = 1; k < HD / 16; ++k)
           umma_f16_c<true>(d, desc_at(q_km, k_major_step(k, QROWS * 128)), desc_at(k_km, k_major_step(k, TILE * 128)), idesc_s);
         tc_commit(&s_full[s]);
+        tc_commit(&k_empty[s]);
       }
       __syncwarp();
       return true;
@@ -206,16 +265,21 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         ok = issue_s(j + 1);
         if (!ok) break;
       }
-      if (!mbar_wait(p_ready, (uint32_t)j & 1, abort_flag, p.status, kPagedKernelId, 5)) { ok = false; break; }
+      // REPL: probability tile j & 1 (4 KB apart), its barriers complete every other tile
+      const int pb = REPL ? (j & 1) : 0;
+      const uint32_t p_phase = REPL ? (((uint32_t)j >> 1) & 1) : ((uint32_t)j & 1);
+      if (!mbar_wait(&p_ready[pb], p_phase, abort_flag, p.status, kPagedKernelId, 5)) { ok = false; break; }
+      if (!mbar_wait(&v_full[j & 1], ((uint32_t)j >> 1) & 1, abort_flag, p.status, kPagedKernelId, 10)) { ok = false; break; }
       tc_fence_after_sync();
       if (lane == 0) {
         const uint32_t v_mn = v_mn0 + (uint32_t)(j & 1) * kStageStep;
-        umma_f16(tmem_base + C::kOCol, desc_at(p_km, 0), desc_at(v_mn, 0), idesc_o, j != 0);
+        const uint32_t p_lo = p_km + (uint32_t)pb * (uint32_t)(kReplTileBytes >> 4);
+        umma_f16(tmem_base + C::kOCol, desc_at(p_lo, 0), desc_at(v_mn, 0), idesc_o, j != 0);
 #pragma unroll
         for (int k = 1; k < TILE / 16; ++k)
-          umma_f16_c<true>(tmem_base + C::kOCol, desc_at(p_km, k_major_step(k, QROWS * 128)), desc_at(v_mn, mn_major_step(k)), idesc_o);
-        tc_commit(pv_done);
-        tc_commit(&kv_empty[j & 1]);
+          umma_f16_c<true>(tmem_base + C::kOCol, desc_at(p_lo, k_major_step(k, QROWS * 128)), desc_at(v_mn, mn_major_step(k)), idesc_o);
+        tc_commit(&pv_done[pb]);
+        tc_commit(&v_empty[j & 1]);
       }
       __syncwarp();
     }
@@ -229,15 +293,19 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const float sl = p.scale * kLog2e;
     float m_run = -INFINITY, l_run = 0.0f;              // l_run: this warp's 16 columns of every tile only
     bool ok = true;
-    // publishes `mine`, waits (bounded) for the other three warps, returns all four values of this row
-    auto exchange = [&](uint32_t phase, float mine, float (&all)[4]) -> bool {
-      float* slot = sExchange + (phase & 1) * 128;
-      slot[quarter * 32 + lane] = mine;
+    // The four warps exchange a value per row through a ring of four slots: `publish` writes this warp's value of
+    // exchange number `x` and arrives, `collect` waits (bounded) until all four have arrived for `x` and reads them.
+    // A warp collects exchange x before it publishes x + 1, so the barrier never runs two phases ahead of a waiter,
+    // and no warp can be four exchanges ahead of another (S tiles are handed back by all four warps).
+    auto publish = [&](uint32_t x, float mine) {
+      sExchange[(x & 3) * 128 + quarter * 32 + lane] = mine;
       __syncwarp();
       if (lane == 0) mbar_arrive(xbar);
-      if (!mbar_wait(xbar, phase & 1, abort_flag, p.status, kPagedKernelId, 9)) return false;
+    };
+    auto collect = [&](uint32_t x, float (&all)[4]) -> bool {
+      if (!mbar_wait(xbar, x & 1, abort_flag, p.status, kPagedKernelId, 9)) return false;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) all[q] = slot[q * 32 + lane];
+      for (int q = 0; q < 4; ++q) all[q] = sExchange[(x & 3) * 128 + q * 32 + lane];
       return true;
     };
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -259,12 +327,20 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         sv[i] = __float_as_uint(x);
         m_loc = fmaxf(m_loc, x);
       }
+      // reference maximum: the first tile waits for its own maxima; tile j > 0 takes those of tile j - 1, which were
+      // published a whole tile ago, and publishes its own for tile j + 1
       float part[4];
-      if (!exchange((uint32_t)j, m_loc, part)) { ok = false; break; }
-      const float m_tile = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
-      // lazy reference maximum (see flash_fwd.cu); every warp sees the same m_tile and decides alike
-      const bool moved = (m_tile - m_run) * sl > 8.0f;
-      const float m_new = moved ? m_tile : m_run;
+      if (j == 0) {
+        publish(0u, m_loc);
+        if (!collect(0u, part)) { ok = false; break; }
+      } else {
+        if (!collect((uint32_t)(j - 1), part)) { ok = false; break; }
+        publish((uint32_t)j, m_loc);
+      }
+      const float m_seen = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+      // lazy reference maximum (see flash_fwd.cu); every warp sees the same m_seen and decides alike
+      const bool moved = (m_seen - m_run) * sl > 8.0f;
+      const float m_new = moved ? m_seen : m_run;
       const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = moved ? exp2f((m_run - m_safe) * sl) : 1.0f;
       const float neg = -m_safe * sl;
@@ -272,42 +348,60 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       uint32_t pk[8];
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
-        const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sl, neg));
-        const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl, neg));
+        // keys of this tile may exceed the reference of the tiles before it: the exponent is capped below overflow
+        const float p0 = exp2f(fminf(fmaf(__uint_as_float(sv[i]), sl, neg), 120.0f));
+        const float p1 = exp2f(fminf(fmaf(__uint_as_float(sv[i + 1]), sl, neg), 120.0f));
         l_tile += p0 + p1;
         pk[i / 2] = pack_bf16x2(p0, p1);
       }
       l_run = l_run * alpha + l_tile;
       m_run = m_new;
-      if (j > 0 && !mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kPagedKernelId, 7)) { ok = false; break; }
-      tc_fence_after_sync();
-      // P row `lane`, key columns of this warp: rows 32..127 of the operand tile are never read back
+      // probability tile j & 1 was last read by the second product of tile j - 2
+      const int pb = j & 1;
+      if (j > 1 && !mbar_wait(&pv_done[pb], (((uint32_t)(j - 2)) >> 1) & 1, abort_flag, p.status, kPagedKernelId, 7)) { ok = false; break; }
+      // P row `lane`, key columns of this warp
+      uint8_t* tile_p = sP + pb * kReplTileBytes;
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch)
-        store_chunk(sP, lane, quarter * 2 + ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
-      if (quarter == 0 && j > 0 && __any_sync(0xffffffffu, moved)) {
+        store_chunk(tile_p, lane, quarter * 2 + ch, make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]));
+      if (j > 0 && __any_sync(0xffffffffu, moved)) {
+        // O changes scale: every product up to tile j - 1 must have landed first (all warps wait, so that none
+        // announces its part of P before the rescaled O is in place ... the first warp rescales)
+        if (!mbar_wait(&pv_done[(j - 1) & 1], (((uint32_t)(j - 1)) >> 1) & 1, abort_flag, p.status, kPagedKernelId, 7)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (quarter == 0) {
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t ov[32];
-          tmem_ld_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
-          tc_wait_ld();
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t ov[32];
+            tmem_ld_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
+            tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st_32x32(tmem_base + (uint32_t)(C::kOCol + c * 32), ov);
+          }
+          tc_wait_st();
         }
-        tc_wait_st();
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[pb]);
     }
     float sums[4] = {0.f, 0.f, 0.f, 0.f};
-    if (ok && n_tiles > 0) ok = exchange((uint32_t)n_tiles, l_run, sums);
+    if (ok && n_tiles > 0) {
+      // exchange n_tiles - 1 (the last tile's maxima) is collected first to keep the order, then the sums go round
+      float unused[4];
+      if (n_tiles > 1) ok = collect((uint32_t)(n_tiles - 1), unused);
+      if (ok) {
+        publish((uint32_t)n_tiles, l_run);
+        ok = collect((uint32_t)n_tiles, sums);
+      }
+    }
     const size_t out_row = (size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h;
     if (p.splits > 1 && quarter == 0 && real && (n_tiles == 0 || !ok))
       p.part_ml[out_row * p.splits + blockIdx.z] = make_float2(0.0f, 0.0f);        // nothing to merge from this part
-    if (ok && quarter == 0 && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
+    if (ok && quarter == 0 && n_tiles > 0 &&
+        mbar_wait(&pv_done[(n_tiles - 1) & 1], (((uint32_t)(n_tiles - 1)) >> 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
       tc_fence_after_sync();
       const float l_all = (sums[0] + sums[1]) + (sums[2] + sums[3]);
       const float inv_l = l_all > 0.0f ? 1.0f / l_all : 0.0f;
@@ -406,7 +500,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[s]);
-      if (j > 0 && !mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag, p.status, kPagedKernelId, 7)) { ok = false; break; }
+      if (j > 0 && !mbar_wait(&pv_done[0], (uint32_t)(j - 1) & 1, abort_flag, p.status, kPagedKernelId, 7)) { ok = false; break; }
       tc_fence_after_sync();
       // inactive quarters write their (zero) rows only once: they never change
       if (active || j == 0) {
@@ -428,12 +522,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[0]);
     }
     const size_t out_row = (size_t)(p.q_start[seq] + qi) * p.heads + kv_head * group + h;
     if (p.splits > 1 && real && (n_tiles == 0 || !ok))
       p.part_ml[out_row * p.splits + blockIdx.z] = make_float2(0.0f, 0.0f);        // nothing to merge from this part
-    if (ok && n_tiles > 0 && mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
+    if (ok && n_tiles > 0 && mbar_wait(&pv_done[0], (uint32_t)(n_tiles - 1) & 1, abort_flag, p.status, kPagedKernelId, 8)) {
       tc_fence_after_sync();
       if (active && p.splits > 1) {
         if (real) p.part_ml[out_row * p.splits + blockIdx.z] = make_float2(m_run == -INFINITY ? 0.0f : m_run * sl, l_run);
