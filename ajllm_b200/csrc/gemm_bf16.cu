@@ -539,6 +539,48 @@ extern "C" int ajb_gemm_bf16_splitk(const void* a, const void* b, void* c, void*
   return 0;
 }
 
+// A few hundred rows (a decoding batch above 128 sequences, a short prompt chunk): out[m, n] bf16 = x[m, k] w[n, k]^T on
+// CTA pairs, where every weight byte is fetched by exactly one CTA (each CTA of a pair stages half of the 256-wide
+// weight tile and 128 of the rows). With few output tiles the K range is cut into slices so that one round of pairs
+// covers the device; the slices add into a zeroed fp32 workspace that is small enough to stay in L2 and a small
+// kernel rounds it to bf16. `split_k` = 0 lets ajb_gemm_skinny_pair_split choose. workspace: m * n floats (split_k > 1).
+extern "C" int ajb_gemm_skinny_pair_split(int m, int n, int k) {
+  using namespace ajb;
+  const int pairs = gemm_pair::capacity();
+  const int tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  const int k_blocks = (k + 63) / 64;
+  // rough cost in units of a quarter microsecond: rounds x (k-blocks of a slice + start-up), plus what the slices'
+  // reductions and the rounding kernel cost (bytes at about 4 TB/s)
+  int best = 1;
+  double best_cost = 1e30;
+  for (int split = 1; split <= 16 && k_blocks / split >= 8; ++split) {
+    const int items = tiles * split;
+    const int rounds = (items + pairs - 1) / pairs;
+    double cost = rounds * ((k_blocks + split - 1) / split + 3.0);
+    if (split > 1) cost += 4.0 + (double)split * m * n * 4.0 / 1.0e6;
+    if (cost < best_cost) { best_cost = cost; best = split; }
+  }
+  return best;
+}
+
+extern "C" int ajb_gemm_bf16_skinny_pair(const void* x, const void* w, void* out, void* workspace, int m, int n, int k,
+                                         long long ldx, long long ldw, int split_k, void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(m > 128 && n > 0 && k > 0 && n % 8 == 0, "skinny pair gemm: needs more than 128 rows and n %% 8 == 0");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (split_k <= 0) split_k = ajb_gemm_skinny_pair_split(m, n, k);
+  if (split_k == 1) return gemm_pair::run(x, w, out, m, n, k, ldx, ldw, n, 0, 0, gemm::kStoreBf16, 1, s);
+  AJB_REQUIRE(workspace != nullptr && (k + 63) / 64 >= split_k, "skinny pair gemm: K slices need a workspace and a k-block each");
+  AJB_CUDA_OK(cudaMemsetAsync(workspace, 0, (size_t)m * n * sizeof(float), s));
+  int rc = gemm_pair::run(x, w, workspace, m, n, k, ldx, ldw, n, 0, 0, gemm::kAtomicAddF32, split_k, s);
+  if (rc) return rc;
+  const long long vecs = (long long)m * n / 8;
+  const int blocks = (int)((vecs + 255) / 256 < (long long)sm_count() * 8 ? (vecs + 255) / 256 : (long long)sm_count() * 8);
+  gemm::splitk_reduce_kernel<<<blocks, 256, 0, s>>>((const float*)workspace, (__nv_bfloat16*)out, vecs, (long long)m * n, 1);
+  AJB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 // Decoding GEMM: out[rows, n] bf16 = x[rows, k] w[n, k]^T for rows <= 128, computed as (w x^T)^T: the tile's
 // 128-row side is filled by weight rows, so there are n / 128 tiles times `split_k` K slices streaming the
 // weights, and the partial products are rows x 128 instead of 128 x 256. workspace: split_k * rows * n floats.

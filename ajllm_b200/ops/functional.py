@@ -227,7 +227,23 @@ class _LinearFn(torch.autograd.Function):
 
 
 _SPLITK_WORKSPACE: dict = {}
+_SPLITK_RETIRED: list = []      # outgrown workspaces stay allocated: a captured graph may still hold their address
 _SKINNY_ROWS = 512
+
+
+def _splitk_workspace(device: torch.device, floats: int) -> torch.Tensor:
+    key = (device.index, )
+    workspace = _SPLITK_WORKSPACE.get(key)
+    if workspace is None or workspace.numel() < floats:
+        if workspace is not None:
+            _SPLITK_RETIRED.append(workspace)
+        workspace = torch.empty(max(floats, 1 << 22), dtype=torch.float32, device=device)
+        _SPLITK_WORKSPACE[key] = workspace
+    return workspace
+# 129 to 512 rows run on CTA pairs with K slices summed in an L2-resident workspace; AJB_SKINNY_PAIR=0 keeps the
+# single-CTA split-K kernel and its separate partial buffers
+SKINNY_PAIR_GEMM = os.environ.get("AJB_SKINNY_PAIR", "1") != "0"
+_SKINNY_SPLITS: dict = {}
 
 
 def linear_skinny(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -237,6 +253,18 @@ def linear_skinny(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     n = weight.shape[0]
     if m <= 128:
         return _linear_decode(x2, weight)
+    if SKINNY_PAIR_GEMM:
+        # CTA pairs: every weight byte is fetched once; K slices (chosen by the library) add into an fp32 workspace
+        split = _SKINNY_SPLITS.get((m, n, k))
+        if split is None:
+            split = _SKINNY_SPLITS[(m, n, k)] = int(native.lib().ajb_gemm_skinny_pair_split(m, n, k))
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x2.device)
+        workspace = None
+        if split > 1:
+            workspace = _splitk_workspace(x2.device, m * n)
+        native.call("ajb_gemm_bf16_skinny_pair", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), native.ptr(workspace), m, n, k,
+                    x2.stride(0), weight.stride(0), split, native.stream_ptr())
+        return out
     tiles = ((m + 127) // 128) * ((n + 255) // 256)
     k_blocks = (k + 63) // 64
     want = max(1, min(k_blocks // 4, (148 + tiles - 1) // tiles))
@@ -245,12 +273,7 @@ def linear_skinny(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     out = torch.empty(m, n, dtype=torch.bfloat16, device=x2.device)
     workspace = None
     if split > 1:
-        key = (x2.device.index, )
-        need = split * m * n
-        workspace = _SPLITK_WORKSPACE.get(key)
-        if workspace is None or workspace.numel() < need:
-            workspace = torch.empty(need, dtype=torch.float32, device=x2.device)
-            _SPLITK_WORKSPACE[key] = workspace
+        workspace = _splitk_workspace(x2.device, split * m * n)
     native.call("ajb_gemm_bf16_splitk", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), native.ptr(workspace), m, n, k,
                 x2.stride(0), weight.stride(0), split, native.stream_ptr())
     return out
@@ -285,12 +308,7 @@ def _linear_decode(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     out = torch.empty(m, n, dtype=torch.bfloat16, device=x2.device)
     workspace = None
     if split > 1:
-        key = (x2.device.index, )
-        need = split * m * n
-        workspace = _SPLITK_WORKSPACE.get(key)
-        if workspace is None or workspace.numel() < need:
-            workspace = torch.empty(need, dtype=torch.float32, device=x2.device)
-            _SPLITK_WORKSPACE[key] = workspace
+        workspace = _splitk_workspace(x2.device, split * m * n)
     native.call("ajb_gemm_bf16_decode", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), native.ptr(workspace), m, n, k,
                 x2.stride(0), weight.stride(0), split, native.stream_ptr())
     return out

@@ -34,6 +34,8 @@ _SIGNATURES: dict[str, list] = {
     "ajb_gemm_bf16_swiglu": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_long,
                              c_int, c_void],
     "ajb_gemm_pair_capacity": [],
+    "ajb_gemm_skinny_pair_split": [c_int, c_int, c_int],
+    "ajb_gemm_bf16_skinny_pair": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_int, c_void],
     "ajb_set_sm_budget": [c_int],
     "ajb_sm_count": [],
     "ajb_gemm_decode_cluster_slices": [c_int, c_int],
@@ -165,7 +167,7 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 
 # kernels launched per entry point (everything else launches one)
-_LAUNCHES_PER_CALL = {"ajb_flash_bwd": 3, "ajb_sumsq_f32": 2, "ajb_gemm_bf16_decode": 2}
+_LAUNCHES_PER_CALL = {"ajb_flash_bwd": 3, "ajb_sumsq_f32": 2, "ajb_gemm_bf16_decode": 2, "ajb_gemm_bf16_skinny_pair": 2}
 launch_count = 0
 
 

@@ -83,7 +83,10 @@ def paged_splits(ctas: int, max_context: int) -> int:
         _SM_COUNT.append(int(native.lib().ajb_sm_count()))
     want = (2 * _SM_COUNT[0]) // max(1, ctas)
     tiles = max(1, (max_context + 63) // 64)
-    return max(1, min(want, tiles, 16))
+    # a part should keep enough 64-key steps to amortise its start and the merge kernel: 16 steps when the launch
+    # already covers half the SMs (measured: 16 sequences x 1024 keys, 24 us whole against 34 us in two parts), 8 below that
+    per_part = 16 if 2 * ctas >= _SM_COUNT[0] else 8
+    return max(1, min(want, tiles // per_part, 16))
 
 
 def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, block_tables: torch.Tensor,

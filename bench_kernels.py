@@ -110,7 +110,7 @@ def run_decode_gemm(dev, small: bool) -> None:
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     base = timeit(lambda: flush.zero_(), iters=20)
     with torch.no_grad():
-        for rows in ((64,) if small else (16, 64, 128)):
+        for rows in ((64,) if small else (16, 64, 128, 256)):
             for n, k in shapes:
                 x = torch.randn(rows, k, device=dev).to(torch.bfloat16)
                 w = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)

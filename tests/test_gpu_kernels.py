@@ -321,7 +321,8 @@ def test_decoding_gemm_with_cluster_reduction(m, n, k):
     assert _rel_err(got, x.float() @ w.float().t()) < 5e-3
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (128, 6144, 4096), (256, 4096, 14336), (40, 1000, 264)])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (128, 6144, 4096), (256, 4096, 14336), (40, 1000, 264),
+                                   (256, 6144, 4096), (200, 28672, 4096), (384, 1000, 512), (512, 4096, 4096)])
 def test_split_k_linear_for_few_rows(m, n, k):
     from ajllm_b200.ops.functional import linear_skinny
 
