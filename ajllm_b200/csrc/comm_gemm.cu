@@ -839,6 +839,11 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
   const bool pair = pairs_enabled && a.mode != kAllReduce && p.m_local % (2 * BM) == 0;   // decoding has too few rows
   p.copy_ctas = gathers ? a.copy_ctas : 0;
   if (pair) p.copy_ctas = (p.copy_ctas + 1) / 2 * 2;      // whole clusters copy
+  // every CTA of this kernel must be resident at once (copy CTAs feed compute CTAs): one CTA per SM, and for the
+  // pair variant as many clusters as the device can hold at once. Under a small SM budget the pulling CTAs are at
+  // most half of the launch.
+  const int grid = pair ? 2 * gemm_pair::capacity() : sm_count();
+  if (gathers && p.copy_ctas * 2 > grid) p.copy_ctas = pair ? (grid / 4) * 2 : grid / 2;
   p.shard_bytes = a.mode == kGatherWeight ? a.shard_elems * 2 : (long long)p.m_local * a.k * 2;
   p.b_offset = a.b_offset_elems * 2;
   p.b_row_bytes = (long long)a.k * 2;
@@ -906,9 +911,6 @@ extern "C" int ajb_comm_gemm(const AjbCommArgs* args, void* stream) {
     }
     configured[which] = true;
   }
-  // every CTA of this kernel must be resident at once (copy CTAs feed compute CTAs): one CTA per SM, and for the
-  // pair variant as many clusters as the device can hold at once
-  const int grid = pair ? 2 * gemm_pair::capacity() : sm_count();
   AJB_REQUIRE(p.copy_ctas < grid && (!gathers || p.copy_ctas >= 1), "comm_gemm: copy CTA count %d is out of range", p.copy_ctas);
   switch (which) {
     case 0: comm_gemm_kernel<false><<<grid, kThreads, Cfg<false>::kSmemBytes, s>>>(map_a, map_b, p); break;

@@ -59,7 +59,12 @@ class FusedTensorParallel:
         # CTAs that pull the peers' shards before they join the products. Two ranks hide their one transfer behind the
         # products with 20; from four ranks on the transfer is the longer part and more pulling SMs shorten it
         # (measured on four GPUs: 588 / 485 / 472 / 444 us for the QKV gather with 20 / 32 / 48 / 64)
-        self.copy_ctas = int(copy_ctas or os.environ.get("AJB_COPY_CTAS", "20" if self.size <= 2 else "48"))
+        fixed = copy_ctas or os.environ.get("AJB_COPY_CTAS")
+        self.copy_ctas = int(fixed or ("20" if self.size <= 2 else "48"))
+        # a gather whose transfer outlasts its products is bound by how many SMs pull (one SM moves about 9 GB/s of
+        # remote data; eight ranks measured 429 GB/s with 48): such calls pull with more CTAs, which join the products
+        # afterwards anyway
+        self.copy_ctas_link_bound = int(fixed or os.environ.get("AJB_COPY_CTAS_LINK", "20" if self.size <= 2 else "96"))
         # Buffers that peers read (staging) or write (receive) exist twice and alternate with the call number, so a
         # call never waits for its peers to finish the same call (csrc/comm_gemm.cu explains the protocol). Gathering
         # calls are counted here; reducing calls are counted on the device so that CUDA graphs can replay them.
@@ -74,11 +79,14 @@ class FusedTensorParallel:
         self._flag_ptrs = list(symm_mem.rendezvous(self._flags, group).buffer_ptrs)
         self._local = torch.zeros(272, dtype=torch.int32, device=device)   # flags, counters, per-group arrival flags
         self._reduce_state = torch.zeros(4, dtype=torch.int32, device=device)   # [calls completed, arrivals expected]
-        # SM budget of the fused kernels. A call whose NVLink transfer takes longer than its tensor work cannot use
-        # the whole device: it is given the share of the SMs that keeps its products in step with the link, and the
-        # rest stays free for kernels on other streams (weight gradients, a second micro-batch). "auto" computes that
-        # share per call; `sm_cap` bounds it (two fused kernels of two micro-batch streams must fit side by side).
-        mode = os.environ.get("AJB_FUSED_SM_BUDGET", "auto")
+        # SM budget of the fused kernels: "off" (default) gives every call the whole device. Moving remote data takes
+        # SMs as well as link time (about 9 GB/s per pulling or pushing SM), so a transfer-bound call finishes soonest
+        # with all of them: on eight ranks, budgets sized by tensor work alone stretched the output projection's
+        # GEMM -> reduce-scatter to 1355 us where NCCL's reduce-scatter plus the GEMM take 1000. "auto" (opt-in) gives
+        # a call the SMs its products or its transfer need, whichever is more, and leaves the rest to kernels on other
+        # streams (weight gradients, a second micro-batch); `sm_cap` bounds it (two fused kernels of two micro-batch
+        # streams must fit side by side).
+        mode = os.environ.get("AJB_FUSED_SM_BUDGET", "off")
         self.sm_budget_mode = mode if mode in ("auto", "off") else int(mode)
         self.sm_cap: int | None = None
         self._sms = int(native.lib().ajb_sm_count())
@@ -127,7 +135,8 @@ class FusedTensorParallel:
         parity = self.gather_calls & 1          # gathering: _next_stage() advanced the count and filled this parity
         args = _CommArgs()
         args.mode, args.m, args.n, args.k = mode, m, n, k
-        args.tp, args.rank, args.b_mn_major, args.copy_ctas = self.size, self.rank, int(b_mn), self.copy_ctas
+        args.tp, args.rank, args.b_mn_major = self.size, self.rank, int(b_mn)
+        args.copy_ctas = self.copy_ctas_link_bound if (gathers and self._link_bound(mode, m, n, k)) else self.copy_ctas
         args.ldb, args.ldc = (b.stride(0) if b.dim() == 2 else k), out.stride(0)
         args.shard_elems, args.b_offset_elems = shard_elems, b_offset_elems
         args.a = a.data_ptr() if a is not None else None
@@ -157,6 +166,17 @@ class FusedTensorParallel:
     # 1.39 PFLOP/s sustained
     LINK_BYTES_PER_S, TENSOR_FLOPS = 750e9, 1.3e15
 
+    def _times(self, mode: int, m: int, n: int, k: int) -> tuple[float, float]:
+        """(seconds on the link, seconds on the tensor cores) of one fused call at the measured rates."""
+        moved = (self.size - 1) / self.size * m * (n if mode == MODE_REDUCE_SCATTER else k) * 2
+        if mode == MODE_GATHER_WEIGHT:
+            moved = (self.size - 1) / self.size * n * k * 2
+        return moved / self.LINK_BYTES_PER_S, 2.0 * m * n * k / self.TENSOR_FLOPS
+
+    def _link_bound(self, mode: int, m: int, n: int, k: int) -> bool:
+        link_s, tensor_s = self._times(mode, m, n, k)
+        return link_s > tensor_s
+
     def _budget(self, mode: int, m: int, n: int, k: int) -> int | None:
         """SMs for one fused call (None: the whole device)."""
         if self.sm_budget_mode == "off" or mode == MODE_ALL_REDUCE:
@@ -164,13 +184,11 @@ class FusedTensorParallel:
         if self.sm_budget_mode != "auto":
             want = int(self.sm_budget_mode)
         else:
-            moved = (self.size - 1) / self.size * m * (n if mode == MODE_REDUCE_SCATTER else k) * 2
-            if mode == MODE_GATHER_WEIGHT:
-                moved = (self.size - 1) / self.size * n * k * 2
-            link_s = moved / self.LINK_BYTES_PER_S
-            tensor_s = 2.0 * m * n * k / self.TENSOR_FLOPS
+            link_s, tensor_s = self._times(mode, m, n, k)
             share = min(1.0, 1.3 * tensor_s / max(link_s, 1e-9))      # 30 % headroom over the break-even share
-            want = max(40, int(self._sms * share) // 2 * 2)
+            # the link needs SMs too: one SM pulls or pushes about 9 GB/s of remote data
+            floor = (self.copy_ctas_link_bound + 32) if mode != MODE_REDUCE_SCATTER else 96
+            want = max(floor, int(self._sms * share) // 2 * 2)
         if self.sm_cap is not None:
             want = min(want, self.sm_cap)
         return None if want >= self._sms - 8 else want

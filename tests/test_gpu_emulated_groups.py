@@ -39,12 +39,14 @@ def test_all_gather_gemm_as_rank_0(tp, m_local, n, k, b_mn):
     weight = w.t().contiguous() if b_mn else w          # stored [k, n] when n-major
     stage = [x[r * m_local:(r + 1) * m_local].contiguous() for r in range(tp)]
     want = x.float() @ w.float().t()
-    for call in range(3):                               # three calls: epochs advance, flags of earlier calls stay behind
+    for call in range(4):                               # four calls: epochs advance, flags of earlier calls stay behind
         gathered = torch.zeros(m, k, device=dev, dtype=BF)
         gathered[:m_local].copy_(stage[0])
         out = torch.zeros(m, n, device=dev, dtype=BF)
+        # the last call asks for more pulling CTAs than its SM budget holds: the launch keeps half of it for the products
+        group.copy_ctas = 96 if call == 3 else 20
         group.launch(MODE_ALL_GATHER, m, n, k, out, b=weight, b_mn=b_mn, gathered=gathered, stage=stage,
-                     sm_budget=64 if call == 2 else None)
+                     sm_budget=64 if call == 2 else (40 if call == 3 else None))
         torch.cuda.synchronize()
         assert torch.equal(gathered, x)
         assert _rel(out, want) < 5e-3, (call, _rel(out, want))
