@@ -61,10 +61,10 @@ class FusedTensorParallel:
         # (measured on four GPUs: 588 / 485 / 472 / 444 us for the QKV gather with 20 / 32 / 48 / 64)
         fixed = copy_ctas or os.environ.get("AJB_COPY_CTAS")
         self.copy_ctas = int(fixed or ("20" if self.size <= 2 else "48"))
-        # a gather whose transfer outlasts its products is bound by how many SMs pull (one SM moves about 9 GB/s of
-        # remote data; eight ranks measured 429 GB/s with 48): such calls pull with more CTAs, which join the products
-        # afterwards anyway
-        self.copy_ctas_link_bound = int(fixed or os.environ.get("AJB_COPY_CTAS_LINK", "20" if self.size <= 2 else "96"))
+        # pulling CTAs of a gather whose transfer outlasts its products (`AJB_COPY_CTAS_LINK`). Same count by default:
+        # on eight ranks 96 instead of 48 moved no more bytes per second (377 against 429 GB/s) and kept the SMs from the
+        # products, 1418 against 918 us for the W13 gather
+        self.copy_ctas_link_bound = int(fixed or os.environ.get("AJB_COPY_CTAS_LINK", str(self.copy_ctas)))
         # Buffers that peers read (staging) or write (receive) exist twice and alternate with the call number, so a
         # call never waits for its peers to finish the same call (csrc/comm_gemm.cu explains the protocol). Gathering
         # calls are counted here; reducing calls are counted on the device so that CUDA graphs can replay them.
