@@ -69,6 +69,7 @@ class FusedTensorParallel:
         # call never waits for its peers to finish the same call (csrc/comm_gemm.cu explains the protocol). Gathering
         # calls are counted here; reducing calls are counted on the device so that CUDA graphs can replay them.
         self.gather_calls = 0
+        self._retired: list = []
         self._stage = [None, None]
         self._recv = [None, None]
         self._stage_ptrs = [None, None]
@@ -104,6 +105,12 @@ class FusedTensorParallel:
         buffers = getattr(self, f"_{which}")
         if buffers[0] is not None and buffers[0].numel() - self.GUARD_BYTES >= nbytes:
             return
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(f"the symmetric {which} buffer would have to grow to {nbytes} bytes during a graph capture; "
+                               "run the step once outside the capture first")
+        # Outgrown buffers stay allocated: a CUDA graph captured earlier carries their (and the peers') addresses in its
+        # kernel arguments, and every rank replays the same graphs, so such a graph keeps exchanging through the old set
+        self._retired.extend(b for b in buffers if b is not None)
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
         size = max(nbytes, 1 << 20)
