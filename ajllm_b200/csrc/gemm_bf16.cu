@@ -554,6 +554,7 @@ extern "C" int ajb_gemm_skinny_pair_split(int m, int n, int k) {
   int best = 1;
   double best_cost = 1e30;
   for (int split = 1; split <= 16 && k_blocks / split >= 8; ++split) {
+    if ((split - 1) * ((k_blocks + split - 1) / split) >= k_blocks) continue;      // the last slice would be empty
     const int items = tiles * split;
     const int rounds = (items + pairs - 1) / pairs;
     double cost = rounds * ((k_blocks + split - 1) / split + 3.0);
@@ -570,7 +571,9 @@ extern "C" int ajb_gemm_bf16_skinny_pair(const void* x, const void* w, void* out
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (split_k <= 0) split_k = ajb_gemm_skinny_pair_split(m, n, k);
   if (split_k == 1) return gemm_pair::run(x, w, out, m, n, k, ldx, ldw, n, 0, 0, gemm::kStoreBf16, 1, s);
-  AJB_REQUIRE(workspace != nullptr && (k + 63) / 64 >= split_k, "skinny pair gemm: K slices need a workspace and a k-block each");
+  const int k_blocks = (k + 63) / 64;
+  AJB_REQUIRE(workspace != nullptr && (split_k - 1) * ((k_blocks + split_k - 1) / split_k) < k_blocks,
+              "skinny pair gemm: K slices need a workspace and at least one k-block each");
   AJB_CUDA_OK(cudaMemsetAsync(workspace, 0, (size_t)m * n * sizeof(float), s));
   int rc = gemm_pair::run(x, w, workspace, m, n, k, ldx, ldw, n, 0, 0, gemm::kAtomicAddF32, split_k, s);
   if (rc) return rc;
