@@ -74,7 +74,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     ap.add_argument("--vocab-size", type=int, default=10000)
     ap.add_argument("--d-model", type=int, default=512)
     ap.add_argument("--num-layers", type=int, default=4)
-    ap.add_argument("--num-heads", type=int, default=4)
+    ap.add_argument("--num-heads", type=int, default=16)
     ap.add_argument("--batch-size", type=int, default=32)
     ap.add_argument("--context-length", type=int, default=256)
     ap.add_argument("--steps", type=int, default=5)
