@@ -29,7 +29,10 @@ constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;
 
-enum Epilogue : int { kStoreBf16 = 0, kAccumF32 = 1, kStoreF32 = 2, kAtomicAddF32 = 3 };
+// kStoreBf16Swiglu / kSwigluBackward: as in gemm_bf16_pair.cu (activation from the (gate, up) product's epilogue; gradient
+// of the pairs from the epilogue of d_out W2), here for the batched per-expert form as well.
+enum Epilogue : int { kStoreBf16 = 0, kAccumF32 = 1, kStoreF32 = 2, kAtomicAddF32 = 3, kStoreBf16Swiglu = 4,
+                      kSwigluBackward = 5 };
 
 template <int BN>
 struct Config {
@@ -38,11 +41,13 @@ struct Config {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
-  static constexpr int kSmemBytes = kStages * kStageBytes + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 256 /*barriers*/ + 4 * kSwigluWarpBytes /*a row block per epilogue warp*/;
 };
 
 struct Params {
   void* c;
+  void* c2;                 // SwiGLU epilogues: the activation (written) or the saved (gate, up) pairs (read)
+  long long ldc2, c2_batch_stride;
   int m, n, k;
   long long ldc;
   int epilogue;
@@ -253,6 +258,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const int col0 = tn * BN;
       const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.m;
+      if (p.epilogue == kSwigluBackward) {
+        // the accumulators are d_act; c2 holds the saved (gate, up) pairs, c receives their gradient (n % 32 == 0)
+        const int row0 = row - lane;
+        const long long at = 2 * col0;
+        swiglu_backward_rows(taddr, reinterpret_cast<const __nv_bfloat16*>(p.c2) + b * p.c2_batch_stride + (long long)row0 * p.ldc2 + at,
+                             p.ldc2, reinterpret_cast<__nv_bfloat16*>(p.c) + b * p.c_batch_stride + (long long)row0 * p.ldc + at, p.ldc,
+                             min(32, p.m - row0), min(BN, p.n - col0),
+                             smem + Cfg::kStages * Cfg::kStageBytes + 256 + quarter * kSwigluWarpBytes, lane);
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
@@ -261,6 +275,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int col = col0 + c;
         if (!row_ok || col >= p.n) continue;
         const int valid = min(32, p.n - col);
+        if (p.epilogue == kStoreBf16Swiglu) {
+          // (gate, up) pairs in neighbouring columns (n % 32 == 0): the pairs go to c (when given), silu(gate) * up to c2
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+          if (p.c != nullptr) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.c) + b * p.c_batch_stride + (long long)row * p.ldc + col);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          }
+          swiglu_store_activation(w, reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.c2) + b * p.c2_batch_stride +
+                                                             (long long)row * p.ldc2 + (col >> 1)));
+          continue;
+        }
         if (p.transpose_c) {
           // consecutive lanes hold consecutive rows: each store instruction writes 32 neighbours of one output row
           const long long base = b * (p.split_k > 1 ? p.split_stride : p.c_batch_stride) + (long long)col * p.ldc + row;
@@ -344,6 +372,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 struct BatchSpec {
   int batch = 1;
   long long a_stride = 0, b_stride = 0, c_stride = 0;   // elements between consecutive problems
+  void* c2 = nullptr;                                    // SwiGLU epilogues: second array, its row and problem strides
+  long long ldc2 = 0, c2_stride = 0;
   const int* valid_rows = nullptr;
   int segment_rows = 0;
   int split_k = 1;
@@ -381,6 +411,7 @@ static int launch(const void* a, const void* b, void* c, int m, int n, int k, lo
   }
   Params p;
   p.c = c; p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.epilogue = epilogue;
+  p.c2 = spec.c2; p.ldc2 = spec.ldc2; p.c2_batch_stride = spec.c2_stride;
   p.tiles_m = (m + BM - 1) / BM;
   p.tiles_n = (n + BN - 1) / BN;
   p.batch = spec.batch;
@@ -515,6 +546,39 @@ extern "C" int ajb_gemm_bf16_batched(const void* a, const void* b, void* c, int 
   spec.valid_rows = (const int*)valid_rows; spec.segment_rows = segment_rows;
   return gemm::dispatch<true>(a, b, c, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, spec,
                               reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Per-expert SwiGLU projections (`batch` problems, operands and outputs `*_stride` elements apart, valid_rows as in
+// ajb_gemm_bf16_batched).
+//   backward = 0: gate_up[b][m, n] = x[b][m, k] w13[b][n, k]^T with (gate, up) pairs in neighbouring columns (gate_up may be
+//                 null) and other[b][m, n / 2] = silu(gate) * up from the same accumulators.
+//   backward = 1: d_act[b][m, n] = d_out[b][m, k] w2[b][k, n] stays in tensor memory; the epilogue reads the saved
+//                 gate_up[b][m, 2 n] and writes other[b][m, 2 n], the gradient of the pairs.
+// n % 32 == 0; row strides multiples of 8; problem strides multiples of 8; bases 16-byte aligned.
+extern "C" int ajb_gemm_bf16_batched_swiglu(const void* a, const void* b, void* gate_up, void* other, int batch, int m, int n,
+                                            int k, long long lda, long long ldb, long long ld_gate_up, long long ld_other,
+                                            long long a_stride, long long b_stride, long long gate_up_stride,
+                                            long long other_stride, int backward, const void* valid_rows, int segment_rows,
+                                            void* stream) {
+  using namespace ajb;
+  AJB_REQUIRE(batch > 0 && m > 0 && n > 0 && k > 0, "batched swiglu gemm: empty problem");
+  AJB_REQUIRE(n % 32 == 0 && ld_gate_up % 8 == 0 && ld_other % 8 == 0 && gate_up_stride % 8 == 0 && other_stride % 8 == 0,
+              "batched swiglu gemm: n must be a multiple of 32, strides multiples of 8");
+  AJB_REQUIRE(other != nullptr && (backward == 0 || gate_up != nullptr), "batched swiglu gemm: missing operand");
+  AJB_REQUIRE(((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(other)) & 15) == 0,
+              "batched swiglu gemm: arrays must be 16-byte aligned");
+  AJB_REQUIRE(valid_rows == nullptr || (segment_rows > 0 && segment_rows % gemm::BM == 0),
+              "batched swiglu gemm: segment_rows must be a positive multiple of %d", gemm::BM);
+  gemm::BatchSpec spec;
+  spec.batch = batch; spec.a_stride = a_stride; spec.b_stride = b_stride;
+  spec.valid_rows = (const int*)valid_rows; spec.segment_rows = segment_rows;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (backward) {
+    spec.c_stride = other_stride; spec.c2 = gate_up; spec.ldc2 = ld_gate_up; spec.c2_stride = gate_up_stride;
+    return gemm::dispatch<true>(a, b, other, m, n, k, lda, ldb, ld_other, 0, 1, gemm::kSwigluBackward, spec, s);
+  }
+  spec.c_stride = gate_up_stride; spec.c2 = other; spec.ldc2 = ld_other; spec.c2_stride = other_stride;
+  return gemm::dispatch<true>(a, b, gate_up, m, n, k, lda, ldb, ld_gate_up, 0, 0, gemm::kStoreBf16Swiglu, spec, s);
 }
 
 // Skinny problems (few rows, e.g. decoding): C[m,n] bf16 = A[m,k] B[n,k]^T with the K range split over `split_k`

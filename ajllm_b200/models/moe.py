@@ -116,8 +116,7 @@ class ExpertBank(nn.Module):
     def forward(self, x: torch.Tensor, valid_rows: torch.Tensor | None = None, segment_rows: int = 0) -> torch.Tensor:
         """All local experts in one batched GEMM per projection; with ``valid_rows`` (rows in use per
         capacity segment) the kernels skip row blocks that hold only padding."""
-        hidden = ops.swiglu_interleaved(ops.linear_batched(x, self.w13, valid_rows, segment_rows))
-        return ops.linear_batched(hidden, self.w2, valid_rows, segment_rows)
+        return ops.swiglu_ffn_batched(x, self.w13, self.w2, valid_rows, segment_rows)
 
 
 class MoEFeedForward(nn.Module):

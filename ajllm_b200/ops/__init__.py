@@ -18,10 +18,11 @@ from ajllm_b200.ops.functional import (
     silu,
     split_packed_qkv,
     swiglu_ffn,
+    swiglu_ffn_batched,
     swiglu_interleaved,
 )
 
 __all__ = [
     "native", "reference", "eager_cuda", "add_rms_norm", "cross_entropy", "embedding", "gemm", "linear",
-    "linear_cross_entropy", "linear_swiglu", "paged_attention_ragged", "rms_norm", "rope_attention", "silu", "split_packed_qkv", "swiglu_ffn", "swiglu_interleaved",
+    "linear_cross_entropy", "linear_swiglu", "paged_attention_ragged", "rms_norm", "rope_attention", "silu", "split_packed_qkv", "swiglu_ffn", "swiglu_ffn_batched", "swiglu_interleaved",
 ]

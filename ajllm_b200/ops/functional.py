@@ -179,6 +179,76 @@ class _BatchedLinearFn(torch.autograd.Function):
         return grad_x, grad_w, None, None
 
 
+def _gemm_batched_swiglu(a, b, gate_up, other, m, n, k, backward: bool, valid_rows, segment_rows) -> None:
+    native.call("ajb_gemm_bf16_batched_swiglu", a.data_ptr(), b.data_ptr(), native.ptr(gate_up), other.data_ptr(), a.shape[0],
+                m, n, k, a.stride(1), b.stride(1), gate_up.stride(1) if gate_up is not None else 0, other.stride(1),
+                a.stride(0), b.stride(0), gate_up.stride(0) if gate_up is not None else 0, other.stride(0),
+                int(backward), native.ptr(valid_rows), segment_rows, native.stream_ptr())
+
+
+class _BatchedSwigluFfnFn(torch.autograd.Function):
+    """Stacked SwiGLU experts ``y[e] = (silu(x[e] W1[e]^T) * x[e] W3[e]^T) W2[e]^T`` with the activation and its gradient
+    computed by the epilogues of the batched GEMMs around them (``w13`` interleaved per expert)."""
+
+    @staticmethod
+    def forward(ctx, x, w13, w2, valid_rows, segment_rows):
+        e, rows, k = x.shape
+        f2, d_out = w13.shape[1], w2.shape[1]
+        x = x.contiguous()
+        make = torch.zeros if valid_rows is not None else torch.empty      # skipped row blocks are never written
+        gate_up = make(e, rows, f2, dtype=torch.bfloat16, device=x.device)
+        act = make(e, rows, f2 // 2, dtype=torch.bfloat16, device=x.device)
+        _gemm_batched_swiglu(x, w13, gate_up, act, rows, f2, k, False, valid_rows, segment_rows)
+        out = make(e, rows, d_out, dtype=torch.bfloat16, device=x.device)
+        gemm_batched(act, w2, out, rows, d_out, f2 // 2, valid_rows=valid_rows, segment_rows=segment_rows)
+        ctx.save_for_backward(x, w13, w2, gate_up, act, valid_rows)
+        ctx.segment_rows = segment_rows
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, w13, w2, gate_up, act, valid_rows = ctx.saved_tensors
+        e, rows, k = x.shape
+        f2, d_out = w13.shape[1], w2.shape[1]
+        f = f2 // 2
+        g = grad_out.contiguous()
+        make = torch.zeros if valid_rows is not None else torch.empty
+        d_gate_up = make(e, rows, f2, dtype=torch.bfloat16, device=g.device)
+        _gemm_batched_swiglu(g, w2, gate_up, d_gate_up, rows, f, d_out, True, valid_rows, ctx.segment_rows)
+        grad_x = grad_w13 = grad_w2 = None
+        if ctx.needs_input_grad[0]:
+            grad_x = make(e, rows, k, dtype=torch.bfloat16, device=g.device)
+            gemm_batched(d_gate_up, w13, grad_x, rows, k, f2, b_mn_major=True, valid_rows=valid_rows,
+                         segment_rows=ctx.segment_rows)
+        # rows past the valid count hold zeros in both operands of the weight gradients (padded dispatch buffer,
+        # zero-initialised intermediates), so the full contraction over rows is exact
+        for weight, left, right, n_out, n_in, slot in ((w2, g, act, d_out, f, 2), (w13, d_gate_up, x, f2, k, 1)):
+            if not ctx.needs_input_grad[slot]:
+                continue
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                gemm_batched(left, right, main, n_out, n_in, rows, a_mn_major=True, b_mn_major=True, epilogue=EPI_ACCUM_F32)
+                weight.main_grad_written = True
+            else:
+                grad = torch.empty(e, n_out, n_in, dtype=torch.bfloat16, device=g.device)
+                gemm_batched(left, right, grad, n_out, n_in, rows, a_mn_major=True, b_mn_major=True)
+                if slot == 2:
+                    grad_w2 = grad
+                else:
+                    grad_w13 = grad
+        return grad_x, grad_w13, grad_w2, None, None
+
+
+def swiglu_ffn_batched(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, valid_rows: torch.Tensor | None = None,
+                       segment_rows: int = 0) -> torch.Tensor:
+    """Stacked SwiGLU experts ``[E, rows, D] -> [E, rows, D]`` (``w13 [E, 2 F, D]`` interleaved, ``w2 [E, D, F]``)."""
+    if (_native(x, "swiglu_ffn_batched") and FUSED_SWIGLU and (w13.shape[1] // 2) % 32 == 0 and x.shape[-1] % 8 == 0
+            and w2.shape[1] % 8 == 0 and w13.is_contiguous() and w2.is_contiguous()):
+        return _BatchedSwigluFfnFn.apply(x, w13, w2, valid_rows, segment_rows)
+    hidden = swiglu_interleaved(linear_batched(x, w13, valid_rows, segment_rows))
+    return linear_batched(hidden, w2, valid_rows, segment_rows)
+
+
 def linear_batched(x: torch.Tensor, weight: torch.Tensor, valid_rows: torch.Tensor | None = None,
                    segment_rows: int = 0) -> torch.Tensor:
     """Stacked-expert projection ``[E, rows, in] x [E, out, in] -> [E, rows, out]``."""

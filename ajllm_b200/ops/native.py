@@ -33,6 +33,8 @@ _SIGNATURES: dict[str, list] = {
                            c_int, c_int, c_int, c_int, c_void],
     "ajb_gemm_bf16_swiglu": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_long, c_long,
                              c_int, c_void],
+    "ajb_gemm_bf16_batched_swiglu": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_long,
+                                     c_long, c_long, c_long, c_long, c_int, c_void, c_int, c_void],
     "ajb_gemm_pair_capacity": [],
     "ajb_gemm_skinny_pair_split": [c_int, c_int, c_int],
     "ajb_gemm_bf16_skinny_pair": [c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_long, c_long, c_int, c_void],

@@ -303,6 +303,39 @@ def test_batched_gemm_with_row_counts():
     assert _rel_err(wg.grad, torch.einsum("ern,erk->enk", g.float(), x.float())) < 5e-3
 
 
+@pytest.mark.parametrize("d_model,d_ff,with_counts", [(256, 352, False), (512, 1408, True), (256, 96, True)])
+def test_stacked_swiglu_experts_in_the_batched_gemm_epilogues(d_model, d_ff, with_counts):
+    """Per-expert SwiGLU blocks with the activation and its gradient inside the batched GEMMs, against fp32 math;
+    with row counts, padding rows (zeros on the way in) stay zero and skipped row blocks are never touched."""
+    torch.manual_seed(61)
+    dev = _dev()
+    e, rows, seg = 3, 512, 256
+    counts = torch.tensor([[256, 100], [0, 129], [17, 0]], dtype=torch.int32, device=dev) if with_counts else None
+    x = torch.randn(e, rows, d_model, device=dev, dtype=torch.bfloat16)
+    g = torch.randn(e, rows, d_model, device=dev, dtype=torch.bfloat16)
+    if with_counts:
+        keep = torch.zeros(e, rows, 1, device=dev, dtype=torch.bool)
+        for b in range(e):
+            for s in range(2):
+                keep[b, s * seg:s * seg + int(counts[b, s])] = True
+        x, g = x * keep, g * keep          # the dispatch buffer holds zeros behind the rows in use
+    x.requires_grad_()
+    w13 = (torch.randn(e, 2 * d_ff, d_model, device=dev) * d_model ** -0.5).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(e, d_model, d_ff, device=dev) * d_ff ** -0.5).to(torch.bfloat16).requires_grad_()
+    before = native.launch_count
+    y = ops.swiglu_ffn_batched(x, w13, w2, counts, seg if with_counts else 0)
+    assert native.launch_count - before == 2
+    y.backward(g)
+    xr, w13r, w2r = (t.detach().float().requires_grad_() for t in (x, w13, w2))
+    hidden = reference.swiglu_interleaved(torch.einsum("erk,enk->ern", xr, w13r))
+    yr = torch.einsum("erf,edf->erd", hidden, w2r)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 8e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(w13.grad, w13r.grad) < 1e-2 and _rel_err(w2.grad, w2r.grad) < 1e-2
+    if with_counts:
+        assert float(y[~keep.expand_as(y)].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 6144, 4096), (64, 4096, 14336), (128, 4096, 4096),
                                    (37, 1000, 4104), (128, 6144, 520)])
 def test_decoding_gemm_with_cluster_reduction(m, n, k):
