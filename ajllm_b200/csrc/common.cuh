@@ -485,9 +485,6 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all_but_two() { asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
-
 // SwiGLU in a GEMM epilogue. A thread holds 32 consecutive accumulator columns of one row.
 // Forward: the columns are 16 (gate, up) pairs, already packed to bf16 in w[16]; 16 activations silu(gate) * up leave
 // as two 16-byte stores to act (32-byte aligned row position).

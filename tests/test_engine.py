@@ -220,3 +220,16 @@ def test_decode_staging_mirrors_the_block_tables_under_churn():
                 assert ctx[i] == q_len and tables[i, 0] == scratch
                 assert list(rows[2, lo:lo+q_len]) == [scratch * 16 + r for r in range(q_len)]
                 assert list(rows[1, lo:lo+q_len]) == list(range(q_len))
+
+
+def test_token_slice_equals_slicing_the_joined_tokens():
+    from ajllm_b200.engine.scheduler import SamplingParams, Sequence
+
+    seq = Sequence(0, list(range(10)), SamplingParams())
+    seq.output.extend(range(100, 107))
+    joined = seq.tokens
+    for start in range(0, 19):
+        for stop in range(start, 19):
+            assert seq.token_slice(start, stop) == joined[start:stop], (start, stop)
+    other = Sequence(0, list(range(10)), SamplingParams())
+    assert seq != other and seq == seq and len({seq, other}) == 2      # identity, not field-wise comparison
