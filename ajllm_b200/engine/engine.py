@@ -331,6 +331,15 @@ class LLMEngine:
         return RequestOutput(seq.request_id, list(seq.prompt[:len(seq.prompt)]), list(seq.output), seq.finish_reason,
                              seq.preemptions, latency)
 
+    def warm_up(self) -> int:
+        """Captures the CUDA graphs of all decoding (and, with a draft model, verification) steps up to the engine's
+        concurrency limit before the first request arrives; a no-op where steps are not replayed from graphs (CPU,
+        expert models, quantised weights under tensor parallelism). Returns the number of graphs held."""
+        graphs = self.runner.capture_decode_graphs(self.scheduler.max_num_seqs, (1, self.k + 1) if self.k else (1,))
+        if self.draft_runner is not None:
+            graphs += self.draft_runner.capture_decode_graphs(self.scheduler.max_num_seqs, (1,))
+        return graphs
+
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None
                  ) -> list[RequestOutput]:
         if not isinstance(params, list):

@@ -208,6 +208,23 @@ class ModelRunner:
         hidden = model.final_norm.add_and_norm(stream, pending)[1]
         return ops.linear(hidden, model.head_weight).float()
 
+    def capture_decode_graphs(self, max_seqs: int, q_lens: tuple[int, ...] = (1,)) -> int:
+        """Captures the decoding graph of every batch-size bucket up to ``max_seqs`` for each number of new tokens per
+        sequence in ``q_lens`` (a start-up cost instead of a stall in the first step that meets a new bucket). Every
+        rank of a tensor-parallel group must call it with the same arguments. Returns the number of graphs held."""
+        if not self.use_graphs:
+            return 0
+        attn0 = self.model.layers[0].attention
+        group = attn0.num_heads // attn0.num_kv_heads
+        top = next((b for b in self.GRAPH_BUCKETS if b >= max_seqs), self.GRAPH_BUCKETS[-1])
+        for q_len in q_lens:
+            if q_len < 1 or q_len > self.cache.block_size or group * q_len > 64:
+                continue
+            for bucket in self.GRAPH_BUCKETS:
+                if bucket <= top:
+                    self._graph_for(bucket, q_len)
+        return len(self._graphs)
+
     def _graph_for(self, bucket: int, q_len: int) -> _DecodeGraph:
         g = self._graphs.get((bucket, q_len))
         if g is not None:

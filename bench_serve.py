@@ -142,7 +142,8 @@ def _one_run(args, model, config, tp, device, rank, world, *, requests, quantiza
                        max_batched_tokens=args.max_batched_tokens, quantization=quantization, draft_model=draft,
                        num_speculative_tokens=speculative or 4, seed=0)
     params = [SamplingParams(n, temperature, None, None, seed=i) for i, n in enumerate(outputs)]
-    # warm-up: a few short requests through every code path
+    # warm-up: the decoding graphs of every batch-size bucket, then a few short requests through every code path
+    engine.warm_up()
     engine.generate([p[:160] for p in prompts[:4]], [SamplingParams(8, temperature, None) for _ in range(4)])
     engine.stats = type(engine.stats)()
     torch.cuda.synchronize()

@@ -233,3 +233,17 @@ def test_token_slice_equals_slicing_the_joined_tokens():
             assert seq.token_slice(start, stop) == joined[start:stop], (start, stop)
     other = Sequence(0, list(range(10)), SamplingParams())
     assert seq != other and seq == seq and len({seq, other}) == 2      # identity, not field-wise comparison
+
+
+def test_warm_up_is_a_no_op_without_graphs():
+    import torch
+
+    from ajllm_b200.engine import LLMEngine, SamplingParams
+    from ajllm_b200.models import build_model
+
+    torch.manual_seed(0)
+    model = build_model({**CFG, "num_layers": 1}, 300)
+    engine = LLMEngine(model, block_size=16, max_num_seqs=4)
+    assert engine.warm_up() == 0
+    out = engine.generate([[1, 2, 3]], SamplingParams(4, 0.0, None, None))
+    assert len(out[0].output) == 4
