@@ -247,3 +247,28 @@ def test_warm_up_is_a_no_op_without_graphs():
     assert engine.warm_up() == 0
     out = engine.generate([[1, 2, 3]], SamplingParams(4, 0.0, None, None))
     assert len(out[0].output) == 4
+
+
+def test_sampling_state_is_reused_while_the_batch_keeps_its_composition():
+    """Seeds and draw counters of the device sampler: rebuilt when the batch changes, advanced in place otherwise, and
+    always equal to what the per-request bookkeeping on the host says."""
+    import torch
+
+    from ajllm_b200.engine import LLMEngine, SamplingParams
+    from ajllm_b200.models import build_model
+
+    torch.manual_seed(0)
+    engine = LLMEngine(build_model({**CFG, "num_layers": 1}, 300), block_size=16, max_num_seqs=4)
+    for seed in (11, 12, 13):
+        engine.add_request([1, 2, 3], SamplingParams(4, 0.7, 0.9, None, seed=seed))
+    seqs = list(engine.scheduler.waiting)
+    cpu = torch.device("cpu")
+    temps, top_ps, seeds, counters = engine._device_sampling_state(seqs, cpu, draws=1)
+    assert seeds.tolist() == [11, 12, 13] and counters.tolist() == [0, 0, 0] and top_ps.tolist() == pytest.approx([0.9] * 3)
+    again = engine._device_sampling_state(seqs, cpu, draws=1)
+    assert again[3] is counters and counters.tolist() == [1, 1, 1]             # same tensors, advanced in place
+    _, _, _, wide = engine._device_sampling_state(seqs, cpu, draws=9)           # another draw width: rebuilt from the host
+    assert wide.tolist() == [2, 2, 2]
+    _, _, seeds2, fewer = engine._device_sampling_state(seqs[1:], cpu, draws=1)  # another composition: rebuilt
+    assert seeds2.tolist() == [12, 13] and fewer.tolist() == [11, 11]
+    assert [engine._draws[s.request_id] for s in seqs] == [11, 12, 12]
